@@ -1,0 +1,99 @@
+"""Build the native parts of the package in-tree.
+
+``lib/libmellin_b200.so``   the C-ABI CUDA library (nvcc, sm_100a only)
+``lib/mellin_torch.so``     the torch binding that registers the ``mellin::``
+                            operators on top of it (g++, links the above)
+
+    python build.py [--force] [--no-torch]
+
+Nothing is installed outside this directory.
+"""
+import os
+import shutil
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+LIBDIR = os.path.join(HERE, "lib")
+INCLUDE = os.path.join(os.path.dirname(HERE), "include")
+CAPI_SO = os.path.join(LIBDIR, "libmellin_b200.so")
+TORCH_SO = os.path.join(LIBDIR, "mellin_torch.so")
+
+CAPI_SOURCES = ["capi.cu", "kernels.cu", "table_cache.cu", "index_map.cpp"]
+CAPI_HEADERS = ["mellin_internal.h", "index_map.h"]
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-lineinfo", "-O3", "-std=c++17", "--use_fast_math=false",
+    "-Xcompiler", "-fPIC", "-shared",
+]
+
+
+def _run(cmd, **kw):
+    proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, **kw)
+    if proc.returncode != 0:
+        raise RuntimeError("command failed: %s\n%s" % (" ".join(cmd), proc.stdout))
+    return proc.stdout
+
+
+def _fresh(target, deps):
+    if not os.path.isfile(target):
+        return False
+    t = os.path.getmtime(target)
+    return all(os.path.getmtime(d) <= t for d in deps)
+
+
+def nvcc_path():
+    cand = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.isfile(cand):
+        raise RuntimeError("nvcc not found")
+    return cand
+
+
+def build_capi(force=False, verbose_ptxas=False):
+    srcs = [os.path.join(CSRC, s) for s in CAPI_SOURCES]
+    deps = srcs + [os.path.join(CSRC, h) for h in CAPI_HEADERS] + [os.path.join(INCLUDE, "mellin_b200.h")]
+    if not force and _fresh(CAPI_SO, deps):
+        return CAPI_SO
+    os.makedirs(LIBDIR, exist_ok=True)
+    flags = [f for f in NVCC_FLAGS if not f.startswith("--use_fast_math")]
+    cmd = [nvcc_path()] + flags + (["-Xptxas", "-v"] if verbose_ptxas else []) + ["-o", CAPI_SO] + srcs
+    out = _run(cmd)
+    if verbose_ptxas:
+        print(out)
+    return CAPI_SO
+
+
+def build_torch_binding(force=False):
+    import torch
+    from torch.utils import cpp_extension
+
+    src = os.path.join(CSRC, "mellin_torch.cpp")
+    if not os.path.isfile(src):
+        return None
+    deps = [src, os.path.join(INCLUDE, "mellin_b200.h"), CAPI_SO]
+    if not force and _fresh(TORCH_SO, deps):
+        return TORCH_SO
+    cxx = shutil.which("g++") or shutil.which("c++")
+    torch_lib = os.path.join(os.path.dirname(torch.__file__), "lib")
+    cuda_home = cpp_extension.CUDA_HOME or "/usr/local/cuda"
+    includes = cpp_extension.include_paths() + [os.path.join(cuda_home, "include"), INCLUDE]
+    cmd = [cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-DTORCH_EXTENSION_NAME=mellin_torch",
+           "-D_GLIBCXX_USE_CXX11_ABI=%d" % int(torch._C._GLIBCXX_USE_CXX11_ABI)]
+    for inc in includes:
+        cmd += ["-isystem", inc]
+    cmd += [src, "-o", TORCH_SO, "-L" + LIBDIR, "-lmellin_b200", "-Wl,-rpath,$ORIGIN",
+            "-L" + torch_lib, "-ltorch", "-ltorch_cpu", "-lc10", "-ltorch_cuda", "-lc10_cuda",
+            "-L" + os.path.join(cuda_home, "lib64"), "-lcudart"]
+    _run(cmd)
+    return TORCH_SO
+
+
+def build(force=False, with_torch=True):
+    capi = build_capi(force)
+    binding = build_torch_binding(force) if with_torch else None
+    return capi, binding
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, with_torch="--no-torch" not in sys.argv))

@@ -1,0 +1,193 @@
+"""ctypes view of the C ABI declared in ``include/mellin_b200.h``.
+
+Used by the tests and the benchmark to call the library exactly as a foreign
+host would: raw device pointers, extents and a stream handle.  Tensors are
+``torch`` CUDA tensors only because torch is how this repository owns device
+memory; nothing here touches their contents.
+"""
+import ctypes
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "lib", "libmellin_b200.so")
+
+_I64 = ctypes.c_int64
+_INT = ctypes.c_int
+_PTR = ctypes.c_void_p
+
+SIZE_FUNCTIONS = {
+    "mellin_mconv_valid_size": 5, "mellin_mconv_support_size": 6, "mellin_mcorr_valid_size": 6,
+    "mellin_mcorr_support_size": 5, "mellin_lconv_valid_size": 4, "mellin_lconv_support_size": 6,
+    "mellin_lcorr_valid_size": 6, "mellin_lcorr_support_size": 4,
+}
+OP1D = ["mellin_mconv1d", "mellin_mcorr1d"]
+OP2D = ["mellin_mconvlconv", "mellin_mcorrlcorr"]
+COL1D = ["mellin_snd2col", "mellin_col2snd"]
+COL2D = ["mellin_spec2col", "mellin_col2spec"]
+LAYER = ["mellin_mcorrlcorr_forward", "mellin_mcorrlcorr_grad_input", "mellin_mcorrlcorr_grad_weight"]
+MISC = ["mellin_abi_version", "mellin_last_error", "mellin_launch_count", "mellin_clear_tables",
+        "mellin_mcorrlcorr_grad_weight_workspace_bytes", "mellin_index_map_build"]
+
+
+def exported_symbols():
+    """Every symbol the header declares."""
+    names = list(SIZE_FUNCTIONS) + MISC
+    for base in OP1D + OP2D + COL1D + COL2D + LAYER:
+        names += [base + "_f32", base + "_f64"]
+    return names
+
+
+class MellinError(RuntimeError):
+    def __init__(self, code, message):
+        super().__init__("mellin_b200 error %d: %s" % (code, message))
+        self.code = code
+
+
+_lib = None
+
+
+def lib():
+    """Load the shared library; fails loudly when it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.isfile(LIB_PATH):
+            raise FileNotFoundError(
+                "%s is missing: run `python cnn-mellin_b200/build.py` (there is no CPU fallback)" % LIB_PATH)
+        _lib = ctypes.CDLL(LIB_PATH)
+        for name, nargs in SIZE_FUNCTIONS.items():
+            fn = getattr(_lib, name)
+            fn.restype, fn.argtypes = _I64, [_I64] * nargs
+        _lib.mellin_last_error.restype = ctypes.c_char_p
+        _lib.mellin_launch_count.restype = _I64
+        _lib.mellin_mcorrlcorr_grad_weight_workspace_bytes.restype = ctypes.c_size_t
+        _lib.mellin_mcorrlcorr_grad_weight_workspace_bytes.argtypes = [_I64] * 17
+    return _lib
+
+
+def _check(code):
+    if code != 0:
+        raise MellinError(code, lib().mellin_last_error().decode())
+
+
+def _sfx(t):
+    import torch
+
+    if t.dtype == torch.float32:
+        return "_f32"
+    if t.dtype == torch.float64:
+        return "_f64"
+    raise TypeError("unsupported dtype %s" % t.dtype)
+
+
+def _p(t):
+    return _PTR(0 if t is None else t.data_ptr())
+
+
+def _stream():
+    import torch
+
+    return _PTR(torch.cuda.current_stream().cuda_stream)
+
+
+def _pair(v):
+    return (int(v), int(v)) if isinstance(v, int) else (int(v[0]), int(v[1]))
+
+
+def index_map(relation, order, nf, ng, nh, s, d, p, u):
+    """Host-side index map as (row_ptr, entries) numpy arrays; needs no GPU."""
+    import numpy as np
+
+    fn = lib().mellin_index_map_build
+    fn.restype = _I64
+    rel = {"corr": 0, "conv": 1}[relation]
+    srt = {"h": 0, "g": 1, "f": 2}[order]
+    args = [_INT(rel), _INT(srt)] + [_I64(v) for v in (nf, ng, nh, s, d, p, u)]
+    count = fn(*args, _PTR(0), _PTR(0), _I64(0))
+    if count < 0:
+        raise MellinError(1, lib().mellin_last_error().decode())
+    rows = {0: nh, 1: ng, 2: nf}[srt]
+    row_ptr = np.zeros(rows + 1, dtype=np.int32)
+    entries = np.zeros((max(count, 1), 2), dtype=np.int32)
+    fn(*args, row_ptr.ctypes.data_as(_PTR), entries.ctypes.data_as(_PTR), _I64(count))
+    return row_ptr, entries[:count]
+
+
+def launch_count():
+    return int(lib().mellin_launch_count())
+
+
+def op2d(name, f, g, h, c_out, c_in, batch, s, d, p, u, tf=False, tg=False, th=False):
+    """``name`` in {"mcorrlcorr", "mconvlconv"}: accumulate into ``h``."""
+    (sx, sy), (dx, dy), (px, py), (ux, uy) = map(_pair, (s, d, p, u))
+    fn = getattr(lib(), "mellin_%s%s" % (name, _sfx(h)))
+    _check(fn(_p(f), _p(g), _I64(c_out), _I64(c_in), _I64(batch), _I64(f.shape[2]), _I64(f.shape[3]),
+              _I64(g.shape[2]), _I64(g.shape[3]), _I64(h.shape[2]), _I64(h.shape[3]), _I64(sx), _I64(sy),
+              _I64(dx), _I64(dy), _I64(px), _I64(py), _I64(ux), _I64(uy), _INT(tf), _INT(tg), _INT(th),
+              _p(h), _stream()))
+    return h
+
+
+def op1d(name, f, g, h, c_out, c_in, batch, s, d, p, u, tf=False, tg=False, th=False):
+    """``name`` in {"mcorr1d", "mconv1d"}: accumulate into ``h``."""
+    fn = getattr(lib(), "mellin_%s%s" % (name, _sfx(h)))
+    _check(fn(_p(f), _p(g), _I64(c_out), _I64(c_in), _I64(batch), _I64(f.shape[2]), _I64(g.shape[2]),
+              _I64(h.shape[2]), _I64(s), _I64(d), _I64(p), _I64(u), _INT(tf), _INT(tg), _INT(th), _p(h),
+              _stream()))
+    return h
+
+
+def col2d(name, src, dst, c_in, batch, nf, ng, ngg, s, d, p, u, tg=False, tgg=False):
+    """``name`` in {"spec2col", "col2spec"}."""
+    (sx, sy), (dx, dy), (px, py), (ux, uy) = map(_pair, (s, d, p, u))
+    fn = getattr(lib(), "mellin_%s%s" % (name, _sfx(dst)))
+    _check(fn(_p(src), _I64(c_in), _I64(batch), _I64(nf[0]), _I64(nf[1]), _I64(ng[0]), _I64(ng[1]),
+              _I64(ngg[0]), _I64(ngg[1]), _I64(sx), _I64(sy), _I64(dx), _I64(dy), _I64(px), _I64(py),
+              _I64(ux), _I64(uy), _INT(tg), _INT(tgg), _p(dst), _stream()))
+    return dst
+
+
+def col1d(name, src, dst, c_in, batch, nf, ng, ngg, s, d, p, u, tg=False, tgg=False):
+    """``name`` in {"snd2col", "col2snd"}."""
+    fn = getattr(lib(), "mellin_%s%s" % (name, _sfx(dst)))
+    _check(fn(_p(src), _I64(c_in), _I64(batch), _I64(nf), _I64(ng), _I64(ngg), _I64(s), _I64(d), _I64(p),
+              _I64(u), _INT(tg), _INT(tgg), _p(dst), _stream()))
+    return dst
+
+
+def _geometry(x_shape, w_shape, y_shape, s, d, p, u):
+    (sx, sy), (dx, dy), (px, py), (ux, uy) = map(_pair, (s, d, p, u))
+    batch, c_in, ngx, ngy = x_shape
+    c_out, _, nfx, nfy = w_shape
+    nhx, nhy = y_shape[2:]
+    return [_I64(v) for v in (batch, c_in, c_out, nfx, nfy, ngx, ngy, nhx, nhy, sx, sy, dx, dy, px, py, ux, uy)]
+
+
+def forward(x, w, bias, y, s, d, p, u):
+    """y = bias + mcorrlcorr(x, w); 4-D tensors (use a singleton last axis for 1-D)."""
+    fn = getattr(lib(), "mellin_mcorrlcorr_forward" + _sfx(y))
+    _check(fn(_p(x), _p(w), _p(bias), *_geometry(x.shape, w.shape, y.shape, s, d, p, u), _p(y), _stream()))
+    return y
+
+
+def grad_input(w, grad_y, grad_x, s, d, p, u):
+    fn = getattr(lib(), "mellin_mcorrlcorr_grad_input" + _sfx(grad_x))
+    _check(fn(_p(w), _p(grad_y), *_geometry(grad_x.shape, w.shape, grad_y.shape, s, d, p, u), _p(grad_x),
+              _stream()))
+    return grad_x
+
+
+def grad_weight_workspace_bytes(x_shape, w_shape, y_shape, s, d, p, u):
+    return int(lib().mellin_mcorrlcorr_grad_weight_workspace_bytes(*_geometry(x_shape, w_shape, y_shape, s, d, p, u)))
+
+
+def grad_weight(x, grad_y, grad_w, grad_b, s, d, p, u, workspace=None):
+    import torch
+
+    geom = _geometry(x.shape, grad_w.shape, grad_y.shape, s, d, p, u)
+    need = int(lib().mellin_mcorrlcorr_grad_weight_workspace_bytes(*geom)) if x.dtype == torch.float32 else 0
+    if workspace is None and need:
+        workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
+    nbytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
+    fn = getattr(lib(), "mellin_mcorrlcorr_grad_weight" + _sfx(grad_w))
+    _check(fn(_p(x), _p(grad_y), *geom, _p(grad_w), _p(grad_b), _p(workspace), ctypes.c_size_t(nbytes), _stream()))
+    return grad_w, grad_b

@@ -1,0 +1,293 @@
+// extern "C" surface of the library: argument validation, translation of the
+// reference's operator vocabulary (f, g, h, transposition flags, s/d/p/u) into
+// the kernels' problem descriptions, table look-up, launch.
+#include <cstdint>
+#include <stdexcept>
+#include <string>
+
+#include "../../include/mellin_b200.h"
+#include "mellin_internal.h"
+
+namespace mellin {
+const std::string &last_error();
+int64_t launch_count();
+}  // namespace mellin
+
+using namespace mellin;
+
+namespace {
+
+constexpr int64_t kMaxExtent = (1LL << 29) - 1;
+
+int64_t floordiv(int64_t a, int64_t b) {
+  int64_t q = a / b;
+  if ((a % b != 0) && ((a < 0) != (b < 0))) --q;
+  return q;
+}
+int64_t nonneg(int64_t v) { return v > 0 ? v : 0; }
+
+struct Geometry2D {
+  int64_t c_out, c_in, batch, nfx, nfy, ngx, ngy, nhx, nhy, sx, sy, dx, dy, px, py, ux, uy;
+};
+
+// Common checks.  Mellin axis: p >= 0 (P = p + 1 is a divisor).  Linear axis:
+// the quantity that ends up as the exact divisor must be >= 1.
+int check_geometry(const char *who, const Geometry2D &q, int64_t linear_divisor) {
+  const int64_t extents[] = {q.c_out, q.c_in, q.batch, q.nfx, q.nfy, q.ngx, q.ngy, q.nhx, q.nhy};
+  for (int64_t e : extents) {
+    if (e < 0) return fail(MELLIN_ERR_BAD_ARGUMENT, std::string(who) + ": negative extent");
+    if (e > kMaxExtent) return fail(MELLIN_ERR_UNSUPPORTED, std::string(who) + ": extent above 2^29 - 1");
+  }
+  const int64_t params[] = {q.sx, q.sy, q.dx, q.dy, q.px, q.py, q.ux, q.uy};
+  for (int64_t e : params)
+    if (e > kMaxExtent || e < -kMaxExtent)
+      return fail(MELLIN_ERR_UNSUPPORTED, std::string(who) + ": parameter magnitude above 2^29 - 1");
+  if (q.px < 0) return fail(MELLIN_ERR_BAD_ARGUMENT, std::string(who) + ": Mellin p must be >= 0");
+  if (linear_divisor < 1)
+    return fail(MELLIN_ERR_BAD_ARGUMENT, std::string(who) + ": linear-axis divisor must be >= 1");
+  return MELLIN_OK;
+}
+
+template <typename T>
+int op2d(const char *who, Relation rel, const T *f, const T *g, const Geometry2D &q, int tf, int tg, int th,
+         T *h, const T *bias, bool accumulate, void *stream) {
+  int rc = check_geometry(who, q, q.uy);
+  if (rc) return rc;
+  const int64_t out_elems = q.batch * q.c_out * q.nhx * q.nhy;
+  if (out_elems == 0) return MELLIN_OK;
+  if (h == nullptr) return fail(MELLIN_ERR_BAD_ARGUMENT, std::string(who) + ": null output");
+  const bool has_terms = q.c_in > 0 && q.nfx > 0 && q.nfy > 0 && q.ngx > 0 && q.ngy > 0;
+  if (has_terms && (f == nullptr || g == nullptr))
+    return fail(MELLIN_ERR_BAD_ARGUMENT, std::string(who) + ": null operand");
+  DirectProblem<T> p;
+  rc = get_device_table(IndexMapKey{rel, SortBy::H, has_terms ? q.nfx : 0, q.ngx, q.nhx, q.sx, q.dx, q.px, q.ux},
+                        &p.table);
+  if (rc) return rc;
+  const int64_t gplane = q.ngx * q.ngy, fplane = q.nfx * q.nfy, hplane = q.nhx * q.nhy;
+  p.in = g, p.w = f, p.bias = bias, p.out = h;
+  p.N = (int)q.batch, p.A = (int)q.c_out, p.B = has_terms ? (int)q.c_in : 0;
+  p.nkx = (int)q.nfx, p.nky = (int)q.nfy, p.nix = (int)q.ngx, p.niy = (int)q.ngy;
+  p.nox = (int)q.nhx, p.noy = (int)q.nhy;
+  p.in_sn = tg ? gplane : q.c_in * gplane;
+  p.in_sb = tg ? q.batch * gplane : gplane;
+  p.w_sa = tf ? fplane : q.c_in * fplane;
+  p.w_sb = tf ? q.c_out * fplane : fplane;
+  p.out_sn = th ? hplane : q.c_out * hplane;
+  p.out_sa = th ? q.batch * hplane : hplane;
+  p.Ay = (int)q.sy;
+  p.By = rel == Relation::Corr ? (int)q.dy : -(int)q.dy;
+  p.Cy = rel == Relation::Corr ? -(int)q.py : (int)q.py;
+  p.Dy = (int)q.uy;
+  p.accumulate = accumulate;
+  return launch_direct<T>(p, static_cast<cudaStream_t>(stream));
+}
+
+template <typename T>
+int grad_input(const char *who, const T *w, const T *go, const Geometry2D &q, T *gx, void *stream) {
+  int rc = check_geometry(who, q, q.sy);
+  if (rc) return rc;
+  if (q.batch * q.c_in * q.ngx * q.ngy == 0) return MELLIN_OK;
+  if (gx == nullptr) return fail(MELLIN_ERR_BAD_ARGUMENT, std::string(who) + ": null output");
+  const bool has_terms = q.c_out > 0 && q.nfx > 0 && q.nfy > 0 && q.nhx > 0 && q.nhy > 0;
+  if (has_terms && (w == nullptr || go == nullptr))
+    return fail(MELLIN_ERR_BAD_ARGUMENT, std::string(who) + ": null operand");
+  DirectProblem<T> p;
+  rc = get_device_table(
+      IndexMapKey{Relation::Corr, SortBy::G, has_terms ? q.nfx : 0, q.ngx, q.nhx, q.sx, q.dx, q.px, q.ux}, &p.table);
+  if (rc) return rc;
+  const int64_t gplane = q.ngx * q.ngy, fplane = q.nfx * q.nfy, hplane = q.nhx * q.nhy;
+  p.in = go, p.w = w, p.bias = nullptr, p.out = gx;
+  p.N = (int)q.batch, p.A = (int)q.c_in, p.B = has_terms ? (int)q.c_out : 0;
+  p.nkx = (int)q.nfx, p.nky = (int)q.nfy, p.nix = (int)q.nhx, p.niy = (int)q.nhy;
+  p.nox = (int)q.ngx, p.noy = (int)q.ngy;
+  p.in_sn = q.c_out * hplane, p.in_sb = hplane;
+  p.w_sa = fplane, p.w_sb = q.c_in * fplane;  // W[a = ci, b = co] = w[co, ci]
+  p.out_sn = q.c_in * gplane, p.out_sa = gplane;
+  // s hy + d fy - p = u gy   =>   hy = (u gy - d fy + p) / s
+  p.Ay = (int)q.uy, p.By = -(int)q.dy, p.Cy = (int)q.py, p.Dy = (int)q.sy;
+  p.accumulate = false;
+  return launch_direct<T>(p, static_cast<cudaStream_t>(stream));
+}
+
+template <typename T>
+int make_gradw_problem(const char *who, const Geometry2D &q, GradWProblem<T> *p, bool need_table) {
+  int rc = check_geometry(who, q, q.uy);
+  if (rc) return rc;
+  p->N = (int)q.batch, p->A = (int)q.c_out, p->B = (int)q.c_in;
+  p->nkx = (int)q.nfx, p->nky = (int)q.nfy, p->nix = (int)q.ngx, p->niy = (int)q.ngy;
+  p->nox = (int)q.nhx, p->noy = (int)q.nhy;
+  p->Ay = (int)q.sy, p->By = (int)q.dy, p->Cy = -(int)q.py, p->Dy = (int)q.uy;
+  if (need_table)
+    rc = get_device_table(IndexMapKey{Relation::Corr, SortBy::F, q.nfx, q.ngx, q.nhx, q.sx, q.dx, q.px, q.ux},
+                          &p->table);
+  return rc;
+}
+
+template <typename T>
+int grad_weight(const char *who, const T *x, const T *go, const Geometry2D &q, T *gw, T *gb, void *workspace,
+                size_t workspace_bytes, void *stream) {
+  GradWProblem<T> p;
+  int rc = make_gradw_problem(who, q, &p, true);
+  if (rc) return rc;
+  const int64_t gw_elems = q.c_out * q.c_in * q.nfx * q.nfy;
+  if (gw_elems > 0 && gw == nullptr) return fail(MELLIN_ERR_BAD_ARGUMENT, std::string(who) + ": null grad_w");
+  const bool has_terms = q.batch > 0 && q.nhx > 0 && q.nhy > 0;
+  if (has_terms && gw_elems > 0 && (x == nullptr || go == nullptr))
+    return fail(MELLIN_ERR_BAD_ARGUMENT, std::string(who) + ": null operand");
+  if (gb != nullptr && has_terms && go == nullptr)
+    return fail(MELLIN_ERR_BAD_ARGUMENT, std::string(who) + ": null grad_y");
+  p.in = x, p.go = go, p.gw = gw, p.gb = gb;
+  if (gw_elems == 0 && (gb == nullptr || q.c_out == 0)) return MELLIN_OK;
+  return launch_gradw<T>(p, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+template <typename T>
+int col_op(const char *who, bool gather, const T *src, T *dst, int64_t c_in, int64_t batch, int64_t nfx,
+           int64_t nfy, int64_t ngx, int64_t ngy, int64_t nggx, int64_t nggy, int64_t sx, int64_t sy, int64_t dx,
+           int64_t dy, int64_t px, int64_t py, int64_t ux, int64_t uy, int tg, int tgg, void *stream) {
+  Geometry2D q{0, c_in, batch, nfx, nfy, ngx, ngy, nggx, nggy, sx, sy, dx, dy, px, py, ux, uy};
+  // gather divides by u on the linear axis, the adjoint by s
+  int rc = check_geometry(who, q, gather ? uy : sy);
+  if (rc) return rc;
+  const int64_t out_elems = gather ? batch * c_in * nfx * nfy * nggx * nggy : batch * c_in * ngx * ngy;
+  if (out_elems == 0) return MELLIN_OK;
+  const int64_t in_elems = gather ? batch * c_in * ngx * ngy : batch * c_in * nfx * nfy * nggx * nggy;
+  if (dst == nullptr || (in_elems > 0 && src == nullptr))
+    return fail(MELLIN_ERR_BAD_ARGUMENT, std::string(who) + ": null pointer");
+  ColProblem<T> p;
+  p.src = src, p.dst = dst, p.N = (int)batch, p.C = (int)c_in;
+  p.nfx = (int)nfx, p.nfy = (int)nfy, p.ngx = (int)ngx, p.ngy = (int)ngy, p.nggx = (int)nggx, p.nggy = (int)nggy;
+  p.sx = (int)sx, p.sy = (int)sy, p.dx = (int)dx, p.dy = (int)dy, p.px = (int)px, p.py = (int)py;
+  p.ux = (int)ux, p.uy = (int)uy;
+  p.transposed_g = tg != 0, p.transposed_gg = tgg != 0;
+  return gather ? launch_spec2col<T>(p, static_cast<cudaStream_t>(stream))
+                : launch_col2spec<T>(p, static_cast<cudaStream_t>(stream));
+}
+
+}  // namespace
+
+extern "C" {
+
+int mellin_abi_version(void) { return 100; }
+const char *mellin_last_error(void) { return last_error().c_str(); }
+int64_t mellin_launch_count(void) { return launch_count(); }
+int mellin_clear_tables(void) { return clear_device_tables(); }
+
+int64_t mellin_mconv_valid_size(int64_t ng, int64_t s, int64_t d, int64_t p, int64_t u) {
+  return nonneg(floordiv(d * (ng + u - 1), p + 1) - s + 1);
+}
+int64_t mellin_mconv_support_size(int64_t nf, int64_t ng, int64_t s, int64_t d, int64_t p, int64_t u) {
+  return nonneg(floordiv((nf + d - 1) * (ng + u - 1), p + 1) - s + 1);
+}
+int64_t mellin_mcorr_valid_size(int64_t nf, int64_t ng, int64_t s, int64_t d, int64_t p, int64_t u) {
+  return nonneg(floordiv((ng + u - 1) * (p + 1), nf + d - 1) - s + 1);
+}
+int64_t mellin_mcorr_support_size(int64_t ng, int64_t s, int64_t d, int64_t p, int64_t u) {
+  return nonneg(floordiv((ng + u - 1) * (p + 1), d) - s + 1);
+}
+int64_t mellin_lconv_valid_size(int64_t ng, int64_t s, int64_t p, int64_t u) {
+  return nonneg(floordiv(u * (ng - 1) - p, s) + 1);
+}
+int64_t mellin_lconv_support_size(int64_t nf, int64_t ng, int64_t s, int64_t d, int64_t p, int64_t u) {
+  return nonneg(floordiv(u * (ng - 1) + d * (nf - 1) - p, s) + 1);
+}
+int64_t mellin_lcorr_valid_size(int64_t nf, int64_t ng, int64_t s, int64_t d, int64_t p, int64_t u) {
+  return nonneg(floordiv(u * (ng - 1) - d * (nf - 1) + p, s) + 1);
+}
+int64_t mellin_lcorr_support_size(int64_t ng, int64_t s, int64_t p, int64_t u) {
+  return nonneg(floordiv(u * (ng - 1) + p, s) + 1);
+}
+
+#define GEOM_FROM_OP2D \
+  Geometry2D { c_out, c_in, batch, nfx, nfy, ngx, ngy, nhx, nhy, sx, sy, dx, dy, px, py, ux, uy }
+#define GEOM_FROM_OP1D \
+  Geometry2D { c_out, c_in, batch, nf, 1, ng, 1, nh, 1, s, 1, d, 1, p, 0, u, 1 }
+#define GEOM_FROM_LAYER \
+  Geometry2D { c_out, c_in, batch, nfx, nfy, ngx, ngy, nhx, nhy, sx, sy, dx, dy, px, py, ux, uy }
+
+#define DEFINE_OPS(T, sfx)                                                                            \
+  MELLIN_DECL_OP1D(mellin_mconv1d_##sfx, T) {                                                         \
+    return op2d<T>("mconv1d", Relation::Conv, f, g, GEOM_FROM_OP1D, transposed_f, transposed_g,       \
+                   transposed_h, h, nullptr, true, stream);                                           \
+  }                                                                                                   \
+  MELLIN_DECL_OP1D(mellin_mcorr1d_##sfx, T) {                                                         \
+    return op2d<T>("mcorr1d", Relation::Corr, f, g, GEOM_FROM_OP1D, transposed_f, transposed_g,       \
+                   transposed_h, h, nullptr, true, stream);                                           \
+  }                                                                                                   \
+  MELLIN_DECL_OP2D(mellin_mconvlconv_##sfx, T) {                                                      \
+    return op2d<T>("mconvlconv", Relation::Conv, f, g, GEOM_FROM_OP2D, transposed_f, transposed_g,    \
+                   transposed_h, h, nullptr, true, stream);                                           \
+  }                                                                                                   \
+  MELLIN_DECL_OP2D(mellin_mcorrlcorr_##sfx, T) {                                                      \
+    return op2d<T>("mcorrlcorr", Relation::Corr, f, g, GEOM_FROM_OP2D, transposed_f, transposed_g,    \
+                   transposed_h, h, nullptr, true, stream);                                           \
+  }                                                                                                   \
+  MELLIN_DECL_COL1D(mellin_snd2col_##sfx, T, g, gg) {                                                 \
+    return col_op<T>("snd2col", true, g, gg, c_in, batch, nf, 1, ng, 1, ngg, 1, s, 1, d, 1, p, 0, u,  \
+                     1, transposed_g, transposed_gg, stream);                                         \
+  }                                                                                                   \
+  MELLIN_DECL_COL1D(mellin_col2snd_##sfx, T, gg, g) {                                                 \
+    return col_op<T>("col2snd", false, gg, g, c_in, batch, nf, 1, ng, 1, ngg, 1, s, 1, d, 1, p, 0, u, \
+                     1, transposed_g, transposed_gg, stream);                                         \
+  }                                                                                                   \
+  MELLIN_DECL_COL2D(mellin_spec2col_##sfx, T, g, gg) {                                                \
+    return col_op<T>("spec2col", true, g, gg, c_in, batch, nfx, nfy, ngx, ngy, nggx, nggy, sx, sy,    \
+                     dx, dy, px, py, ux, uy, transposed_g, transposed_gg, stream);                    \
+  }                                                                                                   \
+  MELLIN_DECL_COL2D(mellin_col2spec_##sfx, T, gg, g) {                                                \
+    return col_op<T>("col2spec", false, gg, g, c_in, batch, nfx, nfy, ngx, ngy, nggx, nggy, sx, sy,   \
+                     dx, dy, px, py, ux, uy, transposed_g, transposed_gg, stream);                    \
+  }                                                                                                   \
+  int mellin_mcorrlcorr_forward_##sfx(const T *x, const T *w, const T *bias, MELLIN_LAYER_GEOMETRY,   \
+                                      T *y, void *stream) {                                           \
+    return op2d<T>("mcorrlcorr_forward", Relation::Corr, w, x, GEOM_FROM_LAYER, 0, 0, 0, y, bias,     \
+                   false, stream);                                                                    \
+  }                                                                                                   \
+  int mellin_mcorrlcorr_grad_input_##sfx(const T *w, const T *grad_y, MELLIN_LAYER_GEOMETRY,          \
+                                         T *grad_x, void *stream) {                                   \
+    return grad_input<T>("mcorrlcorr_grad_input", w, grad_y, GEOM_FROM_LAYER, grad_x, stream);        \
+  }                                                                                                   \
+  int mellin_mcorrlcorr_grad_weight_##sfx(const T *x, const T *grad_y, MELLIN_LAYER_GEOMETRY,         \
+                                          T *grad_w, T *grad_b, void *workspace,                      \
+                                          size_t workspace_bytes, void *stream) {                     \
+    return grad_weight<T>("mcorrlcorr_grad_weight", x, grad_y, GEOM_FROM_LAYER, grad_w, grad_b,       \
+                          workspace, workspace_bytes, stream);                                        \
+  }
+
+DEFINE_OPS(float, f32)
+DEFINE_OPS(double, f64)
+
+int64_t mellin_index_map_build(int relation, int order, int64_t nf, int64_t ng, int64_t nh, int64_t s,
+                               int64_t d, int64_t p, int64_t u, int32_t *row_ptr, int32_t *entries,
+                               int64_t capacity) {
+  if (relation < 0 || relation > 1 || order < 0 || order > 2) {
+    fail(MELLIN_ERR_BAD_ARGUMENT, "index_map_build: relation must be 0/1 and order 0/1/2");
+    return -1;
+  }
+  IndexMap m;
+  try {
+    m = build_index_map(IndexMapKey{static_cast<Relation>(relation), static_cast<SortBy>(order), nf, ng, nh, s, d, p, u});
+  } catch (const std::exception &e) {
+    fail(MELLIN_ERR_BAD_ARGUMENT, e.what());
+    return -1;
+  }
+  if (row_ptr != nullptr)
+    for (size_t i = 0; i < m.row_ptr.size(); ++i) row_ptr[i] = m.row_ptr[i];
+  if (entries != nullptr)
+    for (size_t i = 0; i < m.entries.size() && static_cast<int64_t>(i) < capacity; ++i) {
+      entries[2 * i] = m.entries[i].a;
+      entries[2 * i + 1] = m.entries[i].b;
+    }
+  return static_cast<int64_t>(m.entries.size());
+}
+
+size_t mellin_mcorrlcorr_grad_weight_workspace_bytes(MELLIN_LAYER_GEOMETRY) {
+  GradWProblem<float> p;
+  if (make_gradw_problem<float>("grad_weight_workspace_bytes", GEOM_FROM_LAYER, &p, false)) return 0;
+  // planning only looks at extents, parameters and pointer alignment; probe
+  // with an aligned dummy so that the answer is an upper bound for any buffer
+  p.go = reinterpret_cast<const float *>(uintptr_t(256));
+  return gradw_workspace_bytes<float>(p);
+}
+
+}  // extern "C"

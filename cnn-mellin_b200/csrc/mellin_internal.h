@@ -1,0 +1,96 @@
+// Internal declarations shared by the C-ABI layer and the kernel launchers.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <string>
+
+#include "index_map.h"
+
+namespace mellin {
+
+// ---- error reporting ---------------------------------------------------------
+void set_error(const std::string &msg);
+int fail(int code, const std::string &msg);  // records msg, returns code
+void count_launch(int n = 1);
+
+// ---- device-resident index maps ------------------------------------------------
+struct DeviceTable {
+  const int32_t *row_ptr = nullptr;
+  const int2 *entries = nullptr;
+  const int32_t *order = nullptr;
+  int32_t rows = 0;
+  int32_t max_row = 0;
+  int64_t triples = 0;
+  int64_t num_entries = 0;
+};
+
+// Looks the table up in the per-device cache, building and uploading it on
+// first use (one cudaMalloc + one synchronous cudaMemcpy: a set-up cost paid
+// once per geometry per device).  Returns a status code.
+int get_device_table(const IndexMapKey &key, DeviceTable *out);
+int clear_device_tables();
+int sm_count();  // of the current device (cached)
+
+// ---- problem descriptions ------------------------------------------------------
+//
+// Every multi-channel operator on the path is an instance of
+//
+//   out[n, a, ox, oy] (+)= sum_b sum_{(kx, ix) in row ox of the Mellin table}
+//                        sum_ky W[a, b, kx, ky] * in[n, b, ix, iy(oy, ky)]
+//   iy(oy, ky) = (Ay * oy + By * ky + Cy) / Dy   (exact, 0 <= iy < niy)
+//
+// with arbitrary (n, channel) strides so that the reference's transposition
+// flags and the weight-transposed grad-input form need no copies.
+template <typename T>
+struct DirectProblem {
+  const T *in = nullptr;
+  const T *w = nullptr;
+  const T *bias = nullptr;  // used when !accumulate; may be null
+  T *out = nullptr;
+  DeviceTable table;  // rows = ox, entries (kx, ix)
+  int N = 0, A = 0, B = 0;
+  int nkx = 0, nky = 0, nix = 0, niy = 0, nox = 0, noy = 0;
+  long long in_sn = 0, in_sb = 0;    // element strides of in[n], in[.., b]
+  long long w_sa = 0, w_sb = 0;      // element strides of W[a], W[.., b]; (kx, ky) plane is dense
+  long long out_sn = 0, out_sa = 0;  // element strides of out[n], out[.., a]
+  int Ay = 1, By = 1, Cy = 0, Dy = 1;
+  bool accumulate = false;
+};
+
+// Weight gradient of a correlation layer:
+//   gw[a, b, kx, ky] = sum_n sum_{(ox, ix) in row kx} sum_oy
+//                      go[n, a, ox, oy] * in[n, b, ix, (Ay*oy + By*ky + Cy)/Dy]
+//   gb[a]            = sum_{n, ox, oy} go[n, a, ox, oy]
+// All tensors dense and untransposed.
+template <typename T>
+struct GradWProblem {
+  const T *in = nullptr;   // (N, B, nix, niy)
+  const T *go = nullptr;   // (N, A, nox, noy)
+  T *gw = nullptr;         // (A, B, nkx, nky)
+  T *gb = nullptr;         // (A) or null
+  DeviceTable table;       // rows = kx, entries (ox | flags, ix)
+  int N = 0, A = 0, B = 0;
+  int nkx = 0, nky = 0, nix = 0, niy = 0, nox = 0, noy = 0;
+  int Ay = 1, By = 1, Cy = 0, Dy = 1;
+};
+
+// gather / scatter between a signal and its column form
+template <typename T>
+struct ColProblem {
+  const T *src = nullptr;
+  T *dst = nullptr;
+  int N = 0, C = 0;
+  int nfx = 0, nfy = 0, ngx = 0, ngy = 0, nggx = 0, nggy = 0;
+  int sx = 1, sy = 1, dx = 1, dy = 1, px = 0, py = 0, ux = 1, uy = 1;
+  bool transposed_g = false, transposed_gg = false;
+};
+
+template <typename T> int launch_direct(const DirectProblem<T> &p, cudaStream_t stream);
+template <typename T> size_t gradw_workspace_bytes(const GradWProblem<T> &p);
+template <typename T>
+int launch_gradw(const GradWProblem<T> &p, void *workspace, size_t workspace_bytes, cudaStream_t stream);
+template <typename T> int launch_spec2col(const ColProblem<T> &p, cudaStream_t stream);
+template <typename T> int launch_col2spec(const ColProblem<T> &p, cudaStream_t stream);
+
+}  // namespace mellin

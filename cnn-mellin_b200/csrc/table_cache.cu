@@ -1,0 +1,112 @@
+// Per-device cache of uploaded index maps, error bookkeeping.
+#include <map>
+#include <mutex>
+#include <atomic>
+#include <stdexcept>
+#include <utility>
+#include <vector>
+
+#include "../../include/mellin_b200.h"
+#include "mellin_internal.h"
+
+namespace mellin {
+
+namespace {
+thread_local std::string g_last_error;
+std::atomic<int64_t> g_launches{0};
+
+struct CachedTable {
+  void *block = nullptr;
+  DeviceTable view;
+};
+std::mutex g_mutex;
+std::map<std::pair<int, IndexMapKey>, CachedTable> g_tables;
+std::map<int, int> g_sm_count;
+}  // namespace
+
+void set_error(const std::string &msg) { g_last_error = msg; }
+int fail(int code, const std::string &msg) {
+  g_last_error = msg;
+  return code;
+}
+const std::string &last_error() { return g_last_error; }
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+int64_t launch_count() { return g_launches.load(std::memory_order_relaxed); }
+
+int sm_count() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  auto it = g_sm_count.find(dev);
+  if (it != g_sm_count.end()) return it->second;
+  int n = 0;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  g_sm_count[dev] = n;
+  return n;
+}
+
+int get_device_table(const IndexMapKey &key, DeviceTable *out) {
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return fail(MELLIN_ERR_LAUNCH, std::string("cudaGetDevice: ") + cudaGetErrorString(err));
+  std::lock_guard<std::mutex> lock(g_mutex);
+  auto it = g_tables.find(std::make_pair(dev, key));
+  if (it != g_tables.end()) {
+    *out = it->second.view;
+    return MELLIN_OK;
+  }
+  IndexMap m;
+  try {
+    m = build_index_map(key);
+  } catch (const std::invalid_argument &e) {
+    return fail(MELLIN_ERR_BAD_ARGUMENT, e.what());
+  }
+  // one block: row_ptr | order | entries (entries 8-byte aligned)
+  const size_t n_ptr = m.row_ptr.size(), n_ord = m.order.size(), n_ent = m.entries.size();
+  size_t ints = n_ptr + n_ord;
+  ints += ints & 1;
+  const size_t bytes = ints * sizeof(int32_t) + n_ent * sizeof(Entry);
+  std::vector<int32_t> host(ints + 2 * n_ent, 0);
+  std::copy(m.row_ptr.begin(), m.row_ptr.end(), host.begin());
+  std::copy(m.order.begin(), m.order.end(), host.begin() + n_ptr);
+  for (size_t i = 0; i < n_ent; ++i) {
+    host[ints + 2 * i] = m.entries[i].a;
+    host[ints + 2 * i + 1] = m.entries[i].b;
+  }
+  CachedTable c;
+  err = cudaMalloc(&c.block, bytes > 0 ? bytes : 16);
+  if (err != cudaSuccess) return fail(MELLIN_ERR_LAUNCH, std::string("cudaMalloc(index table): ") + cudaGetErrorString(err));
+  err = cudaMemcpy(c.block, host.data(), bytes, cudaMemcpyHostToDevice);
+  if (err != cudaSuccess) {
+    cudaFree(c.block);
+    return fail(MELLIN_ERR_LAUNCH, std::string("cudaMemcpy(index table): ") + cudaGetErrorString(err));
+  }
+  const int32_t *base = static_cast<const int32_t *>(c.block);
+  c.view.row_ptr = base;
+  c.view.order = base + n_ptr;
+  c.view.entries = reinterpret_cast<const int2 *>(base + ints);
+  c.view.rows = m.rows;
+  c.view.max_row = m.max_row;
+  c.view.triples = m.triples;
+  c.view.num_entries = static_cast<int64_t>(n_ent);
+  g_tables.emplace(std::make_pair(dev, key), c);
+  *out = c.view;
+  return MELLIN_OK;
+}
+
+int clear_device_tables() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return MELLIN_ERR_LAUNCH;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  for (auto it = g_tables.begin(); it != g_tables.end();) {
+    if (it->first.first == dev) {
+      cudaFree(it->second.block);
+      it = g_tables.erase(it);
+    } else {
+      ++it;
+    }
+  }
+  return MELLIN_OK;
+}
+
+}  // namespace mellin

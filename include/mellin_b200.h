@@ -1,0 +1,190 @@
+/* mellin_b200 -- C ABI of the B200 (sm_100a) Mellin / linear correlation and
+ * convolution kernels.
+ *
+ * Every entry point takes plain device pointers, 64-bit extents and a CUDA
+ * stream (passed as void*; a cudaStream_t is a pointer).  Nothing here
+ * depends on PyTorch.  All calls are asynchronous with respect to the host:
+ * they enqueue work on `stream` and return.  The caller owns every buffer.
+ *
+ * Return value: MELLIN_OK (0) or one of the error codes below; a
+ * human-readable description of the most recent failure on the calling thread
+ * is available from mellin_last_error().  Kernels never trap; a failed launch
+ * is reported through the return code.
+ *
+ * Notation (as in the reference, sdrobert/cnn-mellin): f = kernel / weight,
+ * g = signal / input, h = result.  "x" is the Mellin axis (dim 2), "y" the
+ * linear axis (dim 3, contiguous).  With P = p + 1 the taps that contribute are
+ * the integer solutions of
+ *     Mellin correlation:  (hx + s)(fx + d) = P (gx + u)
+ *     Mellin convolution:  P (hx + s)       = (fx + d)(gx + u)
+ *     linear correlation:  s hy + d fy - p  = u gy
+ *     linear convolution:  s hy - d fy + p  = u gy
+ * with 0 <= g < ng.
+ */
+#ifndef MELLIN_B200_H_
+#define MELLIN_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  MELLIN_OK = 0,
+  MELLIN_ERR_BAD_ARGUMENT = 1, /* null pointer, negative extent, zero divisor ... */
+  MELLIN_ERR_LAUNCH = 2,       /* CUDA reported an error for an allocation, copy or launch */
+  MELLIN_ERR_WORKSPACE = 3,    /* workspace missing or smaller than the *_workspace_bytes() answer */
+  MELLIN_ERR_UNSUPPORTED = 4   /* extent beyond what the kernels index (2^31 - 1 per tensor axis product) */
+};
+
+/* Version of this ABI (major * 100 + minor). */
+int mellin_abi_version(void);
+
+/* Description of the last error raised on the calling thread ("" if none). */
+const char *mellin_last_error(void);
+
+/* ---- output sizes ---------------------------------------------------------
+ * Replace the constexpr functions of the reference at
+ * ext/include/cdrobert/mellin/mconv.h:452-672 (Python twins mconv.py:73-118).
+ * "valid": every tap reads inside the signal; "support": at least one tap can.
+ */
+int64_t mellin_mconv_valid_size(int64_t ng, int64_t s, int64_t d, int64_t p, int64_t u);
+int64_t mellin_mconv_support_size(int64_t nf, int64_t ng, int64_t s, int64_t d, int64_t p, int64_t u);
+int64_t mellin_mcorr_valid_size(int64_t nf, int64_t ng, int64_t s, int64_t d, int64_t p, int64_t u);
+int64_t mellin_mcorr_support_size(int64_t ng, int64_t s, int64_t d, int64_t p, int64_t u);
+int64_t mellin_lconv_valid_size(int64_t ng, int64_t s, int64_t p, int64_t u);
+int64_t mellin_lconv_support_size(int64_t nf, int64_t ng, int64_t s, int64_t d, int64_t p, int64_t u);
+int64_t mellin_lcorr_valid_size(int64_t nf, int64_t ng, int64_t s, int64_t d, int64_t p, int64_t u);
+int64_t mellin_lcorr_support_size(int64_t ng, int64_t s, int64_t p, int64_t u);
+
+/* ---- operator-level entry points (accumulate into h) -----------------------
+ * Drop-in for the reference's device entry points MConv1DCuda, MCorr1DCuda,
+ * MConvLConvCuda and MCorrLCorrCuda
+ * (ext/include/cdrobert/mellin/mconv_cuda.cuh:23-71, launchers :962-1052):
+ * same argument order and meaning.  h must be allocated and initialised by
+ * the caller (bias or zero); results are ADDED to it.  A non-zero
+ * transposed_* flag says the operand's two leading extents are swapped in
+ * memory: f is (c_in, c_out, ...), g is (c_in, batch, ...), h is
+ * (c_out, batch, ...).
+ */
+#define MELLIN_DECL_OP1D(name, T)                                                    \
+  int name(const T *f, const T *g, int64_t c_out, int64_t c_in, int64_t batch,        \
+           int64_t nf, int64_t ng, int64_t nh, int64_t s, int64_t d, int64_t p,       \
+           int64_t u, int transposed_f, int transposed_g, int transposed_h, T *h,    \
+           void *stream)
+#define MELLIN_DECL_OP2D(name, T)                                                    \
+  int name(const T *f, const T *g, int64_t c_out, int64_t c_in, int64_t batch,        \
+           int64_t nfx, int64_t nfy, int64_t ngx, int64_t ngy, int64_t nhx,           \
+           int64_t nhy, int64_t sx, int64_t sy, int64_t dx, int64_t dy, int64_t px,   \
+           int64_t py, int64_t ux, int64_t uy, int transposed_f, int transposed_g,   \
+           int transposed_h, T *h, void *stream)
+
+MELLIN_DECL_OP1D(mellin_mconv1d_f32, float);    /* mconv_cuda.cuh:23-33   */
+MELLIN_DECL_OP1D(mellin_mconv1d_f64, double);
+MELLIN_DECL_OP1D(mellin_mcorr1d_f32, float);    /* mconv_cuda.cuh:35-45   */
+MELLIN_DECL_OP1D(mellin_mcorr1d_f64, double);
+MELLIN_DECL_OP2D(mellin_mconvlconv_f32, float); /* mconv_cuda.cuh:47-58   */
+MELLIN_DECL_OP2D(mellin_mconvlconv_f64, double);
+MELLIN_DECL_OP2D(mellin_mcorrlcorr_f32, float); /* mconv_cuda.cuh:60-71   */
+MELLIN_DECL_OP2D(mellin_mcorrlcorr_f64, double);
+
+/* ---- column operators (every output element is written) --------------------
+ * Drop-in for Snd2ColCuda, Col2SndCuda, Spec2ColCuda, Col2SpecCuda
+ * (mconv_cuda.cuh:73-121, launchers :1054-1151).
+ *   snd2col : g (batch, c_in, ng)            -> gg (batch, c_in, nf, ngg)
+ *   col2snd : gg                             -> g    (adjoint: gather-sum)
+ *   spec2col: g (batch, c_in, ngx, ngy)      -> gg (batch, c_in, nfx, nfy, nggx, nggy)
+ *   col2spec: gg                             -> g
+ */
+#define MELLIN_DECL_COL1D(name, T, in, out)                                          \
+  int name(const T *in, int64_t c_in, int64_t batch, int64_t nf, int64_t ng,          \
+           int64_t ngg, int64_t s, int64_t d, int64_t p, int64_t u,                   \
+           int transposed_g, int transposed_gg, T *out, void *stream)
+#define MELLIN_DECL_COL2D(name, T, in, out)                                          \
+  int name(const T *in, int64_t c_in, int64_t batch, int64_t nfx, int64_t nfy,        \
+           int64_t ngx, int64_t ngy, int64_t nggx, int64_t nggy, int64_t sx,          \
+           int64_t sy, int64_t dx, int64_t dy, int64_t px, int64_t py, int64_t ux,    \
+           int64_t uy, int transposed_g, int transposed_gg, T *out, void *stream)
+
+MELLIN_DECL_COL1D(mellin_snd2col_f32, float, g, gg);   /* mconv_cuda.cuh:73-83   */
+MELLIN_DECL_COL1D(mellin_snd2col_f64, double, g, gg);
+MELLIN_DECL_COL1D(mellin_col2snd_f32, float, gg, g);   /* mconv_cuda.cuh:85-95   */
+MELLIN_DECL_COL1D(mellin_col2snd_f64, double, gg, g);
+MELLIN_DECL_COL2D(mellin_spec2col_f32, float, g, gg);  /* mconv_cuda.cuh:97-108  */
+MELLIN_DECL_COL2D(mellin_spec2col_f64, double, g, gg);
+MELLIN_DECL_COL2D(mellin_col2spec_f32, float, gg, g);  /* mconv_cuda.cuh:110-121 */
+MELLIN_DECL_COL2D(mellin_col2spec_f64, double, gg, g);
+
+/* ---- layer-level entry points ----------------------------------------------
+ * One call per tensor a correlation layer produces; they replace what the
+ * reference composes in its torch binding out of the operators above:
+ *   forward     = BuildOutput (bias broadcast / zero fill) followed by
+ *                 mcorrlcorr (ext/torch.cpp:88-101, ext/torch_cuda.cu:144-177);
+ *   grad_input  = mconvlconv(weight^T, grad_out, (s,d,p,u) <- (u,s,p,d))^T
+ *                 (ext/torch.cpp:282-290);
+ *   grad_weight = mcorrlcorr(input^T, grad_out^T, (s,d,p,u) <- (d,s,p,u))^T and
+ *                 grad_bias = grad_out.sum over batch and positions
+ *                 (ext/torch.cpp:292-300).
+ * All tensors are contiguous, untransposed:
+ *   x (batch, c_in, ngx, ngy), w (c_out, c_in, nfx, nfy), bias (c_out) or NULL,
+ *   y / grad_y (batch, c_out, nhx, nhy).
+ * Outputs are WRITTEN (no pre-initialisation needed).  The 1-D Mellin layer
+ * is the case nfy = ngy = nhy = 1, sy = dy = uy = 1, py = 0.
+ */
+#define MELLIN_LAYER_GEOMETRY                                                        \
+  int64_t batch, int64_t c_in, int64_t c_out, int64_t nfx, int64_t nfy, int64_t ngx,  \
+  int64_t ngy, int64_t nhx, int64_t nhy, int64_t sx, int64_t sy, int64_t dx,          \
+  int64_t dy, int64_t px, int64_t py, int64_t ux, int64_t uy
+
+int mellin_mcorrlcorr_forward_f32(const float *x, const float *w, const float *bias,
+                                  MELLIN_LAYER_GEOMETRY, float *y, void *stream);
+int mellin_mcorrlcorr_forward_f64(const double *x, const double *w, const double *bias,
+                                  MELLIN_LAYER_GEOMETRY, double *y, void *stream);
+
+int mellin_mcorrlcorr_grad_input_f32(const float *w, const float *grad_y,
+                                     MELLIN_LAYER_GEOMETRY, float *grad_x, void *stream);
+int mellin_mcorrlcorr_grad_input_f64(const double *w, const double *grad_y,
+                                     MELLIN_LAYER_GEOMETRY, double *grad_x, void *stream);
+
+/* Scratch the grad-weight kernel needs for its per-block partial sums (they
+ * are combined by a second, deterministic pass -- no floating-point atomics).
+ * The answer depends on the geometry and on the current device. */
+size_t mellin_mcorrlcorr_grad_weight_workspace_bytes(MELLIN_LAYER_GEOMETRY);
+
+/* grad_b may be NULL.  workspace must hold at least
+ * mellin_mcorrlcorr_grad_weight_workspace_bytes(...) bytes, 256-byte aligned;
+ * it may be NULL only if that answer is 0.  Its contents are clobbered. */
+int mellin_mcorrlcorr_grad_weight_f32(const float *x, const float *grad_y,
+                                      MELLIN_LAYER_GEOMETRY, float *grad_w, float *grad_b,
+                                      void *workspace, size_t workspace_bytes, void *stream);
+int mellin_mcorrlcorr_grad_weight_f64(const double *x, const double *grad_y,
+                                      MELLIN_LAYER_GEOMETRY, double *grad_w, double *grad_b,
+                                      void *workspace, size_t workspace_bytes, void *stream);
+
+/* ---- diagnostics ------------------------------------------------------------ */
+
+/* Number of kernels this library has launched from the calling process since
+ * it was loaded (all threads, all devices). */
+int64_t mellin_launch_count(void);
+
+/* Drop every cached index table of the current device (frees device memory). */
+int mellin_clear_tables(void);
+
+/* Host-only: build the Mellin index map the kernels consume, for inspection
+ * and validation (no GPU needed).  relation: 0 = correlation, 1 = convolution.
+ * order: 0 = rows are hx, entries (fx, gx); 1 = rows are gx, entries (fx, hx);
+ * 2 = rows are fx, entries (hx | flags, gx) where bit 29 marks the entry that
+ * owns its hx row for the bias sum and bit 30 an hx row no tap reaches.
+ * row_ptr receives rows + 1 ints; entries receives up to `capacity` (a, b)
+ * pairs.  Returns the number of entries of the full table, or -1 on bad
+ * arguments.  Either output pointer may be NULL to query sizes. */
+int64_t mellin_index_map_build(int relation, int order, int64_t nf, int64_t ng, int64_t nh, int64_t s,
+                               int64_t d, int64_t p, int64_t u, int32_t *row_ptr, int32_t *entries,
+                               int64_t capacity);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MELLIN_B200_H_ */

@@ -1,0 +1,226 @@
+"""Acceptance tests of the PyTorch surface (``mconv.py`` + ``torch.ops.mellin``)
+on a B200.  They follow the reference's ``tests/test_mconv.py``: known-answer
+values with and without bias and with the ``r`` argument (:575-647), float64
+``gradcheck`` over the (s, d, p, u) sweep (:663-773), direct-vs-mm equivalence
+(:632-660), training smoke tests (:776-811) and repeatability (:894-919)."""
+import numpy as np
+import pytest
+import torch
+
+import helpers
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def mconv():
+    import mconv as module  # cnn-mellin_b200/mconv.py (conftest puts it on sys.path)
+
+    return module
+
+
+def _conv_ids(kind):
+    return [(op, i) for op, (k, _) in helpers.KAT_CONV_OPS.items() if k == kind for i in range(len(helpers.kat()[op]))]
+
+
+def _with_r(op, g, f_or_size, lead_args, h_exp):
+    """Call once with r = 0 to learn the valid size, then with the r that yields
+    the expected (support-sized) output, as the reference's _test_values does."""
+    nd = h_exp.dim() - 2 if h_exp.dim() <= 4 else 2
+    h0 = op(g, f_or_size, *lead_args)
+    r = [h_exp.size(h_exp.dim() - nd + i) - h0.size(h0.dim() - nd + i) for i in range(nd)]
+    return op(g, f_or_size, *lead_args, r if nd == 2 else r[0])
+
+
+@pytest.mark.parametrize("op,idx", _conv_ids("corr"), ids=lambda v: str(v))
+@pytest.mark.parametrize("bias", [True, False])
+def test_mcorrlcorr_values(mconv, op, idx, bias):
+    prob = helpers.kat_conv_problem(op, idx, np.float32)
+    f, g, h = (torch.from_numpy(prob[k]).cuda() for k in ("f", "g", "h"))
+    b = torch.rand(f.size(0), device="cuda") if bias else None
+    if bias:
+        h = h + b.view(1, -1, 1, 1)
+    got = _with_r(mconv._ext_mcorrlcorr, g, f, (b, prob["s"], prob["d"], prob["p"], prob["u"]), h)
+    assert got.shape == h.shape
+    assert torch.allclose(h, got)
+
+
+@pytest.mark.parametrize("idx", range(len(helpers.kat()["mcorr1d"])))
+@pytest.mark.parametrize("bias", [True, False])
+def test_mcorr1d_values(mconv, idx, bias):
+    prob = helpers.kat_conv_problem("mcorr1d", idx, np.float32)
+    f, g, h = (torch.from_numpy(prob[k][..., 0]).cuda() for k in ("f", "g", "h"))
+    b = torch.rand(f.size(0), device="cuda") if bias else None
+    if bias:
+        h = h + b.view(1, -1, 1)
+    got = _with_r(mconv._ext_mcorr1d, g, f, (b, prob["s"][0], prob["d"][0], prob["p"][0], prob["u"][0]), h)
+    assert got.shape == h.shape
+    assert torch.allclose(h, got)
+
+
+@pytest.mark.parametrize("op,idx", _conv_ids("conv"), ids=lambda v: str(v))
+def test_mconvlconv_values(mconv, op, idx):
+    prob = helpers.kat_conv_problem(op, idx, np.float32)
+    f, g, h = (torch.from_numpy(prob[k]).cuda() for k in ("f", "g", "h"))
+    got = _with_r(torch.ops.mellin.mconvlconv, g, f, (None, prob["s"], prob["d"], prob["p"], prob["u"]), h)
+    assert got.shape == h.shape
+    assert torch.allclose(h, got)
+
+
+def _col_ids(direction):
+    return [(op, i) for op, (k, _) in helpers.KAT_COL_OPS.items() if k == direction
+            for i in range(len(helpers.kat()[op]))]
+
+
+@pytest.mark.parametrize("op,idx", _col_ids("gather"), ids=lambda v: str(v))
+def test_spec2col_values(mconv, op, idx):
+    prob = helpers.kat_col_problem(op, idx, np.float32)
+    g, gg = torch.from_numpy(prob["g"]).cuda(), torch.from_numpy(prob["gg"]).cuda()
+    got = _with_r(mconv._ext_spec2col, g, list(prob["nf"]), (prob["s"], prob["d"], prob["p"], prob["u"]), gg)
+    assert got.shape == gg.shape
+    assert torch.allclose(gg, got)
+
+
+@pytest.mark.parametrize("op,idx", _col_ids("scatter"), ids=lambda v: str(v))
+def test_col2spec_values(mconv, op, idx):
+    prob = helpers.kat_col_problem(op, idx, np.float32)
+    g, gg = torch.from_numpy(prob["g"]).cuda(), torch.from_numpy(prob["gg"]).cuda()
+    got = torch.ops.mellin.col2spec(gg, list(g.shape[2:]), prob["s"], prob["d"], prob["p"], prob["u"])
+    assert torch.allclose(g, got)
+
+
+def test_mcorr1d_impl(mconv):
+    torch.manual_seed(10)
+    batch, c_out, c_in, nf, ng, s, d, p, r = 128, 8, 16, 4, 12, 1, 2, 3, 4
+    f = torch.rand((c_out, c_in, nf), device="cuda")
+    g = torch.rand((batch, c_in, ng), device="cuda")
+    b = torch.rand((c_out,), device="cuda")
+    h_exp = mconv.mcorr1d(g, f, b, s, d, p, r, _impl="direct")
+    h_act = mconv.mcorr1d(g, f, b, s, d, p, r, _impl="mm")
+    assert h_exp.size() == h_act.size()
+    assert torch.allclose(h_exp, h_act, atol=1e-5)
+
+
+def test_mcorrlcorr_impl(mconv):
+    torch.manual_seed(20)
+    batch, c_out, c_in, nf, ng = 64, 16, 8, (32, 32), (8, 8)
+    s, d, p, r = (1, 2), (2, 1), (3, 3), (1, 1)
+    f = torch.rand((c_out, c_in) + nf, device="cuda")
+    g = torch.rand((batch, c_in) + ng, device="cuda")
+    b = torch.rand((c_out,), device="cuda")
+    h_exp = mconv.mcorrlcorr(g, f, b, s, d, p, r, _impl="direct")
+    h_act = mconv.mcorrlcorr(g, f, b, s, d, p, r, _impl="mm")
+    assert h_exp.size() == h_act.size()
+    assert torch.allclose(h_exp, h_act, atol=1e-4, rtol=1e-4)
+
+
+@pytest.mark.parametrize("s", [1, 2])
+@pytest.mark.parametrize("d", [1, 2])
+@pytest.mark.parametrize("p", [3, 4])
+@pytest.mark.parametrize("u", [1, 2])
+@pytest.mark.parametrize("bias", [True, False])
+def test_mcorr1d_gradcheck(mconv, s, d, p, u, bias):
+    c_out, c_in, batch, nf, ng, r = 3, 2, 2, 4, 6, p
+    f = torch.rand((c_out, c_in, nf), dtype=torch.double, device="cuda", requires_grad=True)
+    g = torch.rand((batch, c_in, ng), dtype=torch.double, device="cuda", requires_grad=True)
+    b = torch.rand((c_out,), dtype=torch.double, device="cuda", requires_grad=True) if bias else None
+    assert torch.autograd.gradcheck(mconv._ext_mcorr1d, (g, f, b, s, d, p, u, r))
+
+
+@pytest.mark.parametrize("s", [1, 2])
+@pytest.mark.parametrize("d", [(1, 1), (2, 2), (2, 1)])
+@pytest.mark.parametrize("p", [3, 4])
+@pytest.mark.parametrize("u", [1, 2])
+@pytest.mark.parametrize("extra_layers", [True, False])
+def test_mcorrlcorr_gradcheck(mconv, s, d, p, u, extra_layers):
+    c_out, c_in, batch, nf, ng = 2, 3, 2, (3, 2), (4, 5)
+    f = torch.rand((c_out, c_in) + nf, dtype=torch.double, device="cuda", requires_grad=True)
+    g = torch.rand((batch, c_in) + ng, dtype=torch.double, device="cuda", requires_grad=True)
+    b = torch.rand((c_out,), dtype=torch.double, device="cuda", requires_grad=True)
+    args = ((s, s), d, (p, p), (u, u), (p, p))
+    if extra_layers:
+        m1 = torch.rand((ng[1], ng[1]), dtype=torch.double, device="cuda")
+
+        def func(g_, f_, b_):
+            y = mconv._ext_mcorrlcorr(torch.matmul(g_, m1), f_, b_, *args)
+            return torch.tanh(y).sum(1)
+
+        assert torch.autograd.gradcheck(func, (g, f, b))
+    else:
+        assert torch.autograd.gradcheck(mconv._ext_mcorrlcorr, (g, f, b) + args)
+
+
+@pytest.mark.parametrize("s,d,p,u", [(1, 1, 3, 1), (2, 2, 4, 2), (1, 2, 3, 2)])
+def test_col_gradcheck(mconv, s, d, p, u):
+    g = torch.rand((2, 3, 6), dtype=torch.double, device="cuda", requires_grad=True)
+    assert torch.autograd.gradcheck(mconv._ext_snd2col, (g, 4, s, d, p, u, p))
+    g2 = torch.rand((2, 2, 4, 5), dtype=torch.double, device="cuda", requires_grad=True)
+    assert torch.autograd.gradcheck(mconv._ext_spec2col, (g2, (3, 2), (s, s), (d, d), (p, p), (u, u), (p, p)))
+
+
+def test_can_train_layers(mconv):
+    torch.manual_seed(1)
+    layer = mconv.MCorr1d(4, 5, 12, r=10).cuda()
+    x = torch.rand(3, 4, 40, device="cuda")
+    layer(x).sum().backward()
+    assert layer.weight.grad.abs().sum() > 0 and layer.bias.grad.abs().sum() > 0
+    layer2 = mconv.MCorrLCorr(3, 6, (6, 3), p=(0, 1), r=(35, 1)).cuda()
+    x2 = torch.rand(2, 3, 41, 50, device="cuda", requires_grad=True)
+    y2 = layer2(x2)
+    assert y2.shape == (2, 6, 41, 50)
+    y2.sum().backward()
+    assert layer2.weight.grad.abs().sum() > 0 and layer2.bias.grad.abs().sum() > 0 and x2.grad.abs().sum() > 0
+    assert set(dict(layer2.named_parameters())) == {"weight", "bias"}
+
+
+def test_frozen_inputs_skip_gradients(mconv):
+    w = torch.rand(4, 3, 3, 3, device="cuda", requires_grad=True)
+    x = torch.rand(2, 3, 9, 20, device="cuda")  # no grad wanted for the input
+    y = mconv.mcorrlcorr(x, w, None, 1, 1, (0, 1), (3, 1), _impl="direct")
+    y.sum().backward()
+    assert w.grad is not None and x.grad is None
+
+
+@pytest.mark.parametrize("repeats", [1, 2, 10])
+def test_results_are_repeatable(mconv, repeats):
+    torch.manual_seed(3)
+    layer = mconv.MCorrLCorr(3, 16, (5, 3), p=(0, 1), r=(10, 1)).cuda()
+    x = torch.rand(4, 3, 20, 64, device="cuda", requires_grad=True)
+    first = None
+    for _ in range(repeats):
+        layer.zero_grad()
+        x.grad = None
+        y = layer(x)
+        y.square().sum().backward()
+        now = (y.detach().clone(), x.grad.clone(), layer.weight.grad.clone(), layer.bias.grad.clone())
+        if first is None:
+            first = now
+        else:
+            for a, b in zip(first, now):
+                assert torch.equal(a, b)
+
+
+def test_transposed_operands_need_no_copy(mconv):
+    # dim-0/1 transposes of dense tensors go through the transposition flags
+    torch.manual_seed(5)
+    x = torch.rand(3, 2, 10, 12, device="cuda")
+    w = torch.rand(4, 3, 3, 2, device="cuda")
+    ref = torch.ops.mellin.mcorrlcorr(x.transpose(0, 1).contiguous(), w, None, [1, 1], [1, 1], [0, 1], [1, 1], [2, 1])
+    got = torch.ops.mellin.mcorrlcorr(x.transpose(0, 1), w, None, [1, 1], [1, 1], [0, 1], [1, 1], [2, 1])
+    assert torch.equal(ref, got)
+    wt = w.transpose(0, 1)  # (3, 4, ...) viewed as (c_out=3, c_in=4)
+    x4 = torch.rand(2, 4, 10, 12, device="cuda")
+    ref = torch.ops.mellin.mconvlconv(x4, wt.contiguous(), None, [1, 1], [1, 1], [0, 1], [1, 1], [2, 1])
+    got = torch.ops.mellin.mconvlconv(x4, wt, None, [1, 1], [1, 1], [0, 1], [1, 1], [2, 1])
+    assert torch.equal(ref, got)
+
+
+def test_argument_errors(mconv):
+    with pytest.raises(RuntimeError, match="Expected 3-dimensional"):
+        mconv._ext_mcorr1d(torch.zeros(1, 1, 2, 2, device="cuda"), torch.zeros(1, 1, 2, device="cuda"))
+    with pytest.raises(RuntimeError, match="Expected tensor to have size 3 at dimension 1"):
+        mconv._ext_mcorr1d(torch.zeros(1, 2, 5, device="cuda"), torch.zeros(1, 3, 2, device="cuda"))
+    with pytest.raises(RuntimeError, match="integer or a tuple of 2"):
+        mconv.mcorrlcorr(torch.zeros(1, 1, 2, 2, device="cuda"), torch.zeros(1, 1, 2, 2, device="cuda"), s=(1, 2, 3))
+    with pytest.raises(NotImplementedError):
+        mconv.mcorr1d(torch.zeros(1, 1, 20), torch.zeros(1, 1, 12))  # CPU tensors: no such backend here
