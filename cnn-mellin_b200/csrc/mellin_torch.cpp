@@ -372,9 +372,11 @@ class MCorr1DFunction : public torch::autograd::Function<MCorr1DFunction> {
                                                torch::autograd::tensor_list grads) {
     auto saved = ctx->get_saved_variables();
     auto v = ctx->saved_data["sdpu"].toIntVector();
-    auto out = layer_backward(grads[0], saved[0], saved[1], ctx->saved_data["has_bias"].toBool(), {v[0], 1},
-                              {v[1], 1}, {v[2], 0}, {v[3], 1}, ctx->needs_input_grad(0), ctx->needs_input_grad(1),
-                              ctx->needs_input_grad(2));
+    // gradient edges exist for tensor arguments only; an absent bias has none
+    const bool has_bias = ctx->saved_data["has_bias"].toBool();
+    auto out = layer_backward(grads[0], saved[0], saved[1], has_bias, {v[0], 1}, {v[1], 1}, {v[2], 0}, {v[3], 1},
+                              ctx->needs_input_grad(0), ctx->needs_input_grad(1),
+                              has_bias && ctx->needs_input_grad(2));
     return {out[0], out[1], out[2], Tensor(), Tensor(), Tensor(), Tensor(), Tensor()};
   }
 };
@@ -395,12 +397,13 @@ class MCorrLCorrFunction : public torch::autograd::Function<MCorrLCorrFunction> 
                                                torch::autograd::tensor_list grads) {
     auto saved = ctx->get_saved_variables();
     const char *c = "mcorrlcorr backward";
-    auto out = layer_backward(grads[0], saved[0], saved[1], ctx->saved_data["has_bias"].toBool(),
+    const bool has_bias = ctx->saved_data["has_bias"].toBool();
+    auto out = layer_backward(grads[0], saved[0], saved[1], has_bias,
                               pair_of(ctx->saved_data["s"].toIntVector(), c, "s"),
                               pair_of(ctx->saved_data["d"].toIntVector(), c, "d"),
                               pair_of(ctx->saved_data["p"].toIntVector(), c, "p"),
                               pair_of(ctx->saved_data["u"].toIntVector(), c, "u"), ctx->needs_input_grad(0),
-                              ctx->needs_input_grad(1), ctx->needs_input_grad(2));
+                              ctx->needs_input_grad(1), has_bias && ctx->needs_input_grad(2));
     return {out[0], out[1], out[2], Tensor(), Tensor(), Tensor(), Tensor(), Tensor()};
   }
 };
