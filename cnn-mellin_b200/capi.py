@@ -26,6 +26,8 @@ COL1D = ["mellin_snd2col", "mellin_col2snd"]
 COL2D = ["mellin_spec2col", "mellin_col2spec"]
 LAYER = ["mellin_mcorrlcorr_forward", "mellin_mcorrlcorr_grad_input", "mellin_mcorrlcorr_grad_weight"]
 MISC = ["mellin_abi_version", "mellin_last_error", "mellin_launch_count", "mellin_clear_tables",
+        "mellin_set_tensor_cores", "mellin_device_status", "mellin_mcorrlcorr_forward_workspace_bytes",
+        "mellin_mcorrlcorr_grad_input_workspace_bytes",
         "mellin_mcorrlcorr_grad_weight_workspace_bytes", "mellin_index_map_build"]
 
 
@@ -59,8 +61,9 @@ def lib():
             fn.restype, fn.argtypes = _I64, [_I64] * nargs
         _lib.mellin_last_error.restype = ctypes.c_char_p
         _lib.mellin_launch_count.restype = _I64
-        _lib.mellin_mcorrlcorr_grad_weight_workspace_bytes.restype = ctypes.c_size_t
-        _lib.mellin_mcorrlcorr_grad_weight_workspace_bytes.argtypes = [_I64] * 17
+        for name in ("grad_weight", "forward", "grad_input"):
+            fn = getattr(_lib, "mellin_mcorrlcorr_%s_workspace_bytes" % name)
+            fn.restype, fn.argtypes = ctypes.c_size_t, [_I64] * 17
     return _lib
 
 
@@ -162,17 +165,55 @@ def _geometry(x_shape, w_shape, y_shape, s, d, p, u):
     return [_I64(v) for v in (batch, c_in, c_out, nfx, nfy, ngx, ngy, nhx, nhy, sx, sy, dx, dy, px, py, ux, uy)]
 
 
-def forward(x, w, bias, y, s, d, p, u):
+def set_tensor_cores(enable):
+    """Switch the tcgen05 kernels on/off process-wide; returns the previous setting."""
+    return int(lib().mellin_set_tensor_cores(_INT(1 if enable else 0)))
+
+
+def device_status():
+    """Synchronise and return the tensor-core kernels' timeout code (0 = healthy)."""
+    code = _INT(0)
+    _check(lib().mellin_device_status(ctypes.byref(code)))
+    return code.value
+
+
+def forward_workspace_bytes(x_shape, w_shape, y_shape, s, d, p, u):
+    return int(lib().mellin_mcorrlcorr_forward_workspace_bytes(*_geometry(x_shape, w_shape, y_shape, s, d, p, u)))
+
+
+def grad_input_workspace_bytes(x_shape, w_shape, y_shape, s, d, p, u):
+    return int(lib().mellin_mcorrlcorr_grad_input_workspace_bytes(*_geometry(x_shape, w_shape, y_shape, s, d, p, u)))
+
+
+def _scratch(need, like, workspace):
+    import torch
+
+    if workspace is None and need:
+        workspace = torch.empty(need, dtype=torch.uint8, device=like.device)
+    nbytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
+    return workspace, nbytes
+
+
+def forward(x, w, bias, y, s, d, p, u, workspace=None):
     """y = bias + mcorrlcorr(x, w); 4-D tensors (use a singleton last axis for 1-D)."""
+    import torch
+
+    geom = _geometry(x.shape, w.shape, y.shape, s, d, p, u)
+    need = int(lib().mellin_mcorrlcorr_forward_workspace_bytes(*geom)) if y.dtype == torch.float32 else 0
+    workspace, nbytes = _scratch(need, y, workspace)
     fn = getattr(lib(), "mellin_mcorrlcorr_forward" + _sfx(y))
-    _check(fn(_p(x), _p(w), _p(bias), *_geometry(x.shape, w.shape, y.shape, s, d, p, u), _p(y), _stream()))
+    _check(fn(_p(x), _p(w), _p(bias), *geom, _p(y), _p(workspace), ctypes.c_size_t(nbytes), _stream()))
     return y
 
 
-def grad_input(w, grad_y, grad_x, s, d, p, u):
+def grad_input(w, grad_y, grad_x, s, d, p, u, workspace=None):
+    import torch
+
+    geom = _geometry(grad_x.shape, w.shape, grad_y.shape, s, d, p, u)
+    need = int(lib().mellin_mcorrlcorr_grad_input_workspace_bytes(*geom)) if grad_x.dtype == torch.float32 else 0
+    workspace, nbytes = _scratch(need, grad_x, workspace)
     fn = getattr(lib(), "mellin_mcorrlcorr_grad_input" + _sfx(grad_x))
-    _check(fn(_p(w), _p(grad_y), *_geometry(grad_x.shape, w.shape, grad_y.shape, s, d, p, u), _p(grad_x),
-              _stream()))
+    _check(fn(_p(w), _p(grad_y), *geom, _p(grad_x), _p(workspace), ctypes.c_size_t(nbytes), _stream()))
     return grad_x
 
 

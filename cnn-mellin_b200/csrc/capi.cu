@@ -48,9 +48,24 @@ int check_geometry(const char *who, const Geometry2D &q, int64_t linear_divisor)
   return MELLIN_OK;
 }
 
+// tensor cores when enabled, covered and given scratch; CUDA cores otherwise
+int dispatch_direct(const DirectProblem<float> &p, void *workspace, size_t workspace_bytes, cudaStream_t stream) {
+  if (!p.accumulate && tensor_cores_enabled() && workspace != nullptr) {
+    const size_t need = direct_tc_workspace_bytes(p);
+    if (need > 0 && workspace_bytes >= need) {
+      const int rc = launch_direct_tc(p, workspace, workspace_bytes, stream);
+      if (rc != MELLIN_ERR_UNSUPPORTED) return rc;
+    }
+  }
+  return launch_direct<float>(p, stream);
+}
+int dispatch_direct(const DirectProblem<double> &p, void *, size_t, cudaStream_t stream) {
+  return launch_direct<double>(p, stream);
+}
+
 template <typename T>
 int op2d(const char *who, Relation rel, const T *f, const T *g, const Geometry2D &q, int tf, int tg, int th,
-         T *h, const T *bias, bool accumulate, void *stream) {
+         T *h, const T *bias, bool accumulate, void *workspace, size_t workspace_bytes, void *stream) {
   int rc = check_geometry(who, q, q.uy);
   if (rc) return rc;
   const int64_t out_elems = q.batch * q.c_out * q.nhx * q.nhy;
@@ -79,11 +94,12 @@ int op2d(const char *who, Relation rel, const T *f, const T *g, const Geometry2D
   p.Cy = rel == Relation::Corr ? -(int)q.py : (int)q.py;
   p.Dy = (int)q.uy;
   p.accumulate = accumulate;
-  return launch_direct<T>(p, static_cast<cudaStream_t>(stream));
+  return dispatch_direct(p, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
 template <typename T>
-int grad_input(const char *who, const T *w, const T *go, const Geometry2D &q, T *gx, void *stream) {
+int grad_input(const char *who, const T *w, const T *go, const Geometry2D &q, T *gx, void *workspace,
+               size_t workspace_bytes, void *stream) {
   int rc = check_geometry(who, q, q.sy);
   if (rc) return rc;
   if (q.batch * q.c_in * q.ngx * q.ngy == 0) return MELLIN_OK;
@@ -106,7 +122,7 @@ int grad_input(const char *who, const T *w, const T *go, const Geometry2D &q, T 
   // s hy + d fy - p = u gy   =>   hy = (u gy - d fy + p) / s
   p.Ay = (int)q.uy, p.By = -(int)q.dy, p.Cy = (int)q.py, p.Dy = (int)q.sy;
   p.accumulate = false;
-  return launch_direct<T>(p, static_cast<cudaStream_t>(stream));
+  return dispatch_direct(p, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
 template <typename T>
@@ -208,19 +224,19 @@ int64_t mellin_lcorr_support_size(int64_t ng, int64_t s, int64_t p, int64_t u) {
 #define DEFINE_OPS(T, sfx)                                                                            \
   MELLIN_DECL_OP1D(mellin_mconv1d_##sfx, T) {                                                         \
     return op2d<T>("mconv1d", Relation::Conv, f, g, GEOM_FROM_OP1D, transposed_f, transposed_g,       \
-                   transposed_h, h, nullptr, true, stream);                                           \
+                   transposed_h, h, nullptr, true, nullptr, 0, stream);                                           \
   }                                                                                                   \
   MELLIN_DECL_OP1D(mellin_mcorr1d_##sfx, T) {                                                         \
     return op2d<T>("mcorr1d", Relation::Corr, f, g, GEOM_FROM_OP1D, transposed_f, transposed_g,       \
-                   transposed_h, h, nullptr, true, stream);                                           \
+                   transposed_h, h, nullptr, true, nullptr, 0, stream);                                           \
   }                                                                                                   \
   MELLIN_DECL_OP2D(mellin_mconvlconv_##sfx, T) {                                                      \
     return op2d<T>("mconvlconv", Relation::Conv, f, g, GEOM_FROM_OP2D, transposed_f, transposed_g,    \
-                   transposed_h, h, nullptr, true, stream);                                           \
+                   transposed_h, h, nullptr, true, nullptr, 0, stream);                                           \
   }                                                                                                   \
   MELLIN_DECL_OP2D(mellin_mcorrlcorr_##sfx, T) {                                                      \
     return op2d<T>("mcorrlcorr", Relation::Corr, f, g, GEOM_FROM_OP2D, transposed_f, transposed_g,    \
-                   transposed_h, h, nullptr, true, stream);                                           \
+                   transposed_h, h, nullptr, true, nullptr, 0, stream);                                           \
   }                                                                                                   \
   MELLIN_DECL_COL1D(mellin_snd2col_##sfx, T, g, gg) {                                                 \
     return col_op<T>("snd2col", true, g, gg, c_in, batch, nf, 1, ng, 1, ngg, 1, s, 1, d, 1, p, 0, u,  \
@@ -239,13 +255,15 @@ int64_t mellin_lcorr_support_size(int64_t ng, int64_t s, int64_t p, int64_t u) {
                      dx, dy, px, py, ux, uy, transposed_g, transposed_gg, stream);                    \
   }                                                                                                   \
   int mellin_mcorrlcorr_forward_##sfx(const T *x, const T *w, const T *bias, MELLIN_LAYER_GEOMETRY,   \
-                                      T *y, void *stream) {                                           \
+                                      T *y, void *workspace, size_t workspace_bytes, void *stream) {  \
     return op2d<T>("mcorrlcorr_forward", Relation::Corr, w, x, GEOM_FROM_LAYER, 0, 0, 0, y, bias,     \
-                   false, stream);                                                                    \
+                   false, workspace, workspace_bytes, stream);                                        \
   }                                                                                                   \
   int mellin_mcorrlcorr_grad_input_##sfx(const T *w, const T *grad_y, MELLIN_LAYER_GEOMETRY,          \
-                                         T *grad_x, void *stream) {                                   \
-    return grad_input<T>("mcorrlcorr_grad_input", w, grad_y, GEOM_FROM_LAYER, grad_x, stream);        \
+                                         T *grad_x, void *workspace, size_t workspace_bytes,          \
+                                         void *stream) {                                              \
+    return grad_input<T>("mcorrlcorr_grad_input", w, grad_y, GEOM_FROM_LAYER, grad_x, workspace,      \
+                         workspace_bytes, stream);                                                    \
   }                                                                                                   \
   int mellin_mcorrlcorr_grad_weight_##sfx(const T *x, const T *grad_y, MELLIN_LAYER_GEOMETRY,         \
                                           T *grad_w, T *grad_b, void *workspace,                      \
@@ -256,6 +274,37 @@ int64_t mellin_lcorr_support_size(int64_t ng, int64_t s, int64_t p, int64_t u) {
 
 DEFINE_OPS(float, f32)
 DEFINE_OPS(double, f64)
+
+int mellin_set_tensor_cores(int enable) { return set_tensor_cores(enable); }
+int mellin_device_status(int *code) {
+  if (code == nullptr) return fail(MELLIN_ERR_BAD_ARGUMENT, "device_status: null pointer");
+  return tc_take_error(code);
+}
+
+// Workspace queries plan with the extents only (tables are not needed: the
+// longest table row is bounded by the kernel extent along the Mellin axis).
+static size_t direct_workspace_query(const Geometry2D &q, bool input_gradient) {
+  if (check_geometry("workspace_bytes", q, input_gradient ? q.sy : q.uy)) return 0;
+  DirectProblem<float> p;
+  p.N = (int)q.batch;
+  p.A = input_gradient ? (int)q.c_in : (int)q.c_out;
+  p.B = input_gradient ? (int)q.c_out : (int)q.c_in;
+  p.nkx = (int)q.nfx, p.nky = (int)q.nfy;
+  p.nix = input_gradient ? (int)q.nhx : (int)q.ngx, p.niy = input_gradient ? (int)q.nhy : (int)q.ngy;
+  p.nox = input_gradient ? (int)q.ngx : (int)q.nhx, p.noy = input_gradient ? (int)q.ngy : (int)q.nhy;
+  p.Ay = input_gradient ? (int)q.uy : (int)q.sy;
+  p.By = input_gradient ? -(int)q.dy : (int)q.dy;
+  p.Cy = input_gradient ? (int)q.py : -(int)q.py;
+  p.Dy = input_gradient ? (int)q.sy : (int)q.uy;
+  p.table.max_row = (int)q.nfx;  // upper bound: one entry per kernel tap
+  return direct_tc_workspace_bytes(p);
+}
+size_t mellin_mcorrlcorr_forward_workspace_bytes(MELLIN_LAYER_GEOMETRY) {
+  return direct_workspace_query(GEOM_FROM_LAYER, false);
+}
+size_t mellin_mcorrlcorr_grad_input_workspace_bytes(MELLIN_LAYER_GEOMETRY) {
+  return direct_workspace_query(GEOM_FROM_LAYER, true);
+}
 
 int64_t mellin_index_map_build(int relation, int order, int64_t nf, int64_t ng, int64_t nh, int64_t s,
                                int64_t d, int64_t p, int64_t u, int32_t *row_ptr, int32_t *entries,

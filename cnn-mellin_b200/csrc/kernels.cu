@@ -579,14 +579,26 @@ gradw_tile_kernel(const GradWProblem<float> p, const GradWTiling t, float *__res
   }
 }
 
+// out[i] = sum over slices of part[slice][i].  A block owns 32 outputs; its 8
+// warps split the slices and are combined in a fixed order through shared
+// memory, so the result does not depend on scheduling.
 template <typename T>
 __global__ void reduce_partials_kernel(const T *__restrict__ part, T *__restrict__ out, long long count,
                                        int slices, long long slice_stride) {
-  const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
-  if (i >= count) return;
+  __shared__ T red[8][33];
+  const int lane = threadIdx.x & 31, zs = threadIdx.x >> 5;
+  const long long i = blockIdx.x * 32LL + lane;
   T s = 0;
-  for (int z = 0; z < slices; ++z) s += part[z * slice_stride + i];
-  out[i] = s;
+  if (i < count)
+    for (int z = zs; z < slices; z += 8) s += part[z * slice_stride + i];
+  red[zs][lane] = s;
+  __syncthreads();
+  if (zs == 0 && i < count) {
+    T t = 0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += red[k][lane];
+    out[i] = t;
+  }
 }
 
 bool plan_gradw(const GradWProblem<float> &p, GradWTiling &t, int &RM, int &RN) {
@@ -797,14 +809,13 @@ int launch_gradw<float>(const GradWProblem<float> &p, void *workspace, size_t wo
                    : dispatch_gradw_rn<8>(p, t, RN, part_w, part_b, stream);
   if (rc) return rc;
   const long long gw_elems = (long long)p.A * p.B * p.nkx * p.nky;
-  const int threads = 128;
-  reduce_partials_kernel<float><<<(unsigned)((gw_elems + threads - 1) / threads), threads, 0, stream>>>(
-      part_w, p.gw, gw_elems, t.Z, gw_elems);
+  reduce_partials_kernel<float><<<(unsigned)((gw_elems + 31) / 32), 256, 0, stream>>>(part_w, p.gw, gw_elems, t.Z,
+                                                                                     gw_elems);
   rc = check_launch("reduce_partials_kernel");
   if (rc) return rc;
   if (p.gb != nullptr) {
-    reduce_partials_kernel<float><<<(unsigned)ceil_div(p.A, threads), threads, 0, stream>>>(
-        part_b, p.gb, p.A, p.nkx * t.Z, p.A);
+    reduce_partials_kernel<float><<<(unsigned)ceil_div(p.A, 32), 256, 0, stream>>>(part_b, p.gb, p.A,
+                                                                                   p.nkx * t.Z, p.A);
     rc = check_launch("reduce_partials_kernel(bias)");
   }
   return rc;

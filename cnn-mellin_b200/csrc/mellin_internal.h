@@ -87,6 +87,14 @@ struct ColProblem {
 };
 
 template <typename T> int launch_direct(const DirectProblem<T> &p, cudaStream_t stream);
+// tensor-core path (tc_direct.cu): scratch for the packed hi/lo weights, launch
+// (MELLIN_ERR_UNSUPPORTED when the problem is outside its coverage), and the
+// device-side timeout flag
+size_t direct_tc_workspace_bytes(const DirectProblem<float> &p);
+int launch_direct_tc(const DirectProblem<float> &p, void *workspace, size_t workspace_bytes, cudaStream_t stream);
+int tc_take_error(int *code);
+bool tensor_cores_enabled();
+int set_tensor_cores(int enable);
 template <typename T> size_t gradw_workspace_bytes(const GradWProblem<T> &p);
 template <typename T>
 int launch_gradw(const GradWProblem<T> &p, void *workspace, size_t workspace_bytes, cudaStream_t stream);

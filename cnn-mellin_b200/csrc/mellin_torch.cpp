@@ -158,14 +158,17 @@ Tensor conv_like(const char *c, Op op, int64_t dim, const Tensor &input, const T
     LayerGeometry q{a.batch, a.c_in, a.c_out, a.nfx, a.nfy, a.ngx, a.ngy, nhx, nhy, s, d, p, u};
     Tensor b = bias ? bias->contiguous() : Tensor();
     int rc;
-    if (f64)
+    if (f64) {
       rc = mellin_mcorrlcorr_forward_f64(a.g.dense.data_ptr<double>(), a.f.dense.data_ptr<double>(),
                                          bias ? b.data_ptr<double>() : nullptr, LAYER_ARGS(q), out.data_ptr<double>(),
-                                         stream);
-    else
+                                         nullptr, 0, stream);
+    } else {
+      const size_t bytes = mellin_mcorrlcorr_forward_workspace_bytes(LAYER_ARGS(q));
+      Tensor ws = at::empty({static_cast<int64_t>(bytes ? bytes : 16)}, weight.options().dtype(at::kByte));
       rc = mellin_mcorrlcorr_forward_f32(a.g.dense.data_ptr<float>(), a.f.dense.data_ptr<float>(),
                                          bias ? b.data_ptr<float>() : nullptr, LAYER_ARGS(q), out.data_ptr<float>(),
-                                         stream);
+                                         ws.data_ptr(), bytes, stream);
+    }
     check_status(rc, c);
     return out;
   }
@@ -334,10 +337,12 @@ std::vector<Tensor> layer_backward(const Tensor &grad_out_in, const Tensor &inpu
   Tensor gi, gw, gb;
   if (need_input) {
     gi = at::empty_like(x);
+    const size_t gi_bytes = f64 ? 0 : mellin_mcorrlcorr_grad_input_workspace_bytes(LAYER_ARGS(q));
+    Tensor gi_ws = at::empty({static_cast<int64_t>(gi_bytes ? gi_bytes : 16)}, w.options().dtype(at::kByte));
     int rc = f64 ? mellin_mcorrlcorr_grad_input_f64(w.data_ptr<double>(), go.data_ptr<double>(), LAYER_ARGS(q),
-                                                     gi.data_ptr<double>(), stream)
+                                                     gi.data_ptr<double>(), nullptr, 0, stream)
                  : mellin_mcorrlcorr_grad_input_f32(w.data_ptr<float>(), go.data_ptr<float>(), LAYER_ARGS(q),
-                                                     gi.data_ptr<float>(), stream);
+                                                     gi.data_ptr<float>(), gi_ws.data_ptr(), gi_bytes, stream);
     check_status(rc, "mcorrlcorr_grad_input");
   }
   if (need_weight || (need_bias && has_bias)) {

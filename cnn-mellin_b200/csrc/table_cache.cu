@@ -14,6 +14,7 @@ namespace mellin {
 namespace {
 thread_local std::string g_last_error;
 std::atomic<int64_t> g_launches{0};
+std::atomic<int> g_tensor_cores{1};
 
 struct CachedTable {
   void *block = nullptr;
@@ -32,6 +33,9 @@ int fail(int code, const std::string &msg) {
 const std::string &last_error() { return g_last_error; }
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 int64_t launch_count() { return g_launches.load(std::memory_order_relaxed); }
+
+bool tensor_cores_enabled() { return g_tensor_cores.load(std::memory_order_relaxed) != 0; }
+int set_tensor_cores(int enable) { return g_tensor_cores.exchange(enable ? 1 : 0); }
 
 int sm_count() {
   int dev = 0;

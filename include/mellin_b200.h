@@ -138,15 +138,28 @@ MELLIN_DECL_COL2D(mellin_col2spec_f64, double, gg, g);
   int64_t ngy, int64_t nhx, int64_t nhy, int64_t sx, int64_t sy, int64_t dx,          \
   int64_t dy, int64_t px, int64_t py, int64_t ux, int64_t uy
 
+/* Scratch for the tensor-core path of forward / grad_input (packed hi/lo weight
+ * copies; 37 KB for a 3->64 channel 8x3 kernel).  0 means the geometry is served
+ * by the CUDA-core kernels and needs none. */
+size_t mellin_mcorrlcorr_forward_workspace_bytes(MELLIN_LAYER_GEOMETRY);
+size_t mellin_mcorrlcorr_grad_input_workspace_bytes(MELLIN_LAYER_GEOMETRY);
+
+/* workspace: at least the *_workspace_bytes() answer, 16-byte aligned, clobbered.
+ * With a NULL or smaller workspace the call still succeeds on the CUDA-core
+ * kernels (float64 always uses them). */
 int mellin_mcorrlcorr_forward_f32(const float *x, const float *w, const float *bias,
-                                  MELLIN_LAYER_GEOMETRY, float *y, void *stream);
+                                  MELLIN_LAYER_GEOMETRY, float *y, void *workspace,
+                                  size_t workspace_bytes, void *stream);
 int mellin_mcorrlcorr_forward_f64(const double *x, const double *w, const double *bias,
-                                  MELLIN_LAYER_GEOMETRY, double *y, void *stream);
+                                  MELLIN_LAYER_GEOMETRY, double *y, void *workspace,
+                                  size_t workspace_bytes, void *stream);
 
 int mellin_mcorrlcorr_grad_input_f32(const float *w, const float *grad_y,
-                                     MELLIN_LAYER_GEOMETRY, float *grad_x, void *stream);
+                                     MELLIN_LAYER_GEOMETRY, float *grad_x, void *workspace,
+                                     size_t workspace_bytes, void *stream);
 int mellin_mcorrlcorr_grad_input_f64(const double *w, const double *grad_y,
-                                     MELLIN_LAYER_GEOMETRY, double *grad_x, void *stream);
+                                     MELLIN_LAYER_GEOMETRY, double *grad_x, void *workspace,
+                                     size_t workspace_bytes, void *stream);
 
 /* Scratch the grad-weight kernel needs for its per-block partial sums (they
  * are combined by a second, deterministic pass -- no floating-point atomics).
@@ -168,6 +181,16 @@ int mellin_mcorrlcorr_grad_weight_f64(const double *x, const double *grad_y,
 /* Number of kernels this library has launched from the calling process since
  * it was loaded (all threads, all devices). */
 int64_t mellin_launch_count(void);
+
+/* Enable (1, default) or disable (0) the tcgen05 tensor-core kernels process-wide;
+ * returns the previous setting.  Disabled, every operator runs on CUDA cores. */
+int mellin_set_tensor_cores(int enable);
+
+/* The tensor-core kernels bound every wait on a barrier; if one ever gives up it
+ * records a non-zero code on the device instead of hanging.  This call
+ * synchronises the current device, stores the code (0 = healthy) in *code and
+ * clears it. */
+int mellin_device_status(int *code);
 
 /* Drop every cached index table of the current device (frees device memory). */
 int mellin_clear_tables(void);

@@ -115,6 +115,16 @@ def test_col_1d_entry_points():
     assert helpers.rel_err(host(back), arrays["spec2col.back"]) <= 1e-6
 
 
+@pytest.fixture(params=["tensor_cores", "cuda_cores"])
+def engine(request):
+    """Run a test once on the tcgen05 kernels and once on the CUDA-core kernels;
+    afterwards the tensor-core kernels' timeout flag must still be clear."""
+    previous = capi.set_tensor_cores(request.param == "tensor_cores")
+    yield request.param
+    capi.set_tensor_cores(previous)
+    assert capi.device_status() == 0
+
+
 def layer_all(x, w, b, go, s, d, p, u):
     """forward, grad_input, grad_weight (+bias) through the layer-level entry points."""
     xt, wt, got = dev(x), dev(w), dev(go)
@@ -136,7 +146,7 @@ def _ext_names():
 
 @pytest.mark.parametrize("name", _ext_names())
 @pytest.mark.parametrize("tag,dtype,tol", [("f32", np.float32, F32_TOL), ("f64", np.float64, F64_TOL)])
-def test_layer_against_reference_extension(name, tag, dtype, tol):
+def test_layer_against_reference_extension(engine, name, tag, dtype, tol):
     """Outputs and all gradients vs what the reference's CPU torch extension
     produced for the same inputs (recorded in tests/golden/)."""
     arrays, meta = helpers.ext_cases()
@@ -177,7 +187,7 @@ RANDOM_CASES = [
 
 
 @pytest.mark.parametrize("case", RANDOM_CASES, ids=lambda c: "n%d_ci%d_co%d_g%s_f%s_s%s_d%s_p%s_u%s" % c[:9])
-def test_layer_random_against_oracle(oracle, case):
+def test_layer_random_against_oracle(engine, oracle, case):
     n, ci, co, ng, nf, s, d, p, u, r = case
     rng = np.random.default_rng(abs(hash(case[:9])) % (2 ** 31))
     x = rng.standard_normal((n, ci) + ng).astype(np.float32)
