@@ -9,6 +9,7 @@
 #include "mellin_internal.h"
 
 namespace mellin {
+int tc_read_prof(long long *out);
 const std::string &last_error();
 int64_t launch_count();
 }  // namespace mellin
@@ -133,9 +134,13 @@ int make_gradw_problem(const char *who, const Geometry2D &q, GradWProblem<T> *p,
   p->nkx = (int)q.nfx, p->nky = (int)q.nfy, p->nix = (int)q.ngx, p->niy = (int)q.ngy;
   p->nox = (int)q.nhx, p->noy = (int)q.nhy;
   p->Ay = (int)q.sy, p->By = (int)q.dy, p->Cy = -(int)q.py, p->Dy = (int)q.uy;
-  if (need_table)
+  if (need_table) {
     rc = get_device_table(IndexMapKey{Relation::Corr, SortBy::F, q.nfx, q.ngx, q.nhx, q.sx, q.dx, q.px, q.ux},
                           &p->table);
+    if (rc) return rc;
+    rc = get_device_table(IndexMapKey{Relation::Corr, SortBy::H, q.nfx, q.ngx, q.nhx, q.sx, q.dx, q.px, q.ux},
+                          &p->table_h);
+  }
   return rc;
 }
 
@@ -275,6 +280,7 @@ int64_t mellin_lcorr_support_size(int64_t ng, int64_t s, int64_t p, int64_t u) {
 DEFINE_OPS(float, f32)
 DEFINE_OPS(double, f64)
 
+int mellin_debug_tc_prof(long long *out) { return mellin::tc_read_prof(out); }
 int mellin_set_tensor_cores(int enable) { return set_tensor_cores(enable); }
 int mellin_device_status(int *code) {
   if (code == nullptr) return fail(MELLIN_ERR_BAD_ARGUMENT, "device_status: null pointer");

@@ -1,0 +1,267 @@
+// Weight (+ bias) gradient for layers with few input channels (the first layer
+// of a stack: 3 feature maps in, 64..128 out), where the operation is bound by
+// reading the output gradient once from HBM.
+//
+//   gw[a, b, kx, ky] = sum_{n, ox, oy} go[n, a, ox, oy] * x[n, b, ix(ox, kx), oy + By*ky + Cy]
+//   gb[a]            = sum_{n, ox, oy} go[n, a, ox, oy]
+//
+// Work decomposition.  A tile is (n, ox, 128 positions oy).  Its 64 x 128 slab of
+// `go` is fetched ONCE (16-byte cp.async, three stages in flight) and used for
+// every Mellin tap kx that row ox takes part in; the few input rows those taps
+// read ride along in the same stage.  A thread owns one output channel and a
+// quarter of the positions and keeps the full [kx][b][ky] set of running sums
+// in registers -- which is what limits this kernel to nkx <= 8 and
+// b * nky <= 12.  A block walks many tiles, so its partial sums leave registers
+// once, at the end; a second pass adds the per-block partials in a fixed order
+// (no floating-point atomics: results are bit-reproducible).
+#include <algorithm>
+#include <string>
+
+#include "../../include/mellin_b200.h"
+#include "mellin_internal.h"
+
+namespace mellin {
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kTA = 64;             // output channels per block
+constexpr int kTK = 128;            // positions per tile
+constexpr int kGoPitch = kTK + 4;   // floats; 4 extra keep 16-byte rows and spread banks
+constexpr int kXPitch = kTK + 8;    // floats per staged input row (window + taps)
+constexpr int kMaxKx = 8;
+constexpr int kStages = 3;
+
+struct RowsTiling {
+  int y_tiles = 0, a_tiles = 0;
+  long long tiles = 0;
+  int Z = 0;  // blocks along the tile axis
+  int ws0 = 0;  // first input position of tile 0 relative to its first output position
+  size_t smem = 0;
+};
+
+__device__ __forceinline__ void cp_async16(void *dst, const void *src, bool valid) {
+  const unsigned d = static_cast<unsigned>(__cvta_generic_to_shared(dst));
+  const int bytes = valid ? 16 : 0;  // 0 source bytes: the destination is zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async4(void *dst, const void *src, bool valid) {
+  const unsigned d = static_cast<unsigned>(__cvta_generic_to_shared(dst));
+  const int bytes = valid ? 4 : 0;
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+template <int B, int NKY>
+__global__ void __launch_bounds__(kThreads, 1)
+gradw_rows_kernel(const GradWProblem<float> p, const RowsTiling t, float *__restrict__ part_w,
+                  float *__restrict__ part_b) {
+  constexpr int BN = B * NKY;
+  constexpr int kStageFloats = kTA * kGoPitch + kMaxKx * B * kXPitch;
+  extern __shared__ __align__(16) float smem[];
+
+  const int tid = threadIdx.x;
+  const int co_l = tid & (kTA - 1), q = tid >> 6;  // channel, position slice
+  const int a0 = blockIdx.y * kTA;
+  const int z = blockIdx.x;
+
+  float acc[kMaxKx][BN];
+  float bsum = 0.f;
+#pragma unroll
+  for (int k = 0; k < kMaxKx; ++k)
+#pragma unroll
+    for (int i = 0; i < BN; ++i) acc[k][i] = 0.f;
+
+  // ---- stage loader: every thread issues its share of one tile's copies -------
+  auto load_tile = [&](long long tile, int stage) {
+    if (tile < t.tiles) {
+      const int yt = (int)(tile % t.y_tiles);
+      long long r = tile / t.y_tiles;
+      const int ox = (int)(r % p.nox);
+      const int n = (int)(r / p.nox);
+      const int y0 = yt * kTK;
+      float *gos = smem + stage * kStageFloats;
+      float *xs = gos + kTA * kGoPitch;
+      // output-gradient slab: 64 rows x 32 chunks of 16 bytes
+#pragma unroll
+      for (int k = 0; k < kTA * (kTK / 4) / kThreads; ++k) {
+        const int idx = tid + k * kThreads;
+        const int row = idx >> 5, ch = idx & 31;
+        const int a = a0 + row, y = y0 + 4 * ch;
+        const bool valid = a < p.A && y < p.noy;
+        const float *src = valid ? p.go + (((long long)n * p.A + a) * p.nox + ox) * p.noy + y : p.go;
+        cp_async16(gos + row * kGoPitch + 4 * ch, src, valid);
+      }
+      // input rows of the taps of this ox: slot = kx, one row per input channel
+      const int e0 = p.table_h.row_ptr[ox];
+      const int np = p.table_h.row_ptr[ox + 1] - e0;
+      const int ws = y0 + t.ws0;
+      for (int idx = tid; idx < np * B * kXPitch; idx += kThreads) {
+        const int c = idx % kXPitch;
+        const int rb = idx / kXPitch;
+        const int b = rb % B, pp = rb / B;
+        const int2 e = p.table_h.entries[e0 + pp];
+        const int iy = ws + c;
+        const bool valid = iy >= 0 && iy < p.niy;
+        const float *src = valid ? p.in + (((long long)n * p.B + b) * p.nix + e.y) * p.niy + iy : p.in;
+        cp_async4(xs + (e.x * B + b) * kXPitch + c, src, valid);
+      }
+    }
+    cp_async_commit();
+  };
+
+  long long tile = z;
+#pragma unroll
+  for (int s = 0; s < kStages - 1; ++s) load_tile(tile + (long long)s * t.Z, s);
+
+  for (int it = 0; tile < t.tiles; tile += t.Z, ++it) {
+    load_tile(tile + (long long)(kStages - 1) * t.Z, (it + kStages - 1) % kStages);
+    cp_async_wait<kStages - 1>();
+    __syncthreads();
+
+    const int ox = (int)((tile / t.y_tiles) % p.nox);
+    const int e0 = p.table_h.row_ptr[ox];
+    const int np = p.table_h.row_ptr[ox + 1] - e0;
+    unsigned mask = 0;
+    for (int pp = 0; pp < np; ++pp) mask |= 1u << p.table_h.entries[e0 + pp].x;
+
+    const float *gos = smem + (it % kStages) * kStageFloats + co_l * kGoPitch;
+    const float *xs = smem + (it % kStages) * kStageFloats + kTA * kGoPitch;
+#pragma unroll 1
+    for (int yo = q * (kTK / 4); yo < (q + 1) * (kTK / 4); yo += 8) {
+      const float4 ga = *reinterpret_cast<const float4 *>(gos + yo);
+      const float4 gb4 = *reinterpret_cast<const float4 *>(gos + yo + 4);
+      const float g[8] = {ga.x, ga.y, ga.z, ga.w, gb4.x, gb4.y, gb4.z, gb4.w};
+      bsum += ((g[0] + g[1]) + (g[2] + g[3])) + ((g[4] + g[5]) + (g[6] + g[7]));
+#pragma unroll
+      for (int kx = 0; kx < kMaxKx; ++kx) {
+        if (!((mask >> kx) & 1u)) continue;
+#pragma unroll
+        for (int b = 0; b < B; ++b) {
+          const float4 *xp = reinterpret_cast<const float4 *>(xs + (kx * B + b) * kXPitch + yo);
+          const float4 x0 = xp[0], x1 = xp[1];
+          float xw[12];
+          xw[0] = x0.x, xw[1] = x0.y, xw[2] = x0.z, xw[3] = x0.w, xw[4] = x1.x, xw[5] = x1.y, xw[6] = x1.z, xw[7] = x1.w;
+          if (NKY > 1) {
+            const float4 x2 = xp[2];
+            xw[8] = x2.x, xw[9] = x2.y, xw[10] = x2.z, xw[11] = x2.w;
+          }
+#pragma unroll
+          for (int k = 0; k < NKY; ++k) {
+            float s = acc[kx][b * NKY + k];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) s = fmaf(g[j], xw[j + k], s);
+            acc[kx][b * NKY + k] = s;
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+
+  // ---- combine the four position slices and write this block's partial sums ----
+  float *red = smem;  // [4][64][BN]
+  const long long gw_elems = (long long)p.A * p.B * p.nkx * p.nky;
+  float *pw = part_w + (long long)z * gw_elems;
+  for (int kx = 0; kx < p.nkx && kx < kMaxKx; ++kx) {
+    // static register indexing: select the kx-th row with an unrolled compare
+    float mine[BN];
+#pragma unroll
+    for (int i = 0; i < BN; ++i) mine[i] = 0.f;
+#pragma unroll
+    for (int k = 0; k < kMaxKx; ++k)
+      if (k == kx) {
+#pragma unroll
+        for (int i = 0; i < BN; ++i) mine[i] = acc[k][i];
+      }
+#pragma unroll
+    for (int i = 0; i < BN; ++i) red[(q * kTA + co_l) * BN + i] = mine[i];
+    __syncthreads();
+    if (q == 0) {
+      const int a = a0 + co_l;
+      if (a < p.A) {
+#pragma unroll
+        for (int i = 0; i < BN; ++i) {
+          const float s = (red[co_l * BN + i] + red[(kTA + co_l) * BN + i]) +
+                          (red[(2 * kTA + co_l) * BN + i] + red[(3 * kTA + co_l) * BN + i]);
+          const int b = i / NKY, k = i % NKY;
+          const int ky = p.By < 0 ? NKY - 1 - k : k;  // slot k holds the tap whose input offset is k
+          pw[(((long long)a * p.B + b) * p.nkx + kx) * p.nky + ky] = s;
+        }
+      }
+    }
+    __syncthreads();
+  }
+  if (part_b != nullptr) {
+    red[q * kTA + co_l] = bsum;
+    __syncthreads();
+    const int a = a0 + co_l;
+    if (q == 0 && a < p.A)
+      part_b[(long long)z * p.A + a] = (red[co_l] + red[kTA + co_l]) + (red[2 * kTA + co_l] + red[3 * kTA + co_l]);
+  }
+}
+
+bool plan_rows(const GradWProblem<float> &p, RowsTiling &t) {
+  if (p.Dy != 1 || p.Ay != 1) return false;
+  if (p.nkx < 1 || p.nkx > kMaxKx || p.B < 1 || p.B > 4 || p.nky < 1 || p.nky > 3) return false;
+  if (p.nky > 1 && p.By != 1 && p.By != -1) return false;
+  if (p.noy < 32 || p.noy % 4 != 0 || p.A < 1 || p.N < 1 || p.nox < 1) return false;
+  if (reinterpret_cast<uintptr_t>(p.go) % 16 != 0) return false;
+  t.y_tiles = (p.noy + kTK - 1) / kTK;
+  t.a_tiles = (p.A + kTA - 1) / kTA;
+  t.tiles = (long long)p.N * p.nox * t.y_tiles;
+  t.ws0 = p.Cy + std::min(0, p.By * (p.nky - 1));
+  t.Z = (int)std::min<long long>(t.tiles, std::max(1, sm_count() / t.a_tiles));
+  t.smem = (size_t)kStages * (kTA * kGoPitch + kMaxKx * p.B * kXPitch) * sizeof(float);
+  return t.smem <= 200 * 1024;
+}
+
+template <int B>
+int dispatch_rows_nky(const GradWProblem<float> &p, const RowsTiling &t, float *pw, float *pb, cudaStream_t stream) {
+  void (*kernel)(GradWProblem<float>, RowsTiling, float *, float *) = nullptr;
+  switch (p.nky) {
+    case 1: kernel = gradw_rows_kernel<B, 1>; break;
+    case 2: kernel = gradw_rows_kernel<B, 2>; break;
+    default: kernel = gradw_rows_kernel<B, 3>; break;
+  }
+  cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)t.smem);
+  if (err != cudaSuccess) return fail(MELLIN_ERR_LAUNCH, std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(err));
+  kernel<<<dim3(t.Z, t.a_tiles), kThreads, t.smem, stream>>>(p, t, pw, pb);
+  err = cudaGetLastError();
+  if (err != cudaSuccess) return fail(MELLIN_ERR_LAUNCH, std::string("gradw_rows_kernel: ") + cudaGetErrorString(err));
+  count_launch();
+  return MELLIN_OK;
+}
+
+}  // namespace
+
+size_t gradw_rows_workspace_floats(const GradWProblem<float> &p, size_t *bias_offset) {
+  RowsTiling t;
+  if (!plan_rows(p, t)) return 0;
+  size_t w_part = (size_t)t.Z * p.A * p.B * p.nkx * p.nky;
+  w_part = (w_part + 63) / 64 * 64;
+  if (bias_offset) *bias_offset = w_part;
+  return w_part + (size_t)t.Z * p.A;
+}
+
+// Launches the kernel that fills the per-block partial sums; *slices receives
+// their number.  MELLIN_ERR_UNSUPPORTED when the problem is outside its coverage.
+int launch_gradw_rows(const GradWProblem<float> &p, float *part_w, float *part_b, int *slices, cudaStream_t stream) {
+  RowsTiling t;
+  if (!plan_rows(p, t)) return MELLIN_ERR_UNSUPPORTED;
+  *slices = t.Z;
+  switch (p.B) {
+    case 1: return dispatch_rows_nky<1>(p, t, part_w, part_b, stream);
+    case 2: return dispatch_rows_nky<2>(p, t, part_w, part_b, stream);
+    case 3: return dispatch_rows_nky<3>(p, t, part_w, part_b, stream);
+    default: return dispatch_rows_nky<4>(p, t, part_w, part_b, stream);
+  }
+}
+
+}  // namespace mellin

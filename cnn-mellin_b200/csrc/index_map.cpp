@@ -77,7 +77,9 @@ IndexMap build_index_map(const IndexMapKey &key) {
   // triples arrive in (h, f) order, so rows come out sorted by h (orders G, F)
   // or by f (order H); for order F the first time a row h is seen is at its
   // smallest f only if we walk by f first -- do that explicitly.
-  if (key.sort == SortBy::F) {
+  if (key.sort == SortBy::F || key.sort == SortBy::G) {
+    // order G: within a gx row the taps then come in increasing fx, which the
+    // tensor-core kernel relies on (weight chunks at increasing addresses)
     std::stable_sort(triples.begin(), triples.end(),
                      [](const Triple &a, const Triple &b) { return a.f < b.f; });
   }

@@ -46,7 +46,7 @@ struct Entry {
 struct IndexMap {
   // CSR over `rows` rows.  Meaning of (a, b) per sort order:
   //   SortBy::H : row = hx, a = fx, b = gx
-  //   SortBy::G : row = gx, a = fx, b = hx
+  //   SortBy::G : row = gx, a = fx, b = hx   (entries of a row in increasing fx)
   //   SortBy::F : row = fx, a = hx | flags, b = gx
   std::vector<int32_t> row_ptr;  // rows + 1
   std::vector<Entry> entries;

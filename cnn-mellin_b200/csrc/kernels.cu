@@ -781,10 +781,11 @@ int launch_direct<double>(const DirectProblem<double> &p, cudaStream_t stream) {
 
 template <>
 size_t gradw_workspace_bytes<float>(const GradWProblem<float> &p) {
+  const size_t rows = gradw_rows_workspace_floats(p, nullptr) * sizeof(float);
   GradWTiling t;
   int RM = 0, RN = 0;
-  if (!plan_gradw(p, t, RM, RN)) return 0;
-  return gradw_partial_floats(p, t, nullptr) * sizeof(float);
+  if (!plan_gradw(p, t, RM, RN)) return rows;
+  return std::max(rows, gradw_partial_floats(p, t, nullptr) * sizeof(float));
 }
 
 template <>
@@ -795,6 +796,33 @@ size_t gradw_workspace_bytes<double>(const GradWProblem<double> &) {
 template <>
 int launch_gradw<float>(const GradWProblem<float> &p, void *workspace, size_t workspace_bytes,
                         cudaStream_t stream) {
+  const long long gw_count = (long long)p.A * p.B * p.nkx * p.nky;
+  {
+    // layers with few input channels: the kernel that reads grad_y once
+    size_t rows_bias_off = 0;
+    const size_t rows_need = gradw_rows_workspace_floats(p, &rows_bias_off) * sizeof(float);
+    if (rows_need > 0 && p.table_h.row_ptr != nullptr) {
+      if (workspace == nullptr || workspace_bytes < rows_need)
+        return fail(MELLIN_ERR_WORKSPACE, "grad_weight workspace too small: need " + std::to_string(rows_need) +
+                                              " bytes, got " + std::to_string(workspace_bytes));
+      float *pw = static_cast<float *>(workspace);
+      float *pb = p.gb != nullptr ? pw + rows_bias_off : nullptr;
+      int slices = 0;
+      int rc = launch_gradw_rows(p, pw, pb, &slices, stream);
+      if (rc != MELLIN_ERR_UNSUPPORTED) {
+        if (rc) return rc;
+        reduce_partials_kernel<float><<<(unsigned)((gw_count + 31) / 32), 256, 0, stream>>>(pw, p.gw, gw_count, slices,
+                                                                                           gw_count);
+        rc = check_launch("reduce_partials_kernel");
+        if (rc) return rc;
+        if (p.gb != nullptr) {
+          reduce_partials_kernel<float><<<(unsigned)ceil_div(p.A, 32), 256, 0, stream>>>(pb, p.gb, p.A, slices, p.A);
+          rc = check_launch("reduce_partials_kernel(bias)");
+        }
+        return rc;
+      }
+    }
+  }
   GradWTiling t;
   int RM = 0, RN = 0;
   if (!plan_gradw(p, t, RM, RN)) return launch_gradw_generic<float>(p, stream);

@@ -70,6 +70,7 @@ struct GradWProblem {
   T *gw = nullptr;         // (A, B, nkx, nky)
   T *gb = nullptr;         // (A) or null
   DeviceTable table;       // rows = kx, entries (ox | flags, ix)
+  DeviceTable table_h;     // the same triples by output row: rows = ox, entries (kx, ix)
   int N = 0, A = 0, B = 0;
   int nkx = 0, nky = 0, nix = 0, niy = 0, nox = 0, noy = 0;
   int Ay = 1, By = 1, Cy = 0, Dy = 1;
@@ -98,6 +99,10 @@ int set_tensor_cores(int enable);
 template <typename T> size_t gradw_workspace_bytes(const GradWProblem<T> &p);
 template <typename T>
 int launch_gradw(const GradWProblem<T> &p, void *workspace, size_t workspace_bytes, cudaStream_t stream);
+// few-input-channel weight gradient (gradw_rows.cu): partial-sum scratch in floats
+// (0 = not covered) and the launch that fills it
+size_t gradw_rows_workspace_floats(const GradWProblem<float> &p, size_t *bias_offset);
+int launch_gradw_rows(const GradWProblem<float> &p, float *part_w, float *part_b, int *slices, cudaStream_t stream);
 template <typename T> int launch_spec2col(const ColProblem<T> &p, cudaStream_t stream);
 template <typename T> int launch_col2spec(const ColProblem<T> &p, cudaStream_t stream);
 

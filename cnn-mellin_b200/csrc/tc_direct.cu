@@ -31,12 +31,20 @@
 // accumulated in TMEM from zero, then added by the epilogue warps into FP32
 // registers with round-to-nearest (two-level accumulation).
 //
-// Warp roles (13 warps): 0-3 epilogue (TMEM -> registers -> global, one warp per
-// 32 TMEM lanes), 4-11 producers (gather + split activations, copy packed
-// weights), 12 MMA issuer.  A ring of shared-memory stages and two TMEM
-// accumulators are handed around with mbarriers; every wait is bounded and a
-// timeout raises a device-side error flag instead of hanging.
+// Warp roles (14 warps): 0-3 epilogue (TMEM -> registers -> global, one warp per
+// 32 TMEM lanes); 4-11 converters (raw rows in shared memory -> hi/lo operand
+// layout); 12 MMA issuer; 13 copy issuer: every gathered input row of a K-block
+// (4 rows = 4 consecutive channels of one table entry) is one 4-D TMA box load
+// -- positions outside the signal and channels beyond the last are zero-filled
+// by the copy engine -- and the packed weight chunks are bulk copies straight
+// into operand layout.  The index table, the bias and all per-block constants
+// live in shared memory.  A ring of shared-memory stages and two TMEM accumulators are handed
+// around with mbarriers; every wait is bounded and a timeout raises a
+// device-side error flag instead of hanging.
+#include <cuda.h>
+
 #include <algorithm>
+#include <cstdlib>
 #include <string>
 
 #include "../../include/mellin_b200.h"
@@ -48,37 +56,52 @@ namespace mellin {
 namespace {
 
 constexpr int kEpilogueWarps = 4;
-constexpr int kProducerWarps = 8;
-constexpr int kProducerThreads = kProducerWarps * 32;
-constexpr int kThreads = (kEpilogueWarps + kProducerWarps + 1) * 32;
+constexpr int kConvertWarps = 8;
+constexpr int kConvertThreads = kConvertWarps * 32;
+constexpr int kMmaWarp = kEpilogueWarps + kConvertWarps;
+constexpr int kCopyWarp = kMmaWarp + 1;
+constexpr int kThreads = (kCopyWarp + 1) * 32;
 constexpr int kTileM = 128;
 constexpr uint32_t kSpinLimit = 1u << 20;
 constexpr int kMaxStages = 4;
+constexpr int kMaxKB = 64;          // rows per stage (16 chunks: one lane of the copy warp each)
+constexpr int kMaxTableRows = 512;  // output rows (ox) whose table is cached in shared memory
+constexpr int kMaxTableEntries = 1024;
+constexpr int kMaxBias = 1024;      // output channels whose bias is cached in shared memory
 
-__device__ int g_tc_error = 0;  // first timeout code seen by any block since the last query
+__device__ int g_tc_error = 0;       // first timeout code seen by any block since the last query
+__device__ long long g_tc_prof[16];  // per-role wait / work cycles of block 0 (written when profiling is on)
 
 struct TcParams {
-  const float *in;
   const float *bias;
   float *out;
-  const float *w_hi;  // packed [kx][tap][b / 4][NP][b % 4]
+  const float *w_hi;  // packed [kx][tap][b / 4][NP * a_tiles][b % 4]
   const float *w_lo;
   const int32_t *row_ptr;
   const int2 *entries;
+  int num_entries;
   int N, A, B;
   int Bp;        // B rounded up to a multiple of 4: rows per table entry
-  int nky, niy, nox, noy, nix;
-  long long in_sn, in_sb, out_sn, out_sa;
-  int By, Cy;
-  int NP;        // padded output channels (multiple of 16)
-  int a_tiles;   // tiles over output channels when A > 256
+  int nky, nox, noy;
+  long long out_sn, out_sa;
+  int absBy;     // |By|: positions between consecutive taps
+  int ws0;       // first input position of tile 0: Cy + min(0, By * (nky - 1))
+  int NP;        // padded output channels per tile (multiple of 16, <= 128)
+  int a_tiles;   // tiles over output channels
   int RW;        // staged positions per row (multiple of 8)
+  int RWt;       // positions copied per raw row: RW + 4 (room for the 16-byte alignment lead)
+  int raw_chunk_floats;  // pitch of a raw 4-row chunk in shared memory (128-byte aligned); its rows are RWt apart
   int KB;        // rows per stage (multiple of 8)
   int stages;
   int y_tiles;
-  long long tiles;
+  int tiles;
   int tmem_cols;
   uint32_t a_stage_bytes, w_stage_bytes;  // per hi or lo part
+  uint32_t raw_stage_bytes;
+  uint32_t w_pack_bytes;  // bytes of one packed weight array (hi or lo)
+  uint32_t w_res_bytes;  // > 0: the whole packed weight set (hi, then lo) stays in shared memory for the
+                         // life of the block and stages hold activations only
+  int profile;
 };
 
 __device__ __forceinline__ float tf32_hi(float x) { return __uint_as_float(__float_as_uint(x) & 0xffffe000u); }
@@ -113,46 +136,116 @@ __global__ void pack_weights_kernel(const float *__restrict__ w, long long w_sa,
 
 // ---- shared-memory carve-up -----------------------------------------------------------
 struct TcControl {
-  uint64_t full[kMaxStages];
-  uint64_t empty[kMaxStages];
+  uint64_t raw_full[kMaxStages];  // copies of a stage have landed
+  uint64_t full[kMaxStages];      // operands of a stage are converted
+  uint64_t empty[kMaxStages];     // the MMAs reading a stage have completed
   uint64_t dfull[2];
   uint64_t dempty[2];
   uint32_t tmem_base;
   int abort;
 };
-constexpr int kMaxKB = 64;
-struct TcRowTable {
-  long long in_off[kMaxKB];  // element offset of the gathered input row, -1 for padding rows
-  int w_off[kMaxKB / 4];     // float4 offset of the packed weight chunk (tap 0, channel 0) of every 4 rows, -1 = padding
-};
-constexpr uint32_t kControlBytes = 1024 + kMaxStages * 1024;  // control block, then one row table per stage
+// control block | row_ptr | entries | bias | stages
+constexpr uint32_t kRowPtrOffset = 256;
+constexpr uint32_t kEntriesOffset = kRowPtrOffset + (kMaxTableRows + 1) * 4 + 12;  // 16-byte aligned
+constexpr uint32_t kBiasOffset = kEntriesOffset + kMaxTableEntries * 8;
+constexpr int kMaxKSteps = 1024;      // k-steps (8 rows) over all table rows, resident-weight mode
+constexpr uint32_t kKOfsOffset = kBiasOffset + kMaxBias * 4;             // int[kMaxTableRows + 1]
+constexpr uint32_t kKStepOffset = kKOfsOffset + (kMaxTableRows + 1) * 4 + 4;  // uint2[kMaxKSteps], 8-byte aligned
+constexpr uint32_t kStageOffset = (kKStepOffset + kMaxKSteps * 8 + 1023) / 1024 * 1024;
 
 __device__ __forceinline__ void raise_timeout(TcControl *ctl, int code) {
   atomicCAS(&g_tc_error, 0, code);
   ctl->abort = 1;
 }
 
-__device__ __forceinline__ void producer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kProducerThreads) : "memory"); }
+// Tile coordinates of a block: tile = blockIdx.x + i * gridDim.x, decoded once
+// and then advanced by the (decoded) grid stride with carries -- no divisions
+// in the steady state.
+struct TileWalker {
+  int n, ox, yt, at;     // current tile
+  int sn, sox, syt, sat; // grid stride, decoded
+  int tile;
+  __device__ __forceinline__ void init(const TcParams &p) {
+    tile = blockIdx.x;
+    int t = tile;
+    at = t % p.a_tiles, t /= p.a_tiles;
+    yt = t % p.y_tiles, t /= p.y_tiles;
+    ox = t % p.nox, n = t / p.nox;
+    t = gridDim.x;
+    sat = t % p.a_tiles, t /= p.a_tiles;
+    syt = t % p.y_tiles, t /= p.y_tiles;
+    sox = t % p.nox, sn = t / p.nox;
+  }
+  __device__ __forceinline__ void next(const TcParams &p) {
+    tile += gridDim.x;
+    at += sat;
+    int carry = at >= p.a_tiles;
+    at -= carry ? p.a_tiles : 0;
+    yt += syt + carry;
+    carry = yt >= p.y_tiles;
+    yt -= carry ? p.y_tiles : 0;
+    ox += sox + carry;
+    carry = ox >= p.nox;
+    ox -= carry ? p.nox : 0;
+    n += sn + carry;
+  }
+};
 
-// NPC: padded output channels / 16 (the epilogue keeps 16 * NPC running sums per thread)
+#define PROF_BEGIN() long long prof_t0 = clock64(), prof_wait = 0, prof_t1 = 0
+#define PROF_WAIT_START() prof_t1 = clock64()
+#define PROF_WAIT_END() prof_wait += clock64() - prof_t1
+#define PROF_END(slot)                                           \
+  if (blockIdx.x == 0 && lane == 0 && p.profile) {               \
+    g_tc_prof[2 * (slot)] = prof_wait;                           \
+    g_tc_prof[2 * (slot) + 1] = clock64() - prof_t0 - prof_wait; \
+  }
+
+// NPC: padded output channels per tile / 16 (the epilogue keeps 16 * NPC running sums per thread)
 template <int NPC>
-__global__ void __launch_bounds__(kThreads, 1) tc_direct_kernel(const TcParams p) {
+__global__ void __launch_bounds__(kThreads, 1)
+tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map) {
   extern __shared__ __align__(1024) unsigned char smem[];
   TcControl *ctl = reinterpret_cast<TcControl *>(smem);
-  TcRowTable *tables = reinterpret_cast<TcRowTable *>(smem + 1024);
-  unsigned char *stage_base = smem + kControlBytes;
-  const uint32_t stage_bytes = 2 * (p.a_stage_bytes + p.w_stage_bytes);
+  int *rowptr_s = reinterpret_cast<int *>(smem + kRowPtrOffset);
+  int2 *ent_s = reinterpret_cast<int2 *>(smem + kEntriesOffset);
+  float *bias_s = reinterpret_cast<float *>(smem + kBiasOffset);
+  int *kofs_s = reinterpret_cast<int *>(smem + kKOfsOffset);        // first k-step of every table row
+  uint2 *kstep_s = reinterpret_cast<uint2 *>(smem + kKStepOffset);  // (first weight chunk, distance to the second), 16-byte units
+  unsigned char *w_res = smem + kStageOffset;  // resident weights: hi part, lo part
+  unsigned char *stage_base = w_res + 2 * p.w_res_bytes;
+  const uint32_t stage_bytes = 2 * (p.a_stage_bytes + p.w_stage_bytes) + p.raw_stage_bytes;
   volatile int *abort_flag = &ctl->abort;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int absBy = p.By < 0 ? -p.By : p.By;
   const int JB = p.KB >> 3;
   const int NPtot = p.NP * p.a_tiles;
   const int B4 = p.Bp >> 2;
 
+  // ---- one-time set-up ------------------------------------------------------------
+  for (int i = tid; i <= p.nox; i += kThreads) rowptr_s[i] = p.row_ptr[i];
+  for (int i = tid; i < p.num_entries; i += kThreads) ent_s[i] = p.entries[i];
+  for (int i = tid; i < NPtot; i += kThreads) bias_s[i] = (p.bias != nullptr && i < p.A) ? p.bias[i] : 0.f;
+  {
+    // weight chunks of padding rows are never copied: clear the stages once so
+    // that they hold finite values (they meet zero activations)
+    float4 *z = reinterpret_cast<float4 *>(stage_base);
+    const int n16 = (int)((size_t)p.stages * stage_bytes / 16);
+    for (int i = tid; i < n16; i += kThreads) z[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  if (p.w_res_bytes) {
+    const int n16 = (int)(p.w_res_bytes / 16), have = (int)(p.w_pack_bytes / 16);
+    const float4 *gh = reinterpret_cast<const float4 *>(p.w_hi), *gl = reinterpret_cast<const float4 *>(p.w_lo);
+    float4 *sh = reinterpret_cast<float4 *>(w_res), *sl = reinterpret_cast<float4 *>(w_res + p.w_res_bytes);
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int i = tid; i < n16; i += kThreads) {
+      sh[i] = i < have ? __ldg(gh + i) : zero;
+      sl[i] = i < have ? __ldg(gl + i) : zero;
+    }
+  }
   if (tid == 0) {
     for (int s = 0; s < p.stages; ++s) {
-      tc::mbar_init(&ctl->full[s], kProducerThreads);
+      tc::mbar_init(&ctl->raw_full[s], 1);
+      tc::mbar_init(&ctl->full[s], kConvertThreads);
       tc::mbar_init(&ctl->empty[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -162,225 +255,293 @@ __global__ void __launch_bounds__(kThreads, 1) tc_direct_kernel(const TcParams p
     ctl->abort = 0;
     tc::fence_mbar_init();
   }
-  if (warp == kEpilogueWarps + kProducerWarps) {
+  if (warp == kMmaWarp) {
     tc::tmem_alloc(&ctl->tmem_base, (uint32_t)p.tmem_cols);
     tc::tmem_relinquish();
   }
+  tc::fence_proxy_async();
   tc::tc_fence_before_sync();
   __syncthreads();
   tc::tc_fence_after_sync();
   const uint32_t tmem_base = ctl->tmem_base;
+  if (p.w_res_bytes) {
+    // weight chunk pair of every k-step of every table row (output-channel tile 0)
+    if (tid == 0) {
+      int o = 0;
+      for (int ox = 0; ox <= p.nox; ++ox) {
+        kofs_s[ox] = o;
+        if (ox < p.nox) o += ((rowptr_s[ox + 1] - rowptr_s[ox]) * B4 + 1) >> 1;
+      }
+    }
+    __syncthreads();
+    for (int ox = warp; ox < p.nox; ox += kThreads / 32) {
+      const int e0 = rowptr_s[ox];
+      const int chunks = (rowptr_s[ox + 1] - e0) * B4;
+      for (int j = lane; 2 * j < chunks; j += 32) {
+        const int q0 = 2 * j, pp0 = q0 / B4, pp1 = (q0 + 1) / B4;
+        const uint32_t c0 = (uint32_t)((ent_s[e0 + pp0].x * p.nky * B4 + (q0 - pp0 * B4)) * NPtot);
+        uint32_t c1 = c0 + (uint32_t)p.NP;
+        if (q0 + 1 < chunks) c1 = (uint32_t)((ent_s[e0 + pp1].x * p.nky * B4 + (q0 + 1 - pp1 * B4)) * NPtot);
+        kstep_s[kofs_s[ox] + j] = make_uint2(c0, c1 - c0);
+      }
+    }
+    __syncthreads();
+  }
 
   if (warp < kEpilogueWarps) {
     // =========================== epilogue ===========================
-    long long g = 0;  // K-blocks (accumulation intervals) consumed so far
-    for (long long tile = blockIdx.x; tile < p.tiles; tile += gridDim.x) {
+    int g = 0;  // K-blocks (accumulation intervals) consumed so far
+    PROF_BEGIN();
+    TileWalker tc_;
+    for (tc_.init(p); tc_.tile < p.tiles; tc_.next(p)) {
       // tcgen05.ld is warp-collective: keep every exit decision warp-uniform
       if (__any_sync(0xffffffffu, *abort_flag)) break;
-      long long T = tile;
-      const int at = (int)(T % p.a_tiles);
-      T /= p.a_tiles;
-      const int yt = (int)(T % p.y_tiles);
-      T /= p.y_tiles;
-      const int ox = (int)(T % p.nox);
-      const int n = (int)(T / p.nox);
-      const int np = p.row_ptr[ox + 1] - p.row_ptr[ox];
-      const int Kr = np * p.Bp;
-      const int oy = yt * kTileM + warp * 32 + lane;
-      const int a0 = at * p.NP;
+      const int Kr = (rowptr_s[tc_.ox + 1] - rowptr_s[tc_.ox]) * p.Bp;
+      const int oy = tc_.yt * kTileM + warp * 32 + lane;
+      const int a0 = tc_.at * p.NP;
       float sum[NPC][16];
 #pragma unroll
       for (int c = 0; c < NPC; ++c)
 #pragma unroll
-        for (int i = 0; i < 16; ++i) sum[c][i] = 0.f;
+        for (int i4 = 0; i4 < 4; ++i4) {
+          const float4 b = *reinterpret_cast<const float4 *>(bias_s + a0 + 16 * c + 4 * i4);
+          sum[c][4 * i4] = b.x, sum[c][4 * i4 + 1] = b.y, sum[c][4 * i4 + 2] = b.z, sum[c][4 * i4 + 3] = b.w;
+        }
       bool failed = false;
       for (int k0 = 0; k0 < Kr; k0 += p.KB, ++g) {
-        const int acc = (int)(g & 1);
+        const int acc = g & 1;
+        PROF_WAIT_START();
         const bool ok = tc::mbar_wait(&ctl->dfull[acc], (uint32_t)((g >> 1) & 1), kSpinLimit);
+        PROF_WAIT_END();
         if (!__all_sync(0xffffffffu, ok)) {
           raise_timeout(ctl, 3);
           failed = true;
           break;
         }
         tc::tc_fence_after_sync();
+        constexpr int kGroup = NPC < 4 ? NPC : 4;  // 16-column loads in flight together
 #pragma unroll
-        for (int c = 0; c < NPC; ++c) {
-          uint32_t v[16];
-          tc::tmem_ld16(tmem_base + (uint32_t)(acc * p.NP + 16 * c) + ((uint32_t)(warp * 32) << 16), v);
+        for (int c0 = 0; c0 < NPC; c0 += kGroup) {
+          uint32_t v[kGroup][16];
+#pragma unroll
+          for (int c = 0; c < kGroup; ++c)
+            if (c0 + c < NPC)
+              tc::tmem_ld16(tmem_base + (uint32_t)(acc * p.NP + 16 * (c0 + c)) + ((uint32_t)(warp * 32) << 16), v[c]);
           tc::tmem_ld_wait();
-          if (c == NPC - 1) {
+          if (c0 + kGroup >= NPC) {
             tc::tc_fence_before_sync();
             tc::mbar_arrive(&ctl->dempty[acc]);
           }
 #pragma unroll
-          for (int i = 0; i < 16; ++i) sum[c][i] += __uint_as_float(v[i]);
+          for (int c = 0; c < kGroup; ++c)
+            if (c0 + c < NPC)
+#pragma unroll
+              for (int i = 0; i < 16; ++i) sum[c0 + c][i] += __uint_as_float(v[c][i]);
         }
       }
       if (failed) break;
       if (oy < p.noy) {
-        float *orow = p.out + n * p.out_sn + (long long)ox * p.noy + oy;
+        float *o = p.out + tc_.n * p.out_sn + a0 * p.out_sa + (long long)tc_.ox * p.noy + oy;
+        const int a_left = p.A - a0;
 #pragma unroll
         for (int c = 0; c < NPC; ++c)
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            const int a = a0 + 16 * c + i;
-            if (a < p.A) {
-              const float b = p.bias != nullptr ? __ldg(p.bias + a) : 0.f;
-              orow[a * p.out_sa] = sum[c][i] + b;
-            }
+            if (16 * c + i < a_left) __stcs(o, sum[c][i]);
+            o += p.out_sa;
           }
       }
     }
-  } else if (warp < kEpilogueWarps + kProducerWarps) {
-    // =========================== producers ===========================
-    const int ptid = tid - kEpilogueWarps * 32;
-    long long it = 0;  // stage uses so far
-    for (long long tile = blockIdx.x; tile < p.tiles && !*abort_flag; tile += gridDim.x) {
-      long long T = tile;
-      const int at = (int)(T % p.a_tiles);
-      T /= p.a_tiles;
-      const int yt = (int)(T % p.y_tiles);
-      T /= p.y_tiles;
-      const int ox = (int)(T % p.nox);
-      const int n = (int)(T / p.nox);
-      const int e0 = p.row_ptr[ox];
-      const int np = p.row_ptr[ox + 1] - e0;
-      const int Kr = np * p.Bp;
-      const int ws = yt * kTileM + p.Cy + min(0, p.By * (p.nky - 1));
-      bool failed = false;
+    if (warp == 0) { PROF_END(0); }
+  } else if (warp < kMmaWarp) {
+    // =========================== converters ===========================
+    const int pwarp = warp - kEpilogueWarps;
+    int it = 0;
+    bool failed = false;
+    PROF_BEGIN();
+    TileWalker tc_;
+    for (tc_.init(p); tc_.tile < p.tiles && !*abort_flag && !failed; tc_.next(p)) {
+      const int Kr = (rowptr_s[tc_.ox + 1] - rowptr_s[tc_.ox]) * p.Bp;
+      const int lead = (tc_.yt * kTileM + p.ws0) & 3;  // the copy started at the 16-byte boundary below
       for (int k0 = 0; k0 < Kr; k0 += p.KB, ++it) {
-        const int s = (int)(it % p.stages);
+        const int s = it % p.stages;
         const uint32_t use = (uint32_t)(it / p.stages);
-        if (!tc::mbar_wait(&ctl->empty[s], (use & 1) ^ 1, kSpinLimit)) {
+        PROF_WAIT_START();
+        const bool okw = tc::mbar_wait(&ctl->raw_full[s], use & 1, kSpinLimit);
+        PROF_WAIT_END();
+        if (!okw) {
           raise_timeout(ctl, 1);
           failed = true;
           break;
         }
-        TcRowTable *tab = tables + s;
-        const int rows_here = min(p.KB, Kr - k0);
-        const int rows_pad = (rows_here + 7) & ~7;
-        if (ptid < p.KB) {
-          long long in_off = -1;
-          int w_off = -1;
-          if (ptid < rows_here) {
-            const int r = k0 + ptid;
-            const int pp = r / p.Bp, b = r - pp * p.Bp;
-            const int2 e = p.entries[e0 + pp];
-            if (b < p.B) in_off = n * p.in_sn + b * p.in_sb + (long long)e.y * p.niy;
-            w_off = (e.x * p.nky * B4 + (b >> 2)) * NPtot + at * p.NP;
-          }
-          tab->in_off[ptid] = in_off;
-          if ((ptid & 3) == 0) tab->w_off[ptid >> 2] = w_off;
-        }
-        producer_sync();
         unsigned char *st = stage_base + (size_t)s * stage_bytes;
         float4 *a_hi = reinterpret_cast<float4 *>(st);
         float4 *a_lo = reinterpret_cast<float4 *>(st + p.a_stage_bytes);
-        float4 *w_hi = reinterpret_cast<float4 *>(st + 2 * p.a_stage_bytes);
-        float4 *w_lo = reinterpret_cast<float4 *>(st + 2 * p.a_stage_bytes + p.w_stage_bytes);
-        // activations: item = (chunk of 4 rows, position)
-        const int a_items = (rows_pad >> 2) * p.RW;
-        for (int idx = ptid; idx < a_items; idx += kProducerThreads) {
-          const int c = idx / p.RW, rho = idx - c * p.RW;
-          const int iy = ws + rho;
-          const bool in_range = iy >= 0 && iy < p.niy;
-          float x[4];
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const long long off = tab->in_off[4 * c + i];
-            x[i] = (in_range && off >= 0) ? __ldg(p.in + off + iy) : 0.f;
+        const float *raw = reinterpret_cast<const float *>(st + 2 * (p.a_stage_bytes + p.w_stage_bytes));
+        const int rows_here = min(p.KB, Kr - k0);
+        const int chunks_loaded = (rows_here + 3) >> 2;
+        const int chunks_total = ((rows_here + 7) >> 3) << 1;
+        for (int c = pwarp; c < chunks_total; c += kConvertWarps) {
+          float4 *dh = a_hi + c * p.RW, *dl = a_lo + c * p.RW;
+          if (c < chunks_loaded) {
+            const float *r0 = raw + (size_t)c * p.raw_chunk_floats + lead;
+            for (int rho = lane; rho < p.RW; rho += 32) {
+              const float x0 = r0[rho], x1 = r0[p.RWt + rho], x2 = r0[2 * p.RWt + rho], x3 = r0[3 * p.RWt + rho];
+              float4 h, l;
+              h.x = tf32_hi(x0), h.y = tf32_hi(x1), h.z = tf32_hi(x2), h.w = tf32_hi(x3);
+              l.x = x0 - h.x, l.y = x1 - h.y, l.z = x2 - h.z, l.w = x3 - h.w;
+              dh[rho] = h;
+              dl[rho] = l;
+            }
+          } else {
+            for (int rho = lane; rho < p.RW; rho += 32) {
+              dh[rho] = make_float4(0.f, 0.f, 0.f, 0.f);
+              dl[rho] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
           }
-          float4 h, l;
-          h.x = tf32_hi(x[0]), h.y = tf32_hi(x[1]), h.z = tf32_hi(x[2]), h.w = tf32_hi(x[3]);
-          l.x = x[0] - h.x, l.y = x[1] - h.y, l.z = x[2] - h.z, l.w = x[3] - h.w;
-          a_hi[c * p.RW + rho] = h;
-          a_lo[c * p.RW + rho] = l;
-        }
-        // weights: item = (tap, chunk of 4 rows, output channel); consecutive
-        // threads copy consecutive 16-byte chunks
-        const int chunks_here = rows_pad >> 2;
-        const int w_items = p.nky * chunks_here * p.NP;
-        const float4 *src_hi = reinterpret_cast<const float4 *>(p.w_hi);
-        const float4 *src_lo = reinterpret_cast<const float4 *>(p.w_lo);
-        for (int idx = ptid; idx < w_items; idx += kProducerThreads) {
-          const int nn = idx % p.NP;
-          int rest = idx / p.NP;
-          const int c = rest % chunks_here, t = rest / chunks_here;
-          const int woff = tab->w_off[c];
-          float4 h = make_float4(0.f, 0.f, 0.f, 0.f), l = h;
-          if (woff >= 0) {
-            const long long src = (long long)woff + (long long)t * B4 * NPtot + nn;
-            h = __ldg(src_hi + src);
-            l = __ldg(src_lo + src);
-          }
-          const int dst = (t * JB + (c >> 1)) * (2 * p.NP) + (c & 1) * p.NP + nn;
-          w_hi[dst] = h;
-          w_lo[dst] = l;
         }
         tc::fence_proxy_async();
         tc::mbar_arrive(&ctl->full[s]);
       }
-      if (failed) break;
     }
-  } else {
+    if (pwarp == 0) { PROF_END(1); }
+  } else if (warp == kCopyWarp) {
+    // =========================== copy issuer ===========================
+    int it = 0;
+    bool failed = false;
+    const float4 *src_hi = reinterpret_cast<const float4 *>(p.w_hi);
+    const float4 *src_lo = reinterpret_cast<const float4 *>(p.w_lo);
+    const uint32_t w_chunk_bytes = (uint32_t)p.NP * 16u;
+    const uint32_t bytes_per_chunk =
+        (uint32_t)p.RWt * 16u + (p.w_res_bytes ? 0u : 2u * (uint32_t)p.nky * w_chunk_bytes);
+    PROF_BEGIN();
+    TileWalker tc_;
+    for (tc_.init(p); tc_.tile < p.tiles && !failed; tc_.next(p)) {
+      if (__any_sync(0xffffffffu, *abort_flag)) break;
+      const int e0 = rowptr_s[tc_.ox];
+      const int Kr = (rowptr_s[tc_.ox + 1] - e0) * p.Bp;
+      const int ws = tc_.yt * kTileM + p.ws0;
+      const int x0 = ws - (ws & 3);
+      for (int k0 = 0; k0 < Kr; k0 += p.KB, ++it) {
+        const int s = it % p.stages;
+        const uint32_t use = (uint32_t)(it / p.stages);
+        PROF_WAIT_START();
+        const bool ok = tc::mbar_wait(&ctl->empty[s], (use & 1) ^ 1, kSpinLimit);
+        PROF_WAIT_END();
+        if (!__all_sync(0xffffffffu, ok)) {
+          raise_timeout(ctl, 5);
+          failed = true;
+          break;
+        }
+        unsigned char *st = stage_base + (size_t)s * stage_bytes;
+        float4 *w_hi = reinterpret_cast<float4 *>(st + 2 * p.a_stage_bytes);
+        float4 *w_lo = reinterpret_cast<float4 *>(st + 2 * p.a_stage_bytes + p.w_stage_bytes);
+        float *raw = reinterpret_cast<float *>(st + 2 * (p.a_stage_bytes + p.w_stage_bytes));
+        const int chunks_here = (min(p.KB, Kr - k0) + 3) >> 2;
+        if (lane == 0) tc::mbar_arrive_expect_tx(&ctl->raw_full[s], (uint32_t)chunks_here * bytes_per_chunk);
+        __syncwarp();
+        if (lane < chunks_here) {
+          // lane = chunk: 4 consecutive channels b0..b0+3 of one table entry
+          const int r = k0 + 4 * lane;
+          const int pp = r / p.Bp, b0 = r - pp * p.Bp;
+          const int2 e = ent_s[e0 + pp];
+          tc::tma_load_4d(raw + (size_t)lane * p.raw_chunk_floats, &in_map, x0, e.y, tc_.n, b0, &ctl->raw_full[s]);
+          long long src = ((long long)(e.x * p.nky) * B4 + (b0 >> 2)) * NPtot + tc_.at * p.NP;
+          int dst = (lane >> 1) * (2 * p.NP) + (lane & 1) * p.NP;
+          for (int t = 0; t < p.nky && !p.w_res_bytes; ++t) {
+            tc::bulk_load(w_hi + dst, src_hi + src, w_chunk_bytes, &ctl->raw_full[s]);
+            tc::bulk_load(w_lo + dst, src_lo + src, w_chunk_bytes, &ctl->raw_full[s]);
+            src += (long long)B4 * NPtot;
+            dst += JB * 2 * p.NP;
+          }
+        }
+      }
+    }
+    PROF_END(3);
+  } else if (warp == kMmaWarp) {
     // =========================== MMA issuer ===========================
     if (lane == 0) {
       const uint32_t idesc = tc::idesc_tf32(kTileM, p.NP);
       const uint32_t a_lbo = (uint32_t)p.RW * 16u;
       const uint32_t b_lbo = (uint32_t)p.NP * 16u;
-      long long it = 0;  // K-blocks issued so far: stage = it % stages, accumulator = it & 1
+      int it = 0;  // K-blocks issued so far: stage = it % stages, accumulator = it & 1
       bool failed = false;
-      for (long long tile = blockIdx.x; tile < p.tiles && !*abort_flag && !failed; tile += gridDim.x) {
-        long long T = tile / p.a_tiles / p.y_tiles;
-        const int ox = (int)(T % p.nox);
-        const int np = p.row_ptr[ox + 1] - p.row_ptr[ox];
-        const int Kr = np * p.Bp;
+      PROF_BEGIN();
+      TileWalker tc_;
+      for (tc_.init(p); tc_.tile < p.tiles && !*abort_flag && !failed; tc_.next(p)) {
+        const int Kr = (rowptr_s[tc_.ox + 1] - rowptr_s[tc_.ox]) * p.Bp;
         for (int k0 = 0; k0 < Kr; k0 += p.KB, ++it) {
-          const int s = (int)(it % p.stages);
+          const int s = it % p.stages;
           const uint32_t use = (uint32_t)(it / p.stages);
-          const int acc = (int)(it & 1);
-          if (!tc::mbar_wait(&ctl->full[s], use & 1, kSpinLimit)) {
+          const int acc = it & 1;
+          PROF_WAIT_START();
+          // full[s] completes only after every converter has seen raw_full[s]
+          const bool okf = tc::mbar_wait(&ctl->full[s], use & 1, kSpinLimit) &&
+                           tc::mbar_wait(&ctl->dempty[acc], (uint32_t)(((it >> 1) & 1) ^ 1), kSpinLimit);
+          PROF_WAIT_END();
+          if (!okf) {
             raise_timeout(ctl, 4);
-            failed = true;
-            break;
-          }
-          if (!tc::mbar_wait(&ctl->dempty[acc], (uint32_t)(((it >> 1) & 1) ^ 1), kSpinLimit)) {
-            raise_timeout(ctl, 2);
             failed = true;
             break;
           }
           tc::tc_fence_after_sync();
           const uint32_t d_addr = tmem_base + (uint32_t)(acc * p.NP);
           const uint32_t st = tc::smem_u32(stage_base + (size_t)s * stage_bytes);
-          const uint32_t a_hi = st, a_lo = st + p.a_stage_bytes;
-          const uint32_t w_hi = st + 2 * p.a_stage_bytes, w_lo = w_hi + p.w_stage_bytes;
-          const int jb_here = (min(p.KB, Kr - k0) + 7) >> 3;
+          // descriptors of (k-step 0, tap 0); the others differ only in the start-address field
+          const uint64_t da_hi0 = tc::smem_desc(st, a_lbo, 128u);
+          const uint64_t da_lo0 = tc::smem_desc(st + p.a_stage_bytes, a_lbo, 128u);
+          const uint64_t db_hi0 = tc::smem_desc(st + 2 * p.a_stage_bytes, b_lbo, 128u);
+          const uint64_t db_lo0 = tc::smem_desc(st + 2 * p.a_stage_bytes + p.w_stage_bytes, b_lbo, 128u);
+          const int rows_here = min(p.KB, Kr - k0);
+          const int jb_here = (rows_here + 7) >> 3;
           uint32_t accumulate = 0;
-          for (int j = 0; j < jb_here; ++j) {
-            for (int t = 0; t < p.nky; ++t) {
-              const uint32_t a_off = (uint32_t)(2 * j) * a_lbo + (uint32_t)(t * absBy) * 16u;
-              const uint32_t b_off = (uint32_t)((t * JB + j) * 2 * p.NP) * 16u;
-              const uint64_t da_hi = tc::smem_desc(a_hi + a_off, a_lbo, 128u);
-              const uint64_t da_lo = tc::smem_desc(a_lo + a_off, a_lbo, 128u);
-              const uint64_t db_hi = tc::smem_desc(w_hi + b_off, b_lbo, 128u);
-              const uint64_t db_lo = tc::smem_desc(w_lo + b_off, b_lbo, 128u);
-              tc::mma_tf32(d_addr, da_lo, db_hi, idesc, accumulate);
-              tc::mma_tf32(d_addr, da_hi, db_lo, idesc, 1u);
-              tc::mma_tf32(d_addr, da_hi, db_hi, idesc, 1u);
-              accumulate = 1u;
+          if (p.w_res_bytes) {
+            // resident weights: the two 16-byte K-chunks of a k-step are the chunks
+            // of two consecutive (entry, channel group) rows; their distance goes
+            // into the descriptor
+            const uint32_t wr = tc::smem_u32(w_res) + (uint32_t)(tc_.at * p.NP) * 16u;
+            const uint32_t tap_stride = (uint32_t)(B4 * NPtot);  // 16-byte units between taps
+            const uint2 *ks = kstep_s + kofs_s[tc_.ox] + (k0 >> 3);
+            for (int j = 0; j < jb_here; ++j) {
+              const uint2 k = ks[j];
+              const uint64_t db_hi = tc::smem_desc(wr + k.x * 16u, k.y * 16u, 128u);
+              const uint64_t db_lo = db_hi + (p.w_res_bytes >> 4);
+              uint32_t a_off = (uint32_t)(2 * j * p.RW), b_off = 0;
+              for (int t = 0; t < p.nky; ++t) {
+                tc::mma_tf32(d_addr, da_lo0 + a_off, db_hi + b_off, idesc, accumulate);
+                tc::mma_tf32(d_addr, da_hi0 + a_off, db_lo + b_off, idesc, 1u);
+                tc::mma_tf32(d_addr, da_hi0 + a_off, db_hi + b_off, idesc, 1u);
+                accumulate = 1u;
+                a_off += (uint32_t)p.absBy;
+                b_off += tap_stride;
+              }
             }
+          } else {
+          for (int j = 0; j < jb_here; ++j) {
+            uint32_t a_off = (uint32_t)(2 * j * p.RW);       // 16-byte units
+            uint32_t b_off = (uint32_t)(j * 2 * p.NP);
+            for (int t = 0; t < p.nky; ++t) {
+              tc::mma_tf32(d_addr, da_lo0 + a_off, db_hi0 + b_off, idesc, accumulate);
+              tc::mma_tf32(d_addr, da_hi0 + a_off, db_lo0 + b_off, idesc, 1u);
+              tc::mma_tf32(d_addr, da_hi0 + a_off, db_hi0 + b_off, idesc, 1u);
+              accumulate = 1u;
+              a_off += (uint32_t)p.absBy;
+              b_off += (uint32_t)(JB * 2 * p.NP);
+            }
+          }
           }
           tc::tc_commit(&ctl->empty[s]);
           tc::tc_commit(&ctl->dfull[acc]);
         }
       }
+      PROF_END(2);
     }
     __syncwarp();
   }
 
   tc::tc_fence_before_sync();
   __syncthreads();
-  if (warp == kEpilogueWarps + kProducerWarps) {
+  if (warp == kMmaWarp) {
     tc::tc_fence_after_sync();
     tc::tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
   }
@@ -401,30 +562,47 @@ struct TcPlan {
 
 bool plan_tc_direct(const DirectProblem<float> &p, TcPlan &plan) {
   if (p.Dy != 1 || p.Ay != 1) return false;
-  if (p.A < 1 || p.B < 1 || p.nky < 1 || p.nkx < 1 || p.noy < 32 || p.nox < 1 || p.N < 1) return false;
-  if (p.table.max_row < 1) return false;
+  if (p.A < 1 || p.A > kMaxBias || p.B < 1 || p.nky < 1 || p.nkx < 1 || p.noy < 32 || p.nox < 1 || p.N < 1)
+    return false;
+  if (p.table.max_row < 1 || p.nox > kMaxTableRows || p.table.num_entries > kMaxTableEntries) return false;
   const int absBy = p.By < 0 ? -p.By : p.By;
   const long long halo = (long long)absBy * (p.nky - 1);
-  if (halo > 128) return false;
+  if (halo > 120) return false;
+  // the gathered rows are fetched with TMA: 16-byte aligned base and strides
+  if (p.niy % 4 != 0 || reinterpret_cast<uintptr_t>(p.in) % 16 != 0 || p.in_sn % 4 != 0 || p.in_sb % 4 != 0)
+    return false;
   TcParams &q = plan.params;
-  q.in = p.in, q.bias = p.accumulate ? nullptr : p.bias, q.out = p.out;
-  q.row_ptr = p.table.row_ptr, q.entries = p.table.entries;
-  q.N = p.N, q.A = p.A, q.B = p.B, q.Bp = (p.B + 3) / 4 * 4, q.nky = p.nky, q.niy = p.niy, q.nox = p.nox, q.noy = p.noy, q.nix = p.nix;
-  q.in_sn = p.in_sn, q.in_sb = p.in_sb, q.out_sn = p.out_sn, q.out_sa = p.out_sa;
-  q.By = p.By, q.Cy = p.Cy;
+  q.bias = p.accumulate ? nullptr : p.bias, q.out = p.out;
+  q.row_ptr = p.table.row_ptr, q.entries = p.table.entries, q.num_entries = (int)p.table.num_entries;
+  q.N = p.N, q.A = p.A, q.B = p.B, q.Bp = (p.B + 3) / 4 * 4, q.nky = p.nky, q.nox = p.nox, q.noy = p.noy;
+  q.out_sn = p.out_sn, q.out_sa = p.out_sa;
+  q.absBy = absBy;
+  q.ws0 = p.Cy + std::min(0, p.By * (p.nky - 1));
   const int a16 = (p.A + 15) / 16 * 16;
   q.a_tiles = (a16 + 127) / 128;  // the epilogue keeps NP running sums per thread: NP <= 128
   q.NP = ((a16 + q.a_tiles - 1) / q.a_tiles + 15) / 16 * 16;
   q.RW = (int)((kTileM + halo + 7) / 8 * 8);
+  q.RWt = q.RW + 4;
+  q.raw_chunk_floats = (4 * q.RWt + 31) / 32 * 32;
   q.y_tiles = (p.noy + kTileM - 1) / kTileM;
-  q.tiles = (long long)p.N * p.nox * q.y_tiles * q.a_tiles;
+  const long long tiles = (long long)p.N * p.nox * q.y_tiles * q.a_tiles;
+  if (tiles >= (1LL << 31)) return false;
+  q.tiles = (int)tiles;
   int cols = 32;
   while (cols < 2 * q.NP) cols *= 2;
   q.tmem_cols = cols;
   // rows per stage: as many as fit a budget, at most what the longest table row needs
   const long long max_rows = ((long long)p.table.max_row * q.Bp + 7) / 8 * 8;
-  const size_t per_row = 8u * q.RW + 8u * (size_t)p.nky * q.NP;  // bytes of A (hi+lo) and W (hi+lo) per row
-  const size_t budget = 200 * 1024;
+  // small weight sets stay resident in shared memory for the whole block
+  plan.pack_floats = (size_t)p.nkx * p.nky * q.Bp * q.NP * q.a_tiles;
+  const size_t w_all = plan.pack_floats * sizeof(float) + 2048;  // + room for the dummy second chunk of an odd tail
+  q.w_pack_bytes = (uint32_t)(plan.pack_floats * sizeof(float));
+  const long long ksteps = (p.table.num_entries * (long long)(q.Bp / 4) + 1) / 2 + p.nox;  // upper bound
+  q.w_res_bytes = (2 * w_all <= 72 * 1024 && ksteps <= kMaxKSteps) ? (uint32_t)((w_all + 127) / 128 * 128) : 0u;
+  // bytes per row: raw copy, A (hi+lo) and, unless resident, W (hi+lo)
+  const size_t per_row =
+      (size_t)q.raw_chunk_floats + 8u * q.RW + (q.w_res_bytes ? 0u : 8u * (size_t)p.nky * q.NP);
+  const size_t budget = 227 * 1024 - kStageOffset - 1024 - 2 * (size_t)q.w_res_bytes;
   int stages = 3;
   long long kb = (long long)(budget / stages / per_row) / 8 * 8;
   if (kb < 8) {
@@ -436,17 +614,37 @@ bool plan_tc_direct(const DirectProblem<float> &p, TcPlan &plan) {
   // at most 96 chained MMAs (3 per tap per 8 rows) per K-block, see the note on accumulation above
   kb = std::min<long long>(kb, std::max<long long>(8, 96 / (3 * p.nky) * 8));
   q.KB = (int)kb;
+  // short K-blocks leave room for a deeper ring
+  while (stages < kMaxStages && (size_t)(stages + 1) * q.KB * per_row <= budget) ++stages;
   q.stages = stages;
   q.a_stage_bytes = (uint32_t)(q.KB / 4 * q.RW * 16);
-  q.w_stage_bytes = (uint32_t)(p.nky * (q.KB / 8) * q.NP * 32);
-  plan.smem = kControlBytes + (size_t)stages * 2 * (q.a_stage_bytes + q.w_stage_bytes);
+  q.w_stage_bytes = q.w_res_bytes ? 0u : (uint32_t)(p.nky * (q.KB / 8) * q.NP * 32);
+  q.raw_stage_bytes = (uint32_t)(q.KB / 4 * q.raw_chunk_floats * 4);
+  plan.smem = kStageOffset + 2 * (size_t)q.w_res_bytes +
+              (size_t)stages * (2 * (q.a_stage_bytes + q.w_stage_bytes) + q.raw_stage_bytes);
   // one block per SM: keep shared memory above half of the SM so that the
   // TMEM request of a co-resident block can never wait for columns
   plan.smem = std::max<size_t>(plan.smem, 116 * 1024);
   if (plan.smem > 227 * 1024) return false;
-  plan.pack_floats = (size_t)p.nkx * p.nky * q.Bp * q.NP * q.a_tiles;
   plan.grid = (int)std::min<long long>(q.tiles, sm_count());
+  q.profile = 0;
   return true;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn tensor_map_encoder() {
+  static EncodeTiledFn encode = nullptr;
+  if (encode == nullptr) {
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      encode = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  return encode;
 }
 
 }  // namespace
@@ -466,6 +664,21 @@ int launch_direct_tc(const DirectProblem<float> &p, void *workspace, size_t work
   if (workspace == nullptr || workspace_bytes < 2 * part || reinterpret_cast<uintptr_t>(workspace) % 16 != 0)
     return fail(MELLIN_ERR_WORKSPACE, "workspace too small or misaligned: need " + std::to_string(2 * part) +
                                           " bytes (16-byte aligned), got " + std::to_string(workspace_bytes));
+  // the activations as a 4-D tensor (position, Mellin row, batch, channel) with their real strides
+  CUtensorMap in_map;
+  {
+    EncodeTiledFn encode = tensor_map_encoder();
+    if (encode == nullptr) return fail(MELLIN_ERR_LAUNCH, "cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t dims[4] = {(cuuint64_t)p.niy, (cuuint64_t)p.nix, (cuuint64_t)p.N, (cuuint64_t)p.B};
+    const cuuint64_t strides[3] = {(cuuint64_t)p.niy * sizeof(float), (cuuint64_t)p.in_sn * sizeof(float),
+                                   (cuuint64_t)p.in_sb * sizeof(float)};
+    const cuuint32_t box[4] = {(cuuint32_t)plan.params.RWt, 1u, 1u, 4u};
+    const cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+    const CUresult r = encode(&in_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(p.in), dims, strides, box,
+                              estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return MELLIN_ERR_UNSUPPORTED;  // strides the copy engine cannot express
+  }
   float *w_hi = static_cast<float *>(workspace);
   float *w_lo = reinterpret_cast<float *>(static_cast<unsigned char *>(workspace) + part);
   {
@@ -480,7 +693,9 @@ int launch_direct_tc(const DirectProblem<float> &p, void *workspace, size_t work
   }
   plan.params.w_hi = w_hi;
   plan.params.w_lo = w_lo;
-  void (*kernel)(TcParams) = nullptr;
+  const char *prof = getenv("MELLIN_TC_PROFILE");
+  plan.params.profile = (prof != nullptr && prof[0] == '1') ? 1 : 0;
+  void (*kernel)(TcParams, const CUtensorMap) = nullptr;
   switch (plan.params.NP / 16) {
     case 1: kernel = tc_direct_kernel<1>; break;
     case 2: kernel = tc_direct_kernel<2>; break;
@@ -493,11 +708,15 @@ int launch_direct_tc(const DirectProblem<float> &p, void *workspace, size_t work
   }
   cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem);
   if (err != cudaSuccess) return fail(MELLIN_ERR_LAUNCH, std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(err));
-  kernel<<<plan.grid, kThreads, plan.smem, stream>>>(plan.params);
+  kernel<<<plan.grid, kThreads, plan.smem, stream>>>(plan.params, in_map);
   err = cudaGetLastError();
   if (err != cudaSuccess) return fail(MELLIN_ERR_LAUNCH, std::string("tc_direct_kernel: ") + cudaGetErrorString(err));
   count_launch();
   return MELLIN_OK;
+}
+
+int tc_read_prof(long long *out) {
+  return cudaMemcpyFromSymbol(out, g_tc_prof, 16 * sizeof(long long)) == cudaSuccess ? 0 : 2;
 }
 
 // Reads and clears the device-side timeout flag of the current device

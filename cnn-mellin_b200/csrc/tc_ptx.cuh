@@ -37,6 +37,38 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint32
   return false;
 }
 
+// arrive and announce `bytes` of asynchronous copies that will complete on this barrier
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+
+// ---- TMA (bulk asynchronous copies, global -> this block's shared memory) ---------
+// one box of a 2-D tensor map; coordinates may lie outside the tensor (zero fill),
+// x * element size must be a multiple of 16 bytes
+__device__ __forceinline__ void tma_load_2d(void *dst, const void *tensor_map, int x, int y, uint64_t *bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+          smem_u32(dst)),
+      "l"(tensor_map), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+// one box of a 4-D tensor map (coordinates innermost first)
+__device__ __forceinline__ void tma_load_4d(void *dst, const void *tensor_map, int c0, int c1, int c2, int c3,
+                                            uint64_t *bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::
+          "r"(smem_u32(dst)),
+      "l"(tensor_map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(smem_u32(bar))
+      : "memory");
+}
+// contiguous bytes; both addresses 16-byte aligned, size a multiple of 16
+__device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(dst)),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
 // generic-proxy writes to shared memory must be fenced before the tensor core
 // (async proxy) reads them
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
