@@ -51,6 +51,11 @@ int check_geometry(const char *who, const Geometry2D &q, int64_t linear_divisor)
 
 // tensor cores when enabled, covered and given scratch; CUDA cores otherwise
 int dispatch_direct(const DirectProblem<float> &p, void *workspace, size_t workspace_bytes, cudaStream_t stream) {
+  if (p.A <= 4) {
+    // a handful of output channels: the row-streaming CUDA-core kernel
+    const int rc = launch_direct_rows(p, stream);
+    if (rc != MELLIN_ERR_UNSUPPORTED) return rc;
+  }
   if (!p.accumulate && tensor_cores_enabled() && workspace != nullptr) {
     const size_t need = direct_tc_workspace_bytes(p);
     if (need > 0 && workspace_bytes >= need) {

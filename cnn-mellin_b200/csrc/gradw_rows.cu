@@ -30,7 +30,7 @@ constexpr int kTK = 128;            // positions per tile
 constexpr int kGoPitch = kTK + 4;   // floats; 4 extra keep 16-byte rows and spread banks
 constexpr int kXPitch = kTK + 8;    // floats per staged input row (window + taps)
 constexpr int kMaxKx = 8;
-constexpr int kStages = 3;
+constexpr int kStages = 2;
 
 struct RowsTiling {
   int y_tiles = 0, a_tiles = 0;
@@ -57,7 +57,7 @@ __device__ __forceinline__ void cp_async_wait() {
 }
 
 template <int B, int NKY>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, 2)
 gradw_rows_kernel(const GradWProblem<float> p, const RowsTiling t, float *__restrict__ part_w,
                   float *__restrict__ part_b) {
   constexpr int BN = B * NKY;
@@ -77,38 +77,42 @@ gradw_rows_kernel(const GradWProblem<float> p, const RowsTiling t, float *__rest
     for (int i = 0; i < BN; ++i) acc[k][i] = 0.f;
 
   // ---- stage loader: every thread issues its share of one tile's copies -------
+  const int warp = tid >> 5, lane = tid & 31;
+  const long long go_plane = (long long)p.nox * p.noy;  // one (n, a) plane of grad_y
   auto load_tile = [&](long long tile, int stage) {
     if (tile < t.tiles) {
-      const int yt = (int)(tile % t.y_tiles);
-      long long r = tile / t.y_tiles;
-      const int ox = (int)(r % p.nox);
-      const int n = (int)(r / p.nox);
+      const int tl = (int)tile;
+      const int yt = tl % t.y_tiles;
+      const int r = tl / t.y_tiles;
+      const int ox = r % p.nox, n = r / p.nox;
       const int y0 = yt * kTK;
       float *gos = smem + stage * kStageFloats;
       float *xs = gos + kTA * kGoPitch;
-      // output-gradient slab: 64 rows x 32 chunks of 16 bytes
+      // output-gradient slab: a warp copies a row of 32 chunks of 16 bytes
+      {
+        const int y = y0 + 4 * lane;
+        const float *base = p.go + ((long long)n * p.A + a0) * go_plane + (long long)ox * p.noy + y;
 #pragma unroll
-      for (int k = 0; k < kTA * (kTK / 4) / kThreads; ++k) {
-        const int idx = tid + k * kThreads;
-        const int row = idx >> 5, ch = idx & 31;
-        const int a = a0 + row, y = y0 + 4 * ch;
-        const bool valid = a < p.A && y < p.noy;
-        const float *src = valid ? p.go + (((long long)n * p.A + a) * p.nox + ox) * p.noy + y : p.go;
-        cp_async16(gos + row * kGoPitch + 4 * ch, src, valid);
+        for (int k = 0; k < kTA / 8; ++k) {
+          const int row = warp + 8 * k;
+          const bool valid = a0 + row < p.A && y < p.noy;
+          cp_async16(gos + row * kGoPitch + 4 * lane, valid ? base + row * go_plane : p.go, valid);
+        }
       }
       // input rows of the taps of this ox: slot = kx, one row per input channel
       const int e0 = p.table_h.row_ptr[ox];
       const int np = p.table_h.row_ptr[ox + 1] - e0;
       const int ws = y0 + t.ws0;
-      for (int idx = tid; idx < np * B * kXPitch; idx += kThreads) {
-        const int c = idx % kXPitch;
-        const int rb = idx / kXPitch;
+      for (int rb = warp; rb < np * B; rb += kThreads / 32) {
         const int b = rb % B, pp = rb / B;
         const int2 e = p.table_h.entries[e0 + pp];
-        const int iy = ws + c;
-        const bool valid = iy >= 0 && iy < p.niy;
-        const float *src = valid ? p.in + (((long long)n * p.B + b) * p.nix + e.y) * p.niy + iy : p.in;
-        cp_async4(xs + (e.x * B + b) * kXPitch + c, src, valid);
+        const float *row = p.in + (((long long)n * p.B + b) * p.nix + e.y) * p.niy;
+        float *dst = xs + (e.x * B + b) * kXPitch;
+        for (int c = lane; c < kXPitch; c += 32) {
+          const int iy = ws + c;
+          const bool valid = iy >= 0 && iy < p.niy;
+          cp_async4(dst + c, valid ? row + iy : p.in, valid);
+        }
       }
     }
     cp_async_commit();
@@ -123,7 +127,7 @@ gradw_rows_kernel(const GradWProblem<float> p, const RowsTiling t, float *__rest
     cp_async_wait<kStages - 1>();
     __syncthreads();
 
-    const int ox = (int)((tile / t.y_tiles) % p.nox);
+    const int ox = ((int)tile / t.y_tiles) % p.nox;
     const int e0 = p.table_h.row_ptr[ox];
     const int np = p.table_h.row_ptr[ox + 1] - e0;
     unsigned mask = 0;
@@ -216,8 +220,9 @@ bool plan_rows(const GradWProblem<float> &p, RowsTiling &t) {
   t.y_tiles = (p.noy + kTK - 1) / kTK;
   t.a_tiles = (p.A + kTA - 1) / kTA;
   t.tiles = (long long)p.N * p.nox * t.y_tiles;
+  if (t.tiles >= (1LL << 31)) return false;
   t.ws0 = p.Cy + std::min(0, p.By * (p.nky - 1));
-  t.Z = (int)std::min<long long>(t.tiles, std::max(1, sm_count() / t.a_tiles));
+  t.Z = (int)std::min<long long>(t.tiles, std::max(1, 2 * sm_count() / t.a_tiles));
   t.smem = (size_t)kStages * (kTA * kGoPitch + kMaxKx * p.B * kXPitch) * sizeof(float);
   return t.smem <= 200 * 1024;
 }
