@@ -1,6 +1,7 @@
 // extern "C" surface of the library: argument validation, translation of the
 // reference's operator vocabulary (f, g, h, transposition flags, s/d/p/u) into
 // the kernels' problem descriptions, table look-up, launch.
+#include <algorithm>
 #include <cstdint>
 #include <stdexcept>
 #include <string>
@@ -53,7 +54,7 @@ int check_geometry(const char *who, const Geometry2D &q, int64_t linear_divisor)
 int dispatch_direct(const DirectProblem<float> &p, void *workspace, size_t workspace_bytes, cudaStream_t stream) {
   if (p.A <= 4) {
     // a handful of output channels: the row-streaming CUDA-core kernel
-    const int rc = launch_direct_rows(p, stream);
+    const int rc = launch_direct_rows(p, workspace, workspace_bytes, stream);
     if (rc != MELLIN_ERR_UNSUPPORTED) return rc;
   }
   if (!p.accumulate && tensor_cores_enabled() && workspace != nullptr) {
@@ -308,7 +309,8 @@ static size_t direct_workspace_query(const Geometry2D &q, bool input_gradient) {
   p.Cy = input_gradient ? (int)q.py : -(int)q.py;
   p.Dy = input_gradient ? (int)q.sy : (int)q.uy;
   p.table.max_row = (int)q.nfx;  // upper bound: one entry per kernel tap
-  return direct_tc_workspace_bytes(p);
+  const size_t rows = p.A <= 4 ? direct_rows_workspace_bytes(p) : 0;
+  return std::max(rows, direct_tc_workspace_bytes(p));
 }
 size_t mellin_mcorrlcorr_forward_workspace_bytes(MELLIN_LAYER_GEOMETRY) {
   return direct_workspace_query(GEOM_FROM_LAYER, false);

@@ -6,17 +6,23 @@
 //                       W[a, b, kx, ky] * in[n, b, ix, oy + By * ky + Cy]
 //
 // The work is a long reduction over (table entry, b) of rows of `in`; the
-// output tile is tiny.  A block owns (n, ox, 256 positions).  Each of its 8
-// warps takes every 8th reduced channel and streams "its" rows through a
-// private 4-deep cp.async ring -- there is no block-wide barrier in the main
-// loop -- while the whole weight set sits in shared memory and is read with
-// broadcast loads.  A lane keeps A x 8 running sums (8 consecutive positions);
+// output tile is tiny.  A block owns (n, ox, 240 positions).  Each of its 8
+// warps takes every 8th group of 4 reduced channels and streams "its" rows through a
+// private ring filled by TMA box loads of 4 rows each (one lane issues, an mbarrier
+// per slot signals arrival; positions outside the signal are zero-filled by the
+// copy engine) -- there is no block-wide barrier in the main loop -- while the
+// whole weight set sits in shared memory and is read with broadcast loads.
+// A lane keeps A x 8 running sums (8 consecutive positions);
 // the eight warps' partial sums are combined through shared memory at the end.
+#include <cuda.h>
+
 #include <algorithm>
 #include <string>
 
 #include "../../include/mellin_b200.h"
+
 #include "mellin_internal.h"
+#include "tc_ptx.cuh"
 
 namespace mellin {
 
@@ -25,37 +31,35 @@ namespace {
 constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
 constexpr int kRY = 8;                 // positions per lane
-constexpr int kTY = 32 * kRY;          // positions per block
-constexpr int kRowFloats = kTY + 12;   // staged row: tile + taps (<= 4) + alignment lead (<= 3), multiple of 4
-constexpr int kStages = 4;
+constexpr int kLanes = 30;             // lanes that own positions (a staged row must fit a 256-element TMA box)
+constexpr int kTY = kLanes * kRY;      // positions per block: 240
+constexpr int kRowFloats = 256;        // staged row: tile + taps (<= 4) + alignment lead (<= 3) <= 256
+constexpr int kGroup = 4;              // consecutive reduced channels fetched by one TMA box
+constexpr int kSlotFloats = kGroup * kRowFloats;
+constexpr int kStages = 2;
+constexpr int kRedPitch = 256;
 
 struct RowsPlan {
   int y_tiles = 0;
   int ws0 = 0;     // first input position of tile 0 relative to its first output position
   int WP = 0;      // floats per (kx, b) weight record: A * NKY rounded up to 4
   int vec_store = 0;
+  int w_floats = 0;        // weight records in shared memory, rounded up to 128 bytes
+  const float *w_packed = nullptr;  // records pre-packed in global memory (nullptr: gather in the kernel)
   size_t smem = 0;
 };
 
-__device__ __forceinline__ void cp16(void *dst, const void *src, bool valid) {
-  const unsigned d = static_cast<unsigned>(__cvta_generic_to_shared(dst));
-  const int bytes = valid ? 16 : 0;  // 0 source bytes: the destination is zero-filled
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
-
 template <int A, int NKY>
-__global__ void __launch_bounds__(kThreads) direct_rows_kernel(const DirectProblem<float> p, const RowsPlan t) {
+__global__ void __launch_bounds__(kThreads)
+direct_rows_kernel(const DirectProblem<float> p, const RowsPlan t, const __grid_constant__ CUtensorMap in_map) {
   constexpr int AN = A * NKY;
   constexpr int WP = (AN + 3) / 4 * 4;
   constexpr int kWin = kRY + NKY - 1;
-  extern __shared__ __align__(16) float smem[];
+  extern __shared__ __align__(128) float smem[];
   float *Ws = smem;                                         // [nkx][B][WP]
-  float *ring = smem + (size_t)p.nkx * p.B * WP;            // [warp][stage][kRowFloats]
+  float *ring = smem + t.w_floats;                          // [warp][stage][kSlotFloats]
+  __shared__ uint64_t slot_full[kWarps][kStages];
+  __shared__ uint64_t w_full;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   int bid = blockIdx.x;
@@ -65,44 +69,61 @@ __global__ void __launch_bounds__(kThreads) direct_rows_kernel(const DirectProbl
   const int n = bid / p.nox;
   const int y0 = yt * kTY;
 
-  // ---- weights: record (kx, b) holds W[a, b, kx, .] for all a, taps in increasing input offset
-  for (int i = tid; i < p.nkx * p.B * WP; i += kThreads) {
-    const int e = i % WP;
-    const int rec = i / WP;
-    const int b = rec % p.B, kx = rec / p.B;
-    float v = 0.f;
-    if (e < AN) {
-      const int a = e / NKY, k = e % NKY;
-      const int ky = p.By < 0 ? NKY - 1 - k : k;
-      v = __ldg(p.w + a * p.w_sa + b * p.w_sb + (long long)kx * NKY + ky);
-    }
-    Ws[i] = v;
+  if (tid == 0) {
+    for (int w = 0; w < kWarps; ++w)
+      for (int st = 0; st < kStages; ++st) tc::mbar_init(&slot_full[w][st], 1);
+    tc::mbar_init(&w_full, 1);
+    tc::fence_mbar_init();
   }
   __syncthreads();
+  // ---- weights: record (kx, b) holds W[a, b, kx, .] for all a, taps in increasing input offset
+  if (t.w_packed != nullptr) {
+    if (tid == 0) {
+      const uint32_t bytes = (uint32_t)(p.nkx * p.B * WP) * 4u;
+      tc::mbar_arrive_expect_tx(&w_full, bytes);
+      tc::bulk_load(Ws, t.w_packed, bytes, &w_full);
+    }
+  } else {
+    for (int i = tid; i < p.nkx * p.B * WP; i += kThreads) {
+      const int e = i % WP;
+      const int rec = i / WP;
+      const int b = rec % p.B, kx = rec / p.B;
+      float v = 0.f;
+      if (e < AN) {
+        const int a = e / NKY, k = e % NKY;
+        const int ky = p.By < 0 ? NKY - 1 - k : k;
+        v = __ldg(p.w + a * p.w_sa + b * p.w_sb + (long long)kx * NKY + ky);
+      }
+      Ws[i] = v;
+    }
+    __syncthreads();
+  }
 
   const int e0 = p.table.row_ptr[ox];
   const int np = p.table.row_ptr[ox + 1] - e0;
   const int ws = y0 + t.ws0;
   const int start = ws & ~3;  // 16-byte aligned copy origin (two's complement: floors negatives too)
   const int lead = ws - start;
-  float *my_ring = ring + (size_t)warp * kStages * kRowFloats;
-  const int per_entry = (p.B - warp + kWarps - 1) / kWarps;  // reduced channels this warp takes per entry
+  float *my_ring = ring + (size_t)warp * kStages * kSlotFloats;
+  const int groups = (p.B + kGroup - 1) / kGroup;
+  const int per_entry = (groups - warp + kWarps - 1) / kWarps;  // channel groups this warp takes per entry
   const int items = per_entry > 0 ? np * per_entry : 0;
 
-  auto issue = [&](int item, int stage) {
-    if (item < items) {
-      const int pp = item / per_entry;
-      const int b = warp + kWarps * (item - pp * per_entry);
-      const int ix = p.table.entries[e0 + pp].y;
-      const float *row = p.in + n * p.in_sn + b * p.in_sb + (long long)ix * p.niy;
-      float *dst = my_ring + stage * kRowFloats;
-      for (int c = lane; c < kRowFloats / 4; c += 32) {
-        const int iy = start + 4 * c;
-        const bool valid = iy >= 0 && iy < p.niy;  // niy and start are multiples of 4: a chunk is in or out as a whole
-        cp16(dst + 4 * c, valid ? row + iy : p.in, valid);
-      }
+  // issue side: item -> (entry ipp, k-th channel of this warp), advanced incrementally
+  int ipp = 0, ik = 0, iix = np > 0 ? p.table.entries[e0].y : 0;
+  auto issue = [&](int item) {
+    if (item < items && lane == 0) {
+      const int stage = item % kStages;
+      tc::fence_proxy_async();  // the slot's previous contents were read through the generic proxy
+      tc::mbar_arrive_expect_tx(&slot_full[warp][stage], (uint32_t)kSlotFloats * 4u);
+      tc::tma_load_4d(my_ring + stage * kSlotFloats, &in_map, start, iix, n, kGroup * (warp + kWarps * ik),
+                      &slot_full[warp][stage]);
     }
-    cp_commit();
+    if (++ik == per_entry) {
+      ik = 0;
+      ++ipp;
+      if (ipp < np) iix = p.table.entries[e0 + ipp].y;
+    }
   };
 
   float acc[A][kRY];
@@ -112,41 +133,54 @@ __global__ void __launch_bounds__(kThreads) direct_rows_kernel(const DirectProbl
     for (int j = 0; j < kRY; ++j) acc[a][j] = 0.f;
 
 #pragma unroll
-  for (int s = 0; s < kStages - 1; ++s) issue(s, s);
-  for (int item = 0; item < items; ++item) {
-    issue(item + kStages - 1, (item + kStages - 1) % kStages);
-    cp_wait<kStages - 1>();
-    __syncwarp();
-    const int pp = item / per_entry;
-    const int b = warp + kWarps * (item - pp * per_entry);
-    const int kx = p.table.entries[e0 + pp].x;
-    const float *row = my_ring + (item % kStages) * kRowFloats + lead + kRY * lane;
-    float xw[kWin];
-#pragma unroll
-    for (int j = 0; j < kWin; ++j) xw[j] = row[j];
-    const float4 *wrec = reinterpret_cast<const float4 *>(Ws + (size_t)(kx * p.B + b) * WP);
-    float wv[WP];
-#pragma unroll
-    for (int i = 0; i < WP / 4; ++i) {
-      const float4 v = wrec[i];
-      wv[4 * i] = v.x, wv[4 * i + 1] = v.y, wv[4 * i + 2] = v.z, wv[4 * i + 3] = v.w;
-    }
-#pragma unroll
-    for (int a = 0; a < A; ++a)
-#pragma unroll
-      for (int k = 0; k < NKY; ++k)
-#pragma unroll
-        for (int j = 0; j < kRY; ++j) acc[a][j] = fmaf(wv[a * NKY + k], xw[j + k], acc[a][j]);
-    __syncwarp();
+  for (int st = 0; st < kStages - 1; ++st) issue(st);
+  if (t.w_packed != nullptr) {
+    const bool ok = tc::mbar_wait(&w_full, 0, 1u << 20);
+    if (!__all_sync(0xffffffffu, ok)) return;  // cannot happen unless the copy engine faulted; never spin forever
   }
-  cp_wait<0>();
+  int cpp = 0, ck = 0, ckx = np > 0 ? p.table.entries[e0].x : 0;
+  for (int item = 0; item < items; ++item) {
+    issue(item + kStages - 1);
+    const bool ok = tc::mbar_wait(&slot_full[warp][item % kStages], (uint32_t)((item / kStages) & 1), 1u << 20);
+    if (!__all_sync(0xffffffffu, ok)) break;
+    const int b0 = kGroup * (warp + kWarps * ck);
+    if (lane < kLanes) {
+#pragma unroll
+      for (int r = 0; r < kGroup; ++r) {
+        if (b0 + r >= p.B) break;  // channels past the last were zero-filled by the copy; they have no weights
+        const float *row = my_ring + (item % kStages) * kSlotFloats + r * kRowFloats + lead + kRY * lane;
+        float xw[kWin];
+#pragma unroll
+        for (int j = 0; j < kWin; ++j) xw[j] = row[j];
+        const float4 *wrec = reinterpret_cast<const float4 *>(Ws + (size_t)(ckx * p.B + b0 + r) * WP);
+        float wv[WP];
+#pragma unroll
+        for (int i = 0; i < WP / 4; ++i) {
+          const float4 v = wrec[i];
+          wv[4 * i] = v.x, wv[4 * i + 1] = v.y, wv[4 * i + 2] = v.z, wv[4 * i + 3] = v.w;
+        }
+#pragma unroll
+        for (int a = 0; a < A; ++a)
+#pragma unroll
+          for (int k = 0; k < NKY; ++k)
+#pragma unroll
+            for (int j = 0; j < kRY; ++j) acc[a][j] = fmaf(wv[a * NKY + k], xw[j + k], acc[a][j]);
+      }
+    }
+    __syncwarp();
+    if (++ck == per_entry) {
+      ck = 0;
+      ++cpp;
+      if (cpp < np) ckx = p.table.entries[e0 + cpp].x;
+    }
+  }
   __syncthreads();
 
   // ---- combine the warps: red[warp][a][position] -----------------------------------
   float *red = ring;
 #pragma unroll
   for (int a = 0; a < A; ++a) {
-    float4 *dst = reinterpret_cast<float4 *>(red + ((size_t)warp * A + a) * kTY + kRY * lane);
+    float4 *dst = reinterpret_cast<float4 *>(red + ((size_t)warp * A + a) * kRedPitch + kRY * lane);
     dst[0] = make_float4(acc[a][0], acc[a][1], acc[a][2], acc[a][3]);
     dst[1] = make_float4(acc[a][4], acc[a][5], acc[a][6], acc[a][7]);
   }
@@ -156,7 +190,7 @@ __global__ void __launch_bounds__(kThreads) direct_rows_kernel(const DirectProbl
     float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for (int w = 0; w < kWarps; ++w) {
-      const float4 v = *reinterpret_cast<const float4 *>(red + ((size_t)w * A + a) * kTY + pos);
+      const float4 v = *reinterpret_cast<const float4 *>(red + ((size_t)w * A + a) * kRedPitch + pos);
       s.x += v.x, s.y += v.y, s.z += v.z, s.w += v.w;
     }
     const int y = y0 + pos;
@@ -192,10 +226,11 @@ bool plan_rows(const DirectProblem<float> &p, RowsPlan &t) {
   if ((long long)p.N * p.nox * t.y_tiles >= (1LL << 31)) return false;
   t.ws0 = p.Cy + std::min(0, p.By * (p.nky - 1));
   t.WP = (p.A * p.nky + 3) / 4 * 4;
-  const size_t w_floats = (size_t)p.nkx * p.B * t.WP;
-  const size_t ring_floats = (size_t)kWarps * kStages * kRowFloats;
-  const size_t red_floats = (size_t)kWarps * p.A * kTY;
-  t.smem = (w_floats + std::max(ring_floats, red_floats)) * sizeof(float);
+  const size_t w_floats = ((size_t)p.nkx * p.B * t.WP + 31) / 32 * 32;
+  t.w_floats = (int)w_floats;
+  const size_t ring_floats = (size_t)kWarps * kStages * kSlotFloats;
+  const size_t red_floats = (size_t)kWarps * p.A * kRedPitch;
+  t.smem = (w_floats + std::max(ring_floats, red_floats)) * sizeof(float) + 128;  // + slack to align the base
   if (t.smem > 100 * 1024) return false;
   t.vec_store = (reinterpret_cast<uintptr_t>(p.out) % 16 == 0 && p.noy % 4 == 0 && p.out_sn % 4 == 0 &&
                  p.out_sa % 4 == 0)
@@ -204,9 +239,43 @@ bool plan_rows(const DirectProblem<float> &p, RowsPlan &t) {
   return true;
 }
 
+// weight records in the kernel's shared-memory layout: [kx][b][WP], entry a * nky + k
+// holds W[a, b, kx, ky(k)] with taps in increasing input offset
+__global__ void pack_rows_weights_kernel(const float *__restrict__ w, long long w_sa, long long w_sb, int A, int B,
+                                         int nkx, int nky, int WP, int By, float *__restrict__ out) {
+  const int total = nkx * B * WP;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    const int e = i % WP, rec = i / WP;
+    const int b = rec % B, kx = rec / B;
+    float v = 0.f;
+    if (e < A * nky) {
+      const int a = e / nky, k = e % nky;
+      const int ky = By < 0 ? nky - 1 - k : k;
+      v = w[a * w_sa + b * w_sb + (long long)kx * nky + ky];
+    }
+    out[i] = v;
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn tensor_map_encoder() {
+  static EncodeTiledFn encode = nullptr;
+  if (encode == nullptr) {
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      encode = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  return encode;
+}
+
 template <int A>
-int dispatch_nky(const DirectProblem<float> &p, const RowsPlan &t, cudaStream_t stream) {
-  void (*kernel)(DirectProblem<float>, RowsPlan) = nullptr;
+int dispatch_nky(const DirectProblem<float> &p, const RowsPlan &t, const CUtensorMap &in_map, cudaStream_t stream) {
+  void (*kernel)(DirectProblem<float>, RowsPlan, const CUtensorMap) = nullptr;
   switch (p.nky) {
     case 1: kernel = direct_rows_kernel<A, 1>; break;
     case 2: kernel = direct_rows_kernel<A, 2>; break;
@@ -217,7 +286,7 @@ int dispatch_nky(const DirectProblem<float> &p, const RowsPlan &t, cudaStream_t 
     if (err != cudaSuccess) return fail(MELLIN_ERR_LAUNCH, std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(err));
   }
   const unsigned blocks = (unsigned)((long long)p.N * p.nox * t.y_tiles);
-  kernel<<<blocks, kThreads, t.smem, stream>>>(p, t);
+  kernel<<<blocks, kThreads, t.smem, stream>>>(p, t, in_map);
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return fail(MELLIN_ERR_LAUNCH, std::string("direct_rows_kernel: ") + cudaGetErrorString(err));
   count_launch();
@@ -226,15 +295,51 @@ int dispatch_nky(const DirectProblem<float> &p, const RowsPlan &t, cudaStream_t 
 
 }  // namespace
 
+// scratch for the pre-packed weight records (0 = problem not covered by this kernel)
+size_t direct_rows_workspace_bytes(const DirectProblem<float> &p) {
+  RowsPlan t;
+  if (!plan_rows(p, t)) return 0;
+  return (size_t)p.nkx * p.B * t.WP * sizeof(float);
+}
+
 // MELLIN_ERR_UNSUPPORTED when the problem is outside this kernel's coverage.
-int launch_direct_rows(const DirectProblem<float> &p, cudaStream_t stream) {
+// With too little (or no) workspace the weights are gathered inside the kernel.
+int launch_direct_rows(const DirectProblem<float> &p, void *workspace, size_t workspace_bytes, cudaStream_t stream) {
   RowsPlan t;
   if (!plan_rows(p, t)) return MELLIN_ERR_UNSUPPORTED;
+  EncodeTiledFn encode = tensor_map_encoder();
+  if (encode == nullptr) return MELLIN_ERR_UNSUPPORTED;
+  CUtensorMap in_map;
+  {
+    // the reduced tensor as (position, Mellin row, batch, channel) with its real strides;
+    // a box is one staged row for each of 4 consecutive channels
+    const cuuint64_t dims[4] = {(cuuint64_t)p.niy, (cuuint64_t)p.nix, (cuuint64_t)p.N, (cuuint64_t)p.B};
+    const cuuint64_t strides[3] = {(cuuint64_t)p.niy * sizeof(float), (cuuint64_t)p.in_sn * sizeof(float),
+                                   (cuuint64_t)p.in_sb * sizeof(float)};
+    const cuuint32_t box[4] = {(cuuint32_t)kRowFloats, 1u, 1u, (cuuint32_t)kGroup};
+    const cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+    if (encode(&in_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(p.in), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return MELLIN_ERR_UNSUPPORTED;
+  }
+  const size_t need = (size_t)p.nkx * p.B * t.WP * sizeof(float);
+  if (workspace != nullptr && workspace_bytes >= need && reinterpret_cast<uintptr_t>(workspace) % 16 == 0) {
+    float *packed = static_cast<float *>(workspace);
+    const int total = p.nkx * p.B * t.WP;
+    pack_rows_weights_kernel<<<(total + 255) / 256, 256, 0, stream>>>(p.w, p.w_sa, p.w_sb, p.A, p.B, p.nkx, p.nky, t.WP,
+                                                                      p.By, packed);
+    cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess)
+      return fail(MELLIN_ERR_LAUNCH, std::string("pack_rows_weights_kernel: ") + cudaGetErrorString(err));
+    count_launch();
+    t.w_packed = packed;
+  }
   switch (p.A) {
-    case 1: return dispatch_nky<1>(p, t, stream);
-    case 2: return dispatch_nky<2>(p, t, stream);
-    case 3: return dispatch_nky<3>(p, t, stream);
-    default: return dispatch_nky<4>(p, t, stream);
+    case 1: return dispatch_nky<1>(p, t, in_map, stream);
+    case 2: return dispatch_nky<2>(p, t, in_map, stream);
+    case 3: return dispatch_nky<3>(p, t, in_map, stream);
+    default: return dispatch_nky<4>(p, t, in_map, stream);
   }
 }
 

@@ -92,7 +92,8 @@ template <typename T> int launch_direct(const DirectProblem<T> &p, cudaStream_t 
 // (MELLIN_ERR_UNSUPPORTED when the problem is outside its coverage), and the
 // device-side timeout flag
 // few-output-channel kernel (direct_rows.cu); MELLIN_ERR_UNSUPPORTED when not covered
-int launch_direct_rows(const DirectProblem<float> &p, cudaStream_t stream);
+size_t direct_rows_workspace_bytes(const DirectProblem<float> &p);
+int launch_direct_rows(const DirectProblem<float> &p, void *workspace, size_t workspace_bytes, cudaStream_t stream);
 size_t direct_tc_workspace_bytes(const DirectProblem<float> &p);
 int launch_direct_tc(const DirectProblem<float> &p, void *workspace, size_t workspace_bytes, cudaStream_t stream);
 int tc_take_error(int *code);
