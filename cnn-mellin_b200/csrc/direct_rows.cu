@@ -30,10 +30,9 @@ namespace {
 
 constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
-constexpr int kRY = 8;                 // positions per lane
-constexpr int kLanes = 30;             // lanes that own positions (a staged row must fit a 256-element TMA box)
-constexpr int kTY = kLanes * kRY;      // positions per block: 240
-constexpr int kRowFloats = 256;        // staged row: tile + taps (<= 4) + alignment lead (<= 3) <= 256
+constexpr int kRY = 8;                 // positions per lane: two groups of 4 consecutive ones, 128 apart
+constexpr int kTY = 240;               // output positions per block (a staged row must fit a 256-element TMA box)
+constexpr int kRowFloats = 256;        // staged row: 240 positions + taps (<= 4) + tile shift (<= 3), rounded to the box
 constexpr int kGroup = 4;              // consecutive reduced channels fetched by one TMA box
 constexpr int kSlotFloats = kGroup * kRowFloats;
 constexpr int kStages = 2;
@@ -42,6 +41,7 @@ constexpr int kRedPitch = 256;
 struct RowsPlan {
   int y_tiles = 0;
   int ws0 = 0;     // first input position of tile 0 relative to its first output position
+  int shift = 0;   // tiles start at output position yt * 240 - shift, which makes (tile start + ws0) a multiple of 4
   int WP = 0;      // floats per (kx, b) weight record: A * NKY rounded up to 4
   int vec_store = 0;
   int w_floats = 0;        // weight records in shared memory, rounded up to 128 bytes
@@ -67,7 +67,7 @@ direct_rows_kernel(const DirectProblem<float> p, const RowsPlan t, const __grid_
   bid /= t.y_tiles;
   const int ox = bid % p.nox;
   const int n = bid / p.nox;
-  const int y0 = yt * kTY;
+  const int y0 = yt * kTY - t.shift;  // may be negative for the first tile: those outputs are masked
 
   if (tid == 0) {
     for (int w = 0; w < kWarps; ++w)
@@ -101,9 +101,7 @@ direct_rows_kernel(const DirectProblem<float> p, const RowsPlan t, const __grid_
 
   const int e0 = p.table.row_ptr[ox];
   const int np = p.table.row_ptr[ox + 1] - e0;
-  const int ws = y0 + t.ws0;
-  const int start = ws & ~3;  // 16-byte aligned copy origin (two's complement: floors negatives too)
-  const int lead = ws - start;
+  const int start = y0 + t.ws0;  // first staged input position: a multiple of 4 by construction
   float *my_ring = ring + (size_t)warp * kStages * kSlotFloats;
   const int groups = (p.B + kGroup - 1) / kGroup;
   const int per_entry = (groups - warp + kWarps - 1) / kWarps;  // channel groups this warp takes per entry
@@ -144,28 +142,36 @@ direct_rows_kernel(const DirectProblem<float> p, const RowsPlan t, const __grid_
     const bool ok = tc::mbar_wait(&slot_full[warp][item % kStages], (uint32_t)((item / kStages) & 1), 1u << 20);
     if (!__all_sync(0xffffffffu, ok)) break;
     const int b0 = kGroup * (warp + kWarps * ck);
-    if (lane < kLanes) {
 #pragma unroll
-      for (int r = 0; r < kGroup; ++r) {
-        if (b0 + r >= p.B) break;  // channels past the last were zero-filled by the copy; they have no weights
-        const float *row = my_ring + (item % kStages) * kSlotFloats + r * kRowFloats + lead + kRY * lane;
-        float xw[kWin];
+    for (int r = 0; r < kGroup; ++r) {
+      if (b0 + r >= p.B) break;  // channels past the last were zero-filled by the copy; they have no weights
+      const float *row = my_ring + (item % kStages) * kSlotFloats + r * kRowFloats + 4 * lane;
+      // two windows: positions 4*lane .. +3 and 128 + 4*lane .. +3, each followed by NKY - 1 more values
+      float xw[2][8];
 #pragma unroll
-        for (int j = 0; j < kWin; ++j) xw[j] = row[j];
-        const float4 *wrec = reinterpret_cast<const float4 *>(Ws + (size_t)(ckx * p.B + b0 + r) * WP);
-        float wv[WP];
-#pragma unroll
-        for (int i = 0; i < WP / 4; ++i) {
-          const float4 v = wrec[i];
-          wv[4 * i] = v.x, wv[4 * i + 1] = v.y, wv[4 * i + 2] = v.z, wv[4 * i + 3] = v.w;
+      for (int g = 0; g < 2; ++g) {
+        const float4 v0 = *reinterpret_cast<const float4 *>(row + 128 * g);
+        xw[g][0] = v0.x, xw[g][1] = v0.y, xw[g][2] = v0.z, xw[g][3] = v0.w;
+        if (NKY > 1) {
+          const float2 v1 = *reinterpret_cast<const float2 *>(row + 128 * g + 4);
+          xw[g][4] = v1.x, xw[g][5] = v1.y;
         }
-#pragma unroll
-        for (int a = 0; a < A; ++a)
-#pragma unroll
-          for (int k = 0; k < NKY; ++k)
-#pragma unroll
-            for (int j = 0; j < kRY; ++j) acc[a][j] = fmaf(wv[a * NKY + k], xw[j + k], acc[a][j]);
       }
+      const float4 *wrec = reinterpret_cast<const float4 *>(Ws + (size_t)(ckx * p.B + b0 + r) * WP);
+      float wv[WP];
+#pragma unroll
+      for (int i = 0; i < WP / 4; ++i) {
+        const float4 v = wrec[i];
+        wv[4 * i] = v.x, wv[4 * i + 1] = v.y, wv[4 * i + 2] = v.z, wv[4 * i + 3] = v.w;
+      }
+#pragma unroll
+      for (int a = 0; a < A; ++a)
+#pragma unroll
+        for (int k = 0; k < NKY; ++k)
+#pragma unroll
+          for (int g = 0; g < 2; ++g)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[a][4 * g + j] = fmaf(wv[a * NKY + k], xw[g][j + k], acc[a][4 * g + j]);
     }
     __syncwarp();
     if (++ck == per_entry) {
@@ -180,9 +186,9 @@ direct_rows_kernel(const DirectProblem<float> p, const RowsPlan t, const __grid_
   float *red = ring;
 #pragma unroll
   for (int a = 0; a < A; ++a) {
-    float4 *dst = reinterpret_cast<float4 *>(red + ((size_t)warp * A + a) * kRedPitch + kRY * lane);
-    dst[0] = make_float4(acc[a][0], acc[a][1], acc[a][2], acc[a][3]);
-    dst[1] = make_float4(acc[a][4], acc[a][5], acc[a][6], acc[a][7]);
+    float *dst = red + ((size_t)warp * A + a) * kRedPitch + 4 * lane;
+    *reinterpret_cast<float4 *>(dst) = make_float4(acc[a][0], acc[a][1], acc[a][2], acc[a][3]);
+    *reinterpret_cast<float4 *>(dst + 128) = make_float4(acc[a][4], acc[a][5], acc[a][6], acc[a][7]);
   }
   __syncthreads();
   for (int o = tid; o < A * (kTY / 4); o += kThreads) {
@@ -194,10 +200,10 @@ direct_rows_kernel(const DirectProblem<float> p, const RowsPlan t, const __grid_
       s.x += v.x, s.y += v.y, s.z += v.z, s.w += v.w;
     }
     const int y = y0 + pos;
-    if (y >= p.noy) continue;
+    if (y >= p.noy || y + 3 < 0) continue;
     float *out = p.out + n * p.out_sn + a * p.out_sa + (long long)ox * p.noy + y;
     const float bias = (!p.accumulate && p.bias != nullptr) ? __ldg(p.bias + a) : 0.f;
-    if (t.vec_store && y + 3 < p.noy) {
+    if (t.vec_store && y >= 0 && y + 3 < p.noy) {
       float4 *o4 = reinterpret_cast<float4 *>(out);
       if (p.accumulate) {
         const float4 old = *o4;
@@ -209,7 +215,7 @@ direct_rows_kernel(const DirectProblem<float> p, const RowsPlan t, const __grid_
     } else {
       const float v[4] = {s.x, s.y, s.z, s.w};
       for (int j = 0; j < 4; ++j)
-        if (y + j < p.noy) out[j] = (p.accumulate ? out[j] : bias) + v[j];
+        if (y + j >= 0 && y + j < p.noy) out[j] = (p.accumulate ? out[j] : bias) + v[j];
     }
   }
 }
@@ -222,9 +228,10 @@ bool plan_rows(const DirectProblem<float> &p, RowsPlan &t) {
   // rows are copied in 16-byte chunks
   if (p.niy % 4 != 0 || reinterpret_cast<uintptr_t>(p.in) % 16 != 0 || p.in_sn % 4 != 0 || p.in_sb % 4 != 0)
     return false;
-  t.y_tiles = (p.noy + kTY - 1) / kTY;
-  if ((long long)p.N * p.nox * t.y_tiles >= (1LL << 31)) return false;
   t.ws0 = p.Cy + std::min(0, p.By * (p.nky - 1));
+  t.shift = ((t.ws0 % 4) + 4) % 4;  // (-shift + ws0) is then a multiple of 4
+  t.y_tiles = (p.noy + t.shift + kTY - 1) / kTY;
+  if ((long long)p.N * p.nox * t.y_tiles >= (1LL << 31)) return false;
   t.WP = (p.A * p.nky + 3) / 4 * 4;
   const size_t w_floats = ((size_t)p.nkx * p.B * t.WP + 31) / 32 * 32;
   t.w_floats = (int)w_floats;
@@ -232,8 +239,8 @@ bool plan_rows(const DirectProblem<float> &p, RowsPlan &t) {
   const size_t red_floats = (size_t)kWarps * p.A * kRedPitch;
   t.smem = (w_floats + std::max(ring_floats, red_floats)) * sizeof(float) + 128;  // + slack to align the base
   if (t.smem > 100 * 1024) return false;
-  t.vec_store = (reinterpret_cast<uintptr_t>(p.out) % 16 == 0 && p.noy % 4 == 0 && p.out_sn % 4 == 0 &&
-                 p.out_sa % 4 == 0)
+  t.vec_store = (t.shift == 0 && reinterpret_cast<uintptr_t>(p.out) % 16 == 0 && p.noy % 4 == 0 &&
+                 p.out_sn % 4 == 0 && p.out_sa % 4 == 0)
                     ? 1
                     : 0;
   return true;
