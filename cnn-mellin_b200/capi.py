@@ -27,7 +27,7 @@ COL2D = ["mellin_spec2col", "mellin_col2spec"]
 LAYER = ["mellin_mcorrlcorr_forward", "mellin_mcorrlcorr_grad_input", "mellin_mcorrlcorr_grad_weight"]
 MISC = ["mellin_abi_version", "mellin_last_error", "mellin_launch_count", "mellin_clear_tables",
         "mellin_set_tensor_cores", "mellin_device_status", "mellin_mcorrlcorr_forward_workspace_bytes",
-        "mellin_mcorrlcorr_grad_input_workspace_bytes",
+        "mellin_mcorrlcorr_grad_input_workspace_bytes", "mellin_mcorrlcorr_grad_weight_noalloc_f32",
         "mellin_mcorrlcorr_grad_weight_workspace_bytes", "mellin_index_map_build"]
 
 
@@ -215,6 +215,14 @@ def grad_input(w, grad_y, grad_x, s, d, p, u, workspace=None):
     fn = getattr(lib(), "mellin_mcorrlcorr_grad_input" + _sfx(grad_x))
     _check(fn(_p(w), _p(grad_y), *geom, _p(grad_x), _p(workspace), ctypes.c_size_t(nbytes), _stream()))
     return grad_x
+
+
+def grad_weight_noalloc(x, grad_y, grad_w, grad_b, s, d, p, u):
+    """grad_weight through the entry point that owns its scratch (float32 only)."""
+    geom = _geometry(x.shape, grad_w.shape, grad_y.shape, s, d, p, u)
+    fn = lib().mellin_mcorrlcorr_grad_weight_noalloc_f32
+    _check(fn(_p(x), _p(grad_y), *geom, _p(grad_w), _p(grad_b), _stream()))
+    return grad_w, grad_b
 
 
 def grad_weight_workspace_bytes(x_shape, w_shape, y_shape, s, d, p, u):

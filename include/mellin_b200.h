@@ -176,6 +176,19 @@ int mellin_mcorrlcorr_grad_weight_f64(const double *x, const double *grad_y,
                                       MELLIN_LAYER_GEOMETRY, double *grad_w, double *grad_b,
                                       void *workspace, size_t workspace_bytes, void *stream);
 
+/* No counterpart in the reference: grad_weight (+ grad_b) for callers that may
+ * not allocate device memory -- inside a stream capture, under a framework that
+ * forbids allocation in backward, in a plugin with a fixed arena.  Scratch and
+ * index tables live in a fixed 8.25 MiB array inside the library image (held by
+ * every GPU that loads the library); nothing is allocated, by this call or for
+ * it.  Geometries whose partial sums exceed 8 MiB are rejected
+ * (MELLIN_ERR_WORKSPACE).  The first call on a device resolves the array's
+ * address: make it before any stream capture.  All calls share the array, so
+ * calls that overlap on the GPU race; serialise them.  Results are identical to
+ * mellin_mcorrlcorr_grad_weight_f32. */
+int mellin_mcorrlcorr_grad_weight_noalloc_f32(const float *x, const float *grad_y, MELLIN_LAYER_GEOMETRY,
+                                              float *grad_w, float *grad_b, void *stream);
+
 /* ---- diagnostics ------------------------------------------------------------ */
 
 /* Number of kernels this library has launched from the calling process since
