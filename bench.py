@@ -215,6 +215,7 @@ def run_ours(args):
     import torch.distributed as dist
 
     import capi
+    import dp
     import mconv
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -245,9 +246,12 @@ def run_ours(args):
     gx = torch.empty_like(x)
     gw = torch.empty_like(w)
     gb = torch.empty_like(b)
-    grads_flat = torch.empty(gw.numel() + gb.numel(), device=dev)
+    bucket = dp.GradBucket([ws, (ws[0],)], device=dev)
+    grads_flat = bucket.flat
     ws_bytes = capi.grad_weight_workspace_bytes(xs, ws, ys, s, d, p, u)
     workspace = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
+    ws_fwd = torch.empty(max(capi.forward_workspace_bytes(xs, ws, ys, s, d, p, u), 256), dtype=torch.uint8, device=dev)
+    ws_gin = torch.empty(max(capi.grad_input_workspace_bytes(xs, ws, ys, s, d, p, u), 256), dtype=torch.uint8, device=dev)
     flush = torch.empty(192 * 1024 * 1024, dtype=torch.uint8, device=dev)  # > 126 MB of L2
 
     def ev():
@@ -256,19 +260,18 @@ def run_ours(args):
     def step(events=None):
         if events:
             events[0].record()
-        capi.forward(x, w, b, y, s, d, p, u)
+        capi.forward(x, w, b, y, s, d, p, u, workspace=ws_fwd)
         if events:
             events[1].record()
-        capi.grad_input(w, go, gx, s, d, p, u)
+        capi.grad_input(w, go, gx, s, d, p, u, workspace=ws_gin)
         if events:
             events[2].record()
         capi.grad_weight(x, go, gw, gb, s, d, p, u, workspace=workspace)
         if events:
             events[3].record()
         if world > 1:
-            grads_flat[: gw.numel()].copy_(gw.view(-1))
-            grads_flat[gw.numel():].copy_(gb)
-            dist.all_reduce(grads_flat)
+            bucket.pack([gw, gb])
+            bucket.all_reduce()
         if events:
             events[4].record()
 
@@ -330,9 +333,8 @@ def run_ours(args):
         layer.bias.grad = None
         out.backward(go)
         if world > 1:
-            grads_flat[: gw.numel()].copy_(layer.weight.grad.view(-1))
-            grads_flat[gw.numel():].copy_(layer.bias.grad)
-            dist.all_reduce(grads_flat)
+            bucket.pack([layer.weight.grad, layer.bias.grad])
+            bucket.all_reduce()
             gw_host.copy_(grads_flat[: gw.numel()].view(ws), non_blocking=True)
             gb_host.copy_(grads_flat[gw.numel():], non_blocking=True)
         else:
