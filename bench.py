@@ -397,8 +397,9 @@ def run_ours(args):
                            "weight and bias gradients read back; upstream gradient resident on the device"},
             "gpu_launches": launches,
             "clocks": clocks,
-            "cpu_baseline": cpu_baseline_leg(),
         }
+        if world == 1:
+            line["cpu_baseline"] = cpu_baseline_leg()  # timed on rank 0 of the single-GPU run only
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
