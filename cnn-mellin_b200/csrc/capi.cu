@@ -290,7 +290,12 @@ int mellin_debug_tc_prof(long long *out) { return mellin::tc_read_prof(out); }
 int mellin_set_tensor_cores(int enable) { return set_tensor_cores(enable); }
 int mellin_device_status(int *code) {
   if (code == nullptr) return fail(MELLIN_ERR_BAD_ARGUMENT, "device_status: null pointer");
-  return tc_take_error(code);
+  int rc = tc_take_error(code);
+  if (rc) return rc;
+  int gw_code = 0;
+  rc = tc_gradw_take_error(&gw_code);
+  if (rc == MELLIN_OK && *code == 0 && gw_code != 0) *code = 100 + gw_code;
+  return rc;
 }
 
 // Workspace queries plan with the extents only (tables are not needed: the

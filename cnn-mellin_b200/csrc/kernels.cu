@@ -781,7 +781,7 @@ int launch_direct<double>(const DirectProblem<double> &p, cudaStream_t stream) {
 
 template <>
 size_t gradw_workspace_bytes<float>(const GradWProblem<float> &p) {
-  const size_t rows = gradw_rows_workspace_floats(p, nullptr) * sizeof(float);
+  const size_t rows = std::max(gradw_rows_workspace_floats(p, nullptr), gradw_tc_workspace_floats(p, nullptr)) * sizeof(float);
   GradWTiling t;
   int RM = 0, RN = 0;
   if (!plan_gradw(p, t, RM, RN)) return rows;
@@ -821,6 +821,17 @@ int launch_gradw<float>(const GradWProblem<float> &p, void *workspace, size_t wo
         }
         return rc;
       }
+    }
+  }
+  if (tensor_cores_enabled()) {
+    // wide layers: positions are the reduction axis of a tensor-core GEMM
+    size_t tc_bias_off = 0;
+    const size_t tc_need = gradw_tc_workspace_floats(p, &tc_bias_off) * sizeof(float);
+    if (tc_need > 0 && workspace != nullptr && workspace_bytes >= tc_need) {
+      float *pw = static_cast<float *>(workspace);
+      float *pb = p.gb != nullptr ? pw + tc_bias_off : nullptr;
+      const int rc = launch_gradw_tc(p, pw, pb, stream);
+      if (rc != MELLIN_ERR_UNSUPPORTED) return rc;
     }
   }
   GradWTiling t;

@@ -97,6 +97,11 @@ int launch_direct_rows(const DirectProblem<float> &p, void *workspace, size_t wo
 size_t direct_tc_workspace_bytes(const DirectProblem<float> &p);
 int launch_direct_tc(const DirectProblem<float> &p, void *workspace, size_t workspace_bytes, cudaStream_t stream);
 int tc_take_error(int *code);
+// tensor-core weight gradient for wide layers (tc_gradw.cu): floats of partial
+// sums (0 when not covered), launch, and the device-side timeout flag
+size_t gradw_tc_workspace_floats(const GradWProblem<float> &p, size_t *bias_offset);
+int launch_gradw_tc(const GradWProblem<float> &p, float *part_w, float *part_b, cudaStream_t stream);
+int tc_gradw_take_error(int *code);
 bool tensor_cores_enabled();
 int set_tensor_cores(int enable);
 template <typename T> size_t gradw_workspace_bytes(const GradWProblem<T> &p);

@@ -183,6 +183,11 @@ RANDOM_CASES = [
     (3, 2, 3, (8, 20), (3, 3), (1, 1), (1, 1), (2, 1), (2, 3), (2, 1)),   # u != 1: divisor on the linear axis
     (2, 6, 9, (1, 200), (1, 5), (1, 1), (1, 1), (0, 2), (1, 1), (0, 2)),  # linear correlation only
     (4, 5, 7, (300, 1), (16, 1), (1, 1), (1, 1), (0, 0), (1, 1), (100, 0)),  # 1-D Mellin
+    # wide layers whose linear extent is a multiple of 4: tensor-core weight gradient
+    (2, 64, 128, (41, 48), (6, 3), (1, 1), (2, 1), (0, 1), (1, 1), ("same", 1)),
+    (3, 20, 40, (12, 36), (3, 2), (1, 1), (1, 1), (0, 0), (1, 1), (2, 1)),       # partial channel tiles
+    (2, 70, 130, (10, 52), (4, 3), (1, 1), (1, 2), (0, 2), (1, 1), (1, 2)),      # two tiles each way, dilated taps
+    (1, 16, 32, (30, 200), (5, 1), (1, 1), (1, 1), (0, 0), (1, 1), ("same", 0)),  # one linear tap, long reduction
 ]
 
 
