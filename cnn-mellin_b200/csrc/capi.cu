@@ -11,6 +11,7 @@
 
 namespace mellin {
 int tc_read_prof(long long *out);
+int tc_gradw_read_prof(long long *out);
 const std::string &last_error();
 int64_t launch_count();
 }  // namespace mellin
@@ -287,6 +288,7 @@ DEFINE_OPS(float, f32)
 DEFINE_OPS(double, f64)
 
 int mellin_debug_tc_prof(long long *out) { return mellin::tc_read_prof(out); }
+int mellin_debug_tc_gradw_prof(long long *out) { return mellin::tc_gradw_read_prof(out); }
 int mellin_set_tensor_cores(int enable) { return set_tensor_cores(enable); }
 int mellin_device_status(int *code) {
   if (code == nullptr) return fail(MELLIN_ERR_BAD_ARGUMENT, "device_status: null pointer");

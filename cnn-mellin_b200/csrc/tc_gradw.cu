@@ -28,6 +28,7 @@
 // (each grad_y row is owned by exactly one table entry).
 #include <cuda.h>
 
+#include <cstdlib>
 #include <algorithm>
 #include <string>
 
@@ -40,15 +41,18 @@ namespace mellin {
 namespace {
 
 constexpr int kEpilogueWarps = 4;
-constexpr int kConvertWarps = 8;
-constexpr int kConvertThreads = kConvertWarps * 32;
+constexpr int kConvertGroups = 2;  // groups of converter warps take alternate stages
+constexpr int kGroupWarps = 8;
+constexpr int kConvertWarps = kConvertGroups * kGroupWarps;
+constexpr int kGroupThreads = kGroupWarps * 32;
 constexpr int kMmaWarp = kEpilogueWarps + kConvertWarps;
 constexpr int kCopyWarp = kMmaWarp + 1;
 constexpr int kThreads = (kCopyWarp + 1) * 32;
 constexpr int kTM = 128;       // output channels per block
 constexpr int kNB = 64;        // input channels per block
 constexpr int kKB = 16;        // positions per stage
-constexpr int kStages = 3;
+constexpr int kRawStages = 6;   // TMA boxes in flight (at most): deep, to cover the copy latency
+constexpr int kOpStages = 3;    // converted operand sets
 constexpr int kPromote = 8;    // stages per level-1 interval: 2 k-steps x 3 MMAs x 8 = 48 chained MMAs
 constexpr int kMaxRows = 16;   // Mellin taps
 constexpr int kMaxTaps = 3;
@@ -56,7 +60,10 @@ constexpr uint32_t kSpinLimit = 1u << 20;
 constexpr int kL2Col = 256;    // first TMEM column of the level-2 sums
 // Operand slabs: one per 4-position chunk, rows 16 bytes apart.  32 bytes of
 // padding between slabs spread the converters' 16-byte stores over all banks.
-constexpr uint32_t kGoSlab = kTM * 16 + 32, kXSlab = kNB * 16 + 32;
+// An x slab holds the rows of every linear tap, (tap, b): the taps are extra
+// columns of one MMA.
+constexpr uint32_t kGoSlab = kTM * 16 + 32;
+__host__ __device__ constexpr uint32_t x_slab(int nky) { return (uint32_t)(nky * kNB * 16 + 32); }
 
 struct GwParams {
   const int32_t *row_ptr;  // by-kx table
@@ -70,6 +77,8 @@ struct GwParams {
   int a_tiles, b_tiles;
   int target_slices;       // sum of Z[kx] aimed at
   int stages_per_row;      // ceil(noy / 16)
+  int profile;
+  int raw_stages;          // 3 .. kRawStages, as shared memory allows
   int chunks, chunk_stages;  // a row of positions is cut into `chunks` runs of at most `chunk_stages` stages
   uint32_t go_raw_bytes, x_raw_bytes, go_op_bytes, x_op_bytes;  // per stage; operand sizes per hi or lo part (x: per tap)
 };
@@ -92,15 +101,32 @@ __device__ void slice_prefix(const int32_t *row_ptr, int nkx, long long items_pe
   prefix[nkx] = acc;
 }
 
+constexpr int kHeaderBytes = 2048;  // Control, then the 128-byte aligned stages
+
 struct Control {
-  uint64_t raw_full[kStages], full[kStages], empty[kStages];
+  uint64_t raw_full[kRawStages], raw_empty[kRawStages], full[kOpStages], empty[kOpStages];
   uint64_t l1_full, l1_empty;
   uint32_t tmem_base;
   int abort;
   int prefix[kMaxRows + 1];
+  float bias[kConvertGroups][kTM];
 };
 
+static_assert(sizeof(Control) <= kHeaderBytes, "Control must fit the header");
+
 __device__ int g_gw_error = 0;
+__device__ long long g_gw_prof[16];  // per-role wait / work cycles of block 0 (written when profiling is on)
+
+#define PROF_BEGIN() long long prof_t0 = clock64(), prof_wait = 0, prof_t1 = 0
+#define PROF_WAIT_START() \
+  if (p.profile) prof_t1 = clock64()
+#define PROF_WAIT_END() \
+  if (p.profile) prof_wait += clock64() - prof_t1
+#define PROF_END(slot)                                           \
+  if (blockIdx.x == 0 && lane == 0 && p.profile) {               \
+    g_gw_prof[2 * (slot)] = prof_wait;                           \
+    g_gw_prof[2 * (slot) + 1] = clock64() - prof_t0 - prof_wait; \
+  }
 
 __device__ __forceinline__ float tf32_hi(float x) { return __uint_as_float(__float_as_uint(x) & 0xffffe000u); }
 __device__ __forceinline__ void raise_timeout(Control *ctl, int code) {
@@ -108,13 +134,16 @@ __device__ __forceinline__ void raise_timeout(Control *ctl, int code) {
   ctl->abort = 1;
 }
 
+template <int NKY>
 __global__ void __launch_bounds__(kThreads, 1)
 tc_gradw_kernel(const GwParams p, const __grid_constant__ CUtensorMap go_map, const __grid_constant__ CUtensorMap x_map) {
   extern __shared__ __align__(1024) unsigned char smem[];
   Control *ctl = reinterpret_cast<Control *>(smem);
-  unsigned char *stage_base = smem + 1024;
-  const uint32_t op_bytes = 2 * p.go_op_bytes + 2 * (uint32_t)p.nky * p.x_op_bytes;
-  const uint32_t stage_bytes = p.go_raw_bytes + p.x_raw_bytes + op_bytes;
+  unsigned char *raw_base = smem + kHeaderBytes;
+  constexpr uint32_t kXSlab = x_slab(NKY);
+  const uint32_t op_bytes = 2 * p.go_op_bytes + 2 * p.x_op_bytes;
+  const uint32_t raw_bytes = p.go_raw_bytes + p.x_raw_bytes;
+  unsigned char *op_base = raw_base + (size_t)p.raw_stages * raw_bytes;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
   // block -> (slice, channel tiles); slice -> (tap kx, split index z of Z)
@@ -138,9 +167,12 @@ tc_gradw_kernel(const GwParams p, const __grid_constant__ CUtensorMap go_map, co
 #define ITEM_END_STAGE(i) min(p.stages_per_row, ITEM_FIRST_STAGE(i) + p.chunk_stages)
 
   if (tid == 0) {
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < kRawStages; ++s) {
       tc::mbar_init(&ctl->raw_full[s], 1);
-      tc::mbar_init(&ctl->full[s], kConvertThreads);
+      tc::mbar_init(&ctl->raw_empty[s], kGroupThreads);
+    }
+    for (int s = 0; s < kOpStages; ++s) {
+      tc::mbar_init(&ctl->full[s], kGroupThreads);
       tc::mbar_init(&ctl->empty[s], 1);
     }
     tc::mbar_init(&ctl->l1_full, 1);
@@ -166,7 +198,7 @@ tc_gradw_kernel(const GwParams p, const __grid_constant__ CUtensorMap go_map, co
   if (warp < kEpilogueWarps) {
     // ===================== epilogue: level-1 -> level-2 promotion, final write =====================
     const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-    const int groups = p.nky * (kNB / 16);
+    constexpr int groups = NKY * (kNB / 16);
     {
       uint32_t zero[16];
 #pragma unroll
@@ -175,8 +207,11 @@ tc_gradw_kernel(const GwParams p, const __grid_constant__ CUtensorMap go_map, co
       tc::tmem_st_wait();
     }
     bool failed = false;
+    PROF_BEGIN();
     for (int iv = 0; iv < intervals && !failed; ++iv) {
+      PROF_WAIT_START();
       const bool ok = tc::mbar_wait(&ctl->l1_full, (uint32_t)(iv & 1), kSpinLimit);
+      PROF_WAIT_END();
       if (!__all_sync(0xffffffffu, ok)) {
         raise_timeout(ctl, 3);
         failed = true;
@@ -196,10 +231,11 @@ tc_gradw_kernel(const GwParams p, const __grid_constant__ CUtensorMap go_map, co
       tc::tc_fence_before_sync();
       tc::mbar_arrive(&ctl->l1_empty);
     }
+    if (warp == 0) { PROF_END(0); }
     if (!failed) {
       // partial sums of this block: row a = lane (consecutive addresses), columns (tap slot, b)
       const int a = at * kTM + warp * 32 + lane;
-      float *pw = p.part_w + (long long)slice * p.nky * p.B * p.A;
+      float *pw = p.part_w + (long long)slice * NKY * p.B * p.A;
       for (int g = 0; g < groups; ++g) {
         uint32_t v[16];
         tc::tmem_ld16(tmem_base + lane_base + (uint32_t)(kL2Col + 16 * g), v);
@@ -214,7 +250,8 @@ tc_gradw_kernel(const GwParams p, const __grid_constant__ CUtensorMap go_map, co
     }
   } else if (warp < kMmaWarp) {
     // ===================== converters =====================
-    const int ctid = tid - kEpilogueWarps * 32;
+    const int group = (warp - kEpilogueWarps) / kGroupWarps;
+    const int ctid = (tid - kEpilogueWarps * 32) % kGroupThreads;
     // grad_y items: (row, 4-position chunk); this thread: rows r0 and r0 + 64, chunk cg
     const int go_row = ctid >> 2, go_chunk = ctid & 3;
     // x items: (row, chunk): one per thread
@@ -222,24 +259,31 @@ tc_gradw_kernel(const GwParams p, const __grid_constant__ CUtensorMap go_map, co
     float bsum[2] = {0.f, 0.f};
     int it = 0;
     bool failed = false;
+    PROF_BEGIN();
     for (int i = z; i < items && !failed; i += Z) {
       const int flags = p.entries[ITEM_ENTRY(i)].x;
       const bool bias_only = (flags & kFlagBiasOnly) != 0;
       const bool add_bias = want_bias && (flags & kFlagBiasOwner) != 0;
       const int s_end = ITEM_END_STAGE(i);
       for (int sidx = ITEM_FIRST_STAGE(i); sidx < s_end; ++sidx, ++it) {
-        const int s = it % kStages;
-        if (!tc::mbar_wait(&ctl->raw_full[s], (uint32_t)((it / kStages) & 1), kSpinLimit)) {
+        if (it % kConvertGroups != group) continue;
+        const int r = it % p.raw_stages, s = it % kOpStages;
+        PROF_WAIT_START();
+        const bool raw_ok = tc::mbar_wait(&ctl->raw_full[r], (uint32_t)((it / p.raw_stages) & 1), kSpinLimit) &&
+                            tc::mbar_wait(&ctl->empty[s], (uint32_t)(((it / kOpStages) & 1) ^ 1), kSpinLimit);
+        PROF_WAIT_END();
+        if (!raw_ok) {
           raise_timeout(ctl, 1);
           failed = true;
           break;
         }
-        unsigned char *st = stage_base + (size_t)s * stage_bytes;
-        const float *raw_go = reinterpret_cast<const float *>(st);
-        const float *raw_x = reinterpret_cast<const float *>(st + p.go_raw_bytes);
-        float4 *go_hi = reinterpret_cast<float4 *>(st + p.go_raw_bytes + p.x_raw_bytes);
-        float4 *go_lo = reinterpret_cast<float4 *>(st + p.go_raw_bytes + p.x_raw_bytes + p.go_op_bytes);
-        unsigned char *x_ops = st + p.go_raw_bytes + p.x_raw_bytes + 2 * p.go_op_bytes;
+        const unsigned char *raw = raw_base + (size_t)r * raw_bytes;
+        unsigned char *ops = op_base + (size_t)s * op_bytes;
+        const float *raw_go = reinterpret_cast<const float *>(raw);
+        const float *raw_x = reinterpret_cast<const float *>(raw + p.go_raw_bytes);
+        float4 *go_hi = reinterpret_cast<float4 *>(ops);
+        float4 *go_lo = reinterpret_cast<float4 *>(ops + p.go_op_bytes);
+        unsigned char *x_ops = ops + 2 * p.go_op_bytes;
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
           const int row = go_row + 64 * k;
@@ -257,31 +301,45 @@ tc_gradw_kernel(const GwParams p, const __grid_constant__ CUtensorMap go_map, co
           const int xs = sidx * kKB + p.xs0;
           const int lead = xs & 3;
           const float *xr = raw_x + x_row * p.RXW + lead + 4 * x_chunk;
-          for (int t = 0; t < p.nky; ++t) {
-            const float *q = xr + t * p.absBy;
-            const float v0 = q[0], v1 = q[1], v2 = q[2], v3 = q[3];
+          float win[4 + NKY - 1];  // taps one position apart share a window
+          if (p.absBy == 1) {
+#pragma unroll
+            for (int k = 0; k < 4 + NKY - 1; ++k) win[k] = xr[k];
+          }
+#pragma unroll
+          for (int t = 0; t < NKY; ++t) {
+            float v0, v1, v2, v3;
+            if (p.absBy == 1) {
+              v0 = win[t], v1 = win[t + 1], v2 = win[t + 2], v3 = win[t + 3];
+            } else {
+              const float *q = xr + t * p.absBy;
+              v0 = q[0], v1 = q[1], v2 = q[2], v3 = q[3];
+            }
             float4 h, l;
             h.x = tf32_hi(v0), h.y = tf32_hi(v1), h.z = tf32_hi(v2), h.w = tf32_hi(v3);
             l.x = v0 - h.x, l.y = v1 - h.y, l.z = v2 - h.z, l.w = v3 - h.w;
-            float4 *x_hi = reinterpret_cast<float4 *>(x_ops + (size_t)(2 * t) * p.x_op_bytes);
-            float4 *x_lo = reinterpret_cast<float4 *>(x_ops + (size_t)(2 * t + 1) * p.x_op_bytes);
-            x_hi[x_chunk * (kXSlab / 16) + x_row] = h;
-            x_lo[x_chunk * (kXSlab / 16) + x_row] = l;
+            float4 *x_hi = reinterpret_cast<float4 *>(x_ops);
+            float4 *x_lo = reinterpret_cast<float4 *>(x_ops + p.x_op_bytes);
+            x_hi[x_chunk * (kXSlab / 16) + t * kNB + x_row] = h;
+            x_lo[x_chunk * (kXSlab / 16) + t * kNB + x_row] = l;
           }
         }
+        tc::mbar_arrive(&ctl->raw_empty[r]);
         tc::fence_proxy_async();
         tc::mbar_arrive(&ctl->full[s]);
       }
     }
+    if (warp == kEpilogueWarps) { PROF_END(1); }
+    if (warp == kEpilogueWarps + kGroupWarps) { PROF_END(4); }
     if (want_bias) {
-      // the four chunk threads of a row are adjacent lanes
+      // the four chunk threads of a row are adjacent lanes; each converter group
+      // writes its own slot, added after the block-wide barrier below
 #pragma unroll
       for (int k = 0; k < 2; ++k) {
         float v = bsum[k];
         v += __shfl_xor_sync(0xffffffffu, v, 1);
         v += __shfl_xor_sync(0xffffffffu, v, 2);
-        const int a = at * kTM + go_row + 64 * k;
-        if (go_chunk == 0 && a < p.A) p.part_b[(long long)slice * p.A + a] = v;
+        if (go_chunk == 0) ctl->bias[group][go_row + 64 * k] = v;
       }
     }
   } else if (warp == kCopyWarp) {
@@ -289,6 +347,7 @@ tc_gradw_kernel(const GwParams p, const __grid_constant__ CUtensorMap go_map, co
     if (lane == 0) {
       int it = 0;
       bool failed = false;
+      PROF_BEGIN();
       for (int i = z; i < items && !failed; i += Z) {
         const int n = i / (ne * p.chunks);
         const int2 e = p.entries[ITEM_ENTRY(i)];
@@ -296,13 +355,16 @@ tc_gradw_kernel(const GwParams p, const __grid_constant__ CUtensorMap go_map, co
         const int ox = e.x & kIndexMask;
         const int s_end = ITEM_END_STAGE(i);
         for (int sidx = ITEM_FIRST_STAGE(i); sidx < s_end; ++sidx, ++it) {
-          const int s = it % kStages;
-          if (!tc::mbar_wait(&ctl->empty[s], (uint32_t)(((it / kStages) & 1) ^ 1), kSpinLimit)) {
+          const int s = it % p.raw_stages;
+          PROF_WAIT_START();
+          const bool empty_ok = tc::mbar_wait(&ctl->raw_empty[s], (uint32_t)(((it / p.raw_stages) & 1) ^ 1), kSpinLimit);
+          PROF_WAIT_END();
+          if (!empty_ok) {
             raise_timeout(ctl, 5);
             failed = true;
             break;
           }
-          unsigned char *st = stage_base + (size_t)s * stage_bytes;
+          unsigned char *st = raw_base + (size_t)s * raw_bytes;
           tc::mbar_arrive_expect_tx(&ctl->raw_full[s], p.go_raw_bytes + (bias_only ? 0u : p.x_raw_bytes));
           tc::tma_load_4d(st, &go_map, sidx * kKB, ox, at * kTM, n, &ctl->raw_full[s]);
           if (!bias_only) {
@@ -311,22 +373,33 @@ tc_gradw_kernel(const GwParams p, const __grid_constant__ CUtensorMap go_map, co
           }
         }
       }
+      PROF_END(3);
     }
     __syncwarp();
   } else if (warp == kMmaWarp) {
     // ===================== MMA issuer =====================
     if (lane == 0) {
-      const uint32_t idesc = tc::idesc_tf32(kTM, kNB);
-      const uint32_t a_lbo = kGoSlab, b_lbo = kXSlab;
+      const uint32_t idesc = tc::idesc_tf32(kTM, NKY * kNB);  // the taps side by side in the columns
+      // descriptors of stage 0; a stage's are these plus its offset
+      const uint32_t ops0 = tc::smem_u32(op_base);
+      const uint64_t dgo_hi = tc::smem_desc(ops0, kGoSlab, 128u);
+      const uint64_t dgo_lo = tc::smem_desc(ops0 + p.go_op_bytes, kGoSlab, 128u);
+      const uint64_t dx_hi = tc::smem_desc(ops0 + 2 * p.go_op_bytes, kXSlab, 128u);
+      const uint64_t dx_lo = tc::smem_desc(ops0 + 2 * p.go_op_bytes + p.x_op_bytes, kXSlab, 128u);
       int it = 0, ms = 0;  // stages seen, stages with MMAs issued
-      uint32_t fresh = 0;  // bit t: the next MMA into tap t's level-1 accumulator overwrites it
+      uint32_t fresh = 0;  // 0: the next MMA overwrites the level-1 accumulators
       bool failed = false;
+      long long prof_l1 = 0;
+      PROF_BEGIN();
       for (int i = z; i < items && !failed; i += Z) {
         const bool bias_only = (p.entries[ITEM_ENTRY(i)].x & kFlagBiasOnly) != 0;
         const int s_end = ITEM_END_STAGE(i);
         for (int sidx = ITEM_FIRST_STAGE(i); sidx < s_end; ++sidx, ++it) {
-          const int s = it % kStages;
-          if (!tc::mbar_wait(&ctl->full[s], (uint32_t)((it / kStages) & 1), kSpinLimit)) {
+          const int s = it % kOpStages;
+          PROF_WAIT_START();
+          const bool full_ok = tc::mbar_wait(&ctl->full[s], (uint32_t)((it / kOpStages) & 1), kSpinLimit);
+          PROF_WAIT_END();
+          if (!full_ok) {
             raise_timeout(ctl, 4);
             failed = true;
             break;
@@ -335,7 +408,10 @@ tc_gradw_kernel(const GwParams p, const __grid_constant__ CUtensorMap go_map, co
             if (ms % kPromote == 0) {
               // a new level-1 interval: the epilogue must have drained the previous one
               const int iv = ms / kPromote;
-              if (!tc::mbar_wait(&ctl->l1_empty, (uint32_t)((iv & 1) ^ 1), kSpinLimit)) {
+              const long long l1_t0 = p.profile ? clock64() : 0;
+              const bool l1_ok = tc::mbar_wait(&ctl->l1_empty, (uint32_t)((iv & 1) ^ 1), kSpinLimit);
+              if (p.profile) prof_l1 += clock64() - l1_t0;
+              if (!l1_ok) {
                 raise_timeout(ctl, 2);
                 failed = true;
                 break;
@@ -343,28 +419,15 @@ tc_gradw_kernel(const GwParams p, const __grid_constant__ CUtensorMap go_map, co
               fresh = 0;
             }
             tc::tc_fence_after_sync();
-            const uint32_t st = tc::smem_u32(stage_base + (size_t)s * stage_bytes) + p.go_raw_bytes + p.x_raw_bytes;
-            const uint64_t dgo_hi = tc::smem_desc(st, a_lbo, 128u);
-            const uint64_t dgo_lo = tc::smem_desc(st + p.go_op_bytes, a_lbo, 128u);
-            const uint32_t xo = st + 2 * p.go_op_bytes;
+            const uint32_t soff = (uint32_t)s * (op_bytes >> 4);  // descriptor addresses count 16-byte units
 #pragma unroll
             for (int ks = 0; ks < kKB / 8; ++ks) {
-              // the three products of the hi/lo split, each round-robin over the taps'
-              // accumulators so that consecutive MMAs do not chain on one accumulator
-              const uint32_t ka = (uint32_t)(ks * 2 * (kGoSlab / 16)), kb = (uint32_t)(ks * 2 * (kXSlab / 16));
-              for (int t = 0; t < p.nky; ++t) {
-                const uint64_t dx_hi = tc::smem_desc(xo + (uint32_t)(2 * t) * p.x_op_bytes, b_lbo, 128u) + kb;
-                tc::mma_tf32(tmem_base + (uint32_t)(t * kNB), dgo_lo + ka, dx_hi, idesc, (fresh >> t) & 1u);
-              }
-              fresh = (1u << p.nky) - 1u;
-              for (int t = 0; t < p.nky; ++t) {
-                const uint64_t dx_lo = tc::smem_desc(xo + (uint32_t)(2 * t + 1) * p.x_op_bytes, b_lbo, 128u) + kb;
-                tc::mma_tf32(tmem_base + (uint32_t)(t * kNB), dgo_hi + ka, dx_lo, idesc, 1u);
-              }
-              for (int t = 0; t < p.nky; ++t) {
-                const uint64_t dx_hi = tc::smem_desc(xo + (uint32_t)(2 * t) * p.x_op_bytes, b_lbo, 128u) + kb;
-                tc::mma_tf32(tmem_base + (uint32_t)(t * kNB), dgo_hi + ka, dx_hi, idesc, 1u);
-              }
+              // the three products of the hi/lo split
+              const uint32_t ka = soff + (uint32_t)(ks * 2 * (kGoSlab / 16)), kb = soff + (uint32_t)(ks * 2 * (kXSlab / 16));
+              tc::mma_tf32(tmem_base, dgo_lo + ka, dx_hi + kb, idesc, fresh);
+              tc::mma_tf32(tmem_base, dgo_hi + ka, dx_lo + kb, idesc, 1u);
+              tc::mma_tf32(tmem_base, dgo_hi + ka, dx_hi + kb, idesc, 1u);
+              fresh = 1u;
             }
             ++ms;
           }
@@ -372,6 +435,8 @@ tc_gradw_kernel(const GwParams p, const __grid_constant__ CUtensorMap go_map, co
           if (!bias_only && (ms % kPromote == 0 || ms == mma_stages)) tc::tc_commit(&ctl->l1_full);
         }
       }
+      PROF_END(2);
+      if (blockIdx.x == 0 && p.profile) g_gw_prof[12] = prof_l1, g_gw_prof[13] = it;
     }
     __syncwarp();
   }
@@ -381,6 +446,12 @@ tc_gradw_kernel(const GwParams p, const __grid_constant__ CUtensorMap go_map, co
   if (warp == kMmaWarp) {
     tc::tc_fence_after_sync();
     tc::tmem_dealloc(tmem_base, 512u);
+  }
+  if (want_bias && tid < kTM && at * kTM + tid < p.A) {
+    float v = 0.f;
+#pragma unroll
+    for (int g = 0; g < kConvertGroups; ++g) v += ctl->bias[g][tid];
+    p.part_b[(long long)slice * p.A + at * kTM + tid] = v;
   }
 #undef ITEM_ENTRY
 #undef ITEM_FIRST_STAGE
@@ -444,6 +515,7 @@ bool plan_tc_gradw(const GradWProblem<float> &p, GwPlan &plan) {
       reinterpret_cast<uintptr_t>(p.in) % 16 != 0)
     return false;
   GwParams &q = plan.params;
+  q.profile = 0;
   q.row_ptr = p.table.row_ptr, q.entries = p.table.entries;
   q.N = p.N, q.A = p.A, q.B = p.B, q.nkx = p.nkx, q.nky = p.nky, q.noy = p.noy;
   q.absBy = absBy, q.By = p.By;
@@ -459,9 +531,11 @@ bool plan_tc_gradw(const GradWProblem<float> &p, GwPlan &plan) {
   q.go_raw_bytes = kTM * kKB * 4;
   q.x_raw_bytes = (uint32_t)((kNB * q.RXW * 4 + 127) / 128 * 128);
   q.go_op_bytes = (kKB / 4) * kGoSlab;
-  q.x_op_bytes = (kKB / 4) * kXSlab;
-  const size_t stage = q.go_raw_bytes + q.x_raw_bytes + 2 * q.go_op_bytes + 2 * (size_t)p.nky * q.x_op_bytes;
-  plan.smem = 1024 + kStages * stage;
+  q.x_op_bytes = (kKB / 4) * x_slab(p.nky);
+  const size_t fixed = kHeaderBytes + (size_t)kOpStages * (2 * q.go_op_bytes + 2 * (size_t)q.x_op_bytes);
+  q.raw_stages = kRawStages;
+  while (q.raw_stages > 3 && fixed + (size_t)q.raw_stages * (q.go_raw_bytes + q.x_raw_bytes) > 227 * 1024) --q.raw_stages;
+  plan.smem = fixed + (size_t)q.raw_stages * (q.go_raw_bytes + q.x_raw_bytes);
   plan.smem = std::max<size_t>(plan.smem, 116 * 1024);  // one block per SM: it owns all 512 TMEM columns
   if (plan.smem > 227 * 1024) return false;
   // sum of Z[kx] <= target + 2 nkx whatever the rounding does
@@ -519,10 +593,13 @@ int launch_gradw_tc(const GradWProblem<float> &p, float *part_w, float *part_b, 
       !make_map(&x_map, p.in, p.niy, p.nix, p.B, p.N, plan.params.RXW, kNB))
     return MELLIN_ERR_UNSUPPORTED;
   plan.params.part_w = part_w;
+  const char *prof = getenv("MELLIN_TC_PROFILE");
+  plan.params.profile = (prof != nullptr && prof[0] == '1') ? 1 : 0;
   plan.params.part_b = part_b;
-  cudaError_t err = cudaFuncSetAttribute(tc_gradw_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem);
+  auto kernel = p.nky == 1 ? tc_gradw_kernel<1> : p.nky == 2 ? tc_gradw_kernel<2> : tc_gradw_kernel<3>;
+  cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem);
   if (err != cudaSuccess) return fail(MELLIN_ERR_LAUNCH, std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(err));
-  tc_gradw_kernel<<<plan.blocks, kThreads, plan.smem, stream>>>(plan.params, go_map, x_map);
+  kernel<<<plan.blocks, kThreads, plan.smem, stream>>>(plan.params, go_map, x_map);
   err = cudaGetLastError();
   if (err != cudaSuccess) return fail(MELLIN_ERR_LAUNCH, std::string("tc_gradw_kernel: ") + cudaGetErrorString(err));
   count_launch();
@@ -533,6 +610,10 @@ int launch_gradw_tc(const GradWProblem<float> &p, float *part_w, float *part_b, 
   if (err != cudaSuccess) return fail(MELLIN_ERR_LAUNCH, std::string("tc_gradw_reduce_kernel: ") + cudaGetErrorString(err));
   count_launch();
   return MELLIN_OK;
+}
+
+int tc_gradw_read_prof(long long *out) {
+  return cudaMemcpyFromSymbol(out, g_gw_prof, 16 * sizeof(long long)) == cudaSuccess ? 0 : 2;
 }
 
 int tc_gradw_take_error(int *code) {
