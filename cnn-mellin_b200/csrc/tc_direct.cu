@@ -75,14 +75,15 @@ __device__ long long g_tc_prof[16];  // per-role wait / work cycles of block 0 (
 struct TcParams {
   const float *bias;
   float *out;
-  const float *w_hi;  // packed [kx][tap][b / 4][NP * a_tiles][b % 4]
+  const float *w_hi;  // packed [a tile][kx][tap][b / 4][NP][b % 4]
   const float *w_lo;
   const int32_t *row_ptr;
   const int2 *entries;
+  const int32_t *order;  // table rows, most entries first
   int num_entries;
   int N, A, B;
   int Bp;        // B rounded up to a multiple of 4: rows per table entry
-  int nky, nox, noy;
+  int nkx, nky, nox, noy;
   long long out_sn, out_sa;
   int absBy;     // |By|: positions between consecutive taps
   int ws0;       // first input position of tile 0: Cy + min(0, By * (nky - 1))
@@ -92,6 +93,9 @@ struct TcParams {
   int RWt;       // positions copied per raw row: RW + 4 (room for the 16-byte alignment lead)
   int raw_chunk_floats;  // pitch of a raw 4-row chunk in shared memory (128-byte aligned); its rows are RWt apart
   int KB;        // rows per stage (multiple of 8)
+  int PI;        // stages per accumulation interval: PI * KB / 8 * 3 * nky <= 96 chained MMAs
+  int wide_box;  // 1: one TMA box brings all KB rows of a stage (they belong to one table entry)
+  int kblock_pack;  // 1: weights packed stage by stage, [a tile][kx][b / KB][hi, lo][tap][(b % KB) / 4][NP][b % 4]
   int stages;
   int y_tiles;
   int tiles;
@@ -108,23 +112,54 @@ __device__ __forceinline__ float tf32_hi(float x) { return __uint_as_float(__flo
 
 // ---- weight packing ---------------------------------------------------------------
 // W[a, b, kx, ky] (arbitrary a / b strides) -> hi and lo parts laid out
-// [kx][tap][b / 4][NP_total][b % 4]: 16-byte chunks of 4 consecutive reduced
+// [a tile][kx][tap][b / 4][NP][b % 4]: 16-byte chunks of 4 consecutive reduced
 // channels for one output channel, tap slots in increasing input-offset order,
 // output channels beyond A and reduced channels beyond B zero-filled.
 __global__ void pack_weights_kernel(const float *__restrict__ w, long long w_sa, long long w_sb, int A, int B, int nkx,
-                                    int nky, int NP_total, int By, float *__restrict__ hi, float *__restrict__ lo) {
+                                    int nky, int NP, int a_tiles, int By, int KB, float *__restrict__ hi,
+                                    float *__restrict__ lo) {
   const int B4 = (B + 3) / 4;
-  const long long total = (long long)nkx * nky * B4 * NP_total * 4;
+  if (KB > 0) {
+    // stage-by-stage layout: [a tile][kx][b / KB][hi, lo][tap][(b % KB) / 4][NP][b % 4] in `hi`
+    const int blocks_b = B4 * 4 / KB, C = KB / 4;
+    const long long total = (long long)a_tiles * nkx * blocks_b * 2 * nky * C * NP * 4;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+      const int bl = (int)(i & 3);
+      long long r = i >> 2;
+      int a = (int)(r % NP);
+      r /= NP;
+      const int c = (int)(r % C);
+      r /= C;
+      const int t = (int)(r % nky);
+      r /= nky;
+      const int part = (int)(r & 1);
+      r >>= 1;
+      const int b = ((int)(r % blocks_b) * C + c) * 4 + bl;
+      r /= blocks_b;
+      const int kx = (int)(r % nkx);
+      a += (int)(r / nkx) * NP;
+      const int ky = By < 0 ? nky - 1 - t : t;
+      float v = 0.f;
+      if (a < A && b < B) v = w[a * w_sa + b * w_sb + (long long)kx * nky + ky];
+      const float h = tf32_hi(v);
+      hi[i] = part ? v - h : h;
+    }
+    return;
+  }
+  const long long total = (long long)a_tiles * nkx * nky * B4 * NP * 4;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
     const int bl = (int)(i & 3);
     long long r = i >> 2;
-    const int a = (int)(r % NP_total);
-    r /= NP_total;
+    int a = (int)(r % NP);
+    r /= NP;
     const int b = (int)(r % B4) * 4 + bl;
     r /= B4;
     const int t = (int)(r % nky);
-    const int kx = (int)(r / nky);
+    r /= nky;
+    const int kx = (int)(r % nkx);
+    a += (int)(r / nkx) * NP;
     const int ky = By < 0 ? nky - 1 - t : t;
     float v = 0.f;
     if (a < A && b < B) v = w[a * w_sa + b * w_sb + (long long)kx * nky + ky];
@@ -151,7 +186,8 @@ constexpr uint32_t kBiasOffset = kEntriesOffset + kMaxTableEntries * 8;
 constexpr int kMaxKSteps = 1024;      // k-steps (8 rows) over all table rows, resident-weight mode
 constexpr uint32_t kKOfsOffset = kBiasOffset + kMaxBias * 4;             // int[kMaxTableRows + 1]
 constexpr uint32_t kKStepOffset = kKOfsOffset + (kMaxTableRows + 1) * 4 + 4;  // uint2[kMaxKSteps], 8-byte aligned
-constexpr uint32_t kStageOffset = (kKStepOffset + kMaxKSteps * 8 + 1023) / 1024 * 1024;
+constexpr uint32_t kOrderOffset = kKStepOffset + kMaxKSteps * 8;  // int[kMaxTableRows]
+constexpr uint32_t kStageOffset = (kOrderOffset + kMaxTableRows * 4 + 1023) / 1024 * 1024;
 
 __device__ __forceinline__ void raise_timeout(TcControl *ctl, int code) {
   atomicCAS(&g_tc_error, 0, code);
@@ -161,35 +197,59 @@ __device__ __forceinline__ void raise_timeout(TcControl *ctl, int code) {
 // Tile coordinates of a block: tile = blockIdx.x + i * gridDim.x, decoded once
 // and then advanced by the (decoded) grid stride with carries -- no divisions
 // in the steady state.
+// Tiles in heaviest-row-first order, ((rank, n), yt, at) with at fastest, dealt to the blocks in alternating
+// direction (block b takes b, 2G-1-b, 2G+b, ...): the rows of the Mellin table
+// differ several-fold in their number of entries, and this keeps the blocks'
+// total work within about one tile of each other.  The tiles of one row are
+// adjacent in the order, so blocks that run together share its weights in L2.
 struct TileWalker {
-  int n, ox, yt, at;     // current tile
-  int sn, sox, syt, sat; // grid stride, decoded
-  int tile;
-  __device__ __forceinline__ void init(const TcParams &p) {
+  int n, ox, yt, at;  // current tile
+  int rank;           // of its row in the heaviest-first order
+  int tile;           // its place in the order; >= p.tiles when the block is done
+  int step, step_after;          // tiles to the next round's tile, and from that one to the round after
+  int dat, dyt, dn, drank;       // `step` as digits (at, yt, n, rank): next() adds with carries, no divisions
+  int eat, eyt, en, erank;       // `step_after` as digits; the two swap every round
+  const int *order_s;
+  __device__ __forceinline__ static void digits(const TcParams &p, int t, int &a, int &y, int &nn, int &r) {
+    a = t % p.a_tiles, t /= p.a_tiles;
+    y = t % p.y_tiles, t /= p.y_tiles;
+    nn = t % p.N;
+    r = t / p.N;
+  }
+  __device__ __forceinline__ void init(const TcParams &p, const int *order_smem) {
+    order_s = order_smem;
     tile = blockIdx.x;
-    int t = tile;
-    at = t % p.a_tiles, t /= p.a_tiles;
-    yt = t % p.y_tiles, t /= p.y_tiles;
-    ox = t % p.nox, n = t / p.nox;
-    t = gridDim.x;
-    sat = t % p.a_tiles, t /= p.a_tiles;
-    syt = t % p.y_tiles, t /= p.y_tiles;
-    sox = t % p.nox, sn = t / p.nox;
+    digits(p, tile, at, yt, n, rank);
+    ox = rank < p.nox ? order_s[rank] : 0;
+    step = 2 * (int)gridDim.x - 1 - 2 * (int)blockIdx.x;
+    step_after = 2 * (int)blockIdx.x + 1;
+    digits(p, step, dat, dyt, dn, drank);
+    digits(p, step_after, eat, eyt, en, erank);
   }
   __device__ __forceinline__ void next(const TcParams &p) {
-    tile += gridDim.x;
-    at += sat;
+    tile += step;
+    at += dat;
     int carry = at >= p.a_tiles;
     at -= carry ? p.a_tiles : 0;
-    yt += syt + carry;
+    yt += dyt + carry;
     carry = yt >= p.y_tiles;
     yt -= carry ? p.y_tiles : 0;
-    ox += sox + carry;
-    carry = ox >= p.nox;
-    ox -= carry ? p.nox : 0;
-    n += sn + carry;
+    n += dn + carry;
+    carry = n >= p.N;
+    n -= carry ? p.N : 0;
+    rank += drank + carry;
+    ox = rank < p.nox ? order_s[rank] : 0;
+    int t;
+    t = step, step = step_after, step_after = t;
+    t = dat, dat = eat, eat = t;
+    t = dyt, dyt = eyt, eyt = t;
+    t = dn, dn = en, en = t;
+    t = drank, drank = erank, erank = t;
   }
 };
+
+// position in the stage ring: slot and number of completed laps
+#define RING_NEXT() (++ring_s == p.stages ? (ring_s = 0, ++ring_use) : 0u)
 
 #define PROF_BEGIN() long long prof_t0 = clock64(), prof_wait = 0, prof_t1 = 0
 #define PROF_WAIT_START() prof_t1 = clock64()
@@ -203,10 +263,12 @@ struct TileWalker {
 // NPC: padded output channels per tile / 16 (the epilogue keeps 16 * NPC running sums per thread)
 template <int NPC>
 __global__ void __launch_bounds__(kThreads, 1)
-tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map) {
+tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map,
+                 const __grid_constant__ CUtensorMap in_map_wide) {
   extern __shared__ __align__(1024) unsigned char smem[];
   TcControl *ctl = reinterpret_cast<TcControl *>(smem);
   int *rowptr_s = reinterpret_cast<int *>(smem + kRowPtrOffset);
+  int *order_s = reinterpret_cast<int *>(smem + kOrderOffset);
   int2 *ent_s = reinterpret_cast<int2 *>(smem + kEntriesOffset);
   float *bias_s = reinterpret_cast<float *>(smem + kBiasOffset);
   int *kofs_s = reinterpret_cast<int *>(smem + kKOfsOffset);        // first k-step of every table row
@@ -220,9 +282,11 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map) {
   const int JB = p.KB >> 3;
   const int NPtot = p.NP * p.a_tiles;
   const int B4 = p.Bp >> 2;
+  const int tile_chunks = p.nkx * p.nky * B4 * p.NP;  // 16-byte chunks of one output-channel tile's weights
 
   // ---- one-time set-up ------------------------------------------------------------
   for (int i = tid; i <= p.nox; i += kThreads) rowptr_s[i] = p.row_ptr[i];
+  for (int i = tid; i < p.nox; i += kThreads) order_s[i] = p.order[i];
   for (int i = tid; i < p.num_entries; i += kThreads) ent_s[i] = p.entries[i];
   for (int i = tid; i < NPtot; i += kThreads) bias_s[i] = (p.bias != nullptr && i < p.A) ? p.bias[i] : 0.f;
   {
@@ -279,9 +343,9 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map) {
       const int chunks = (rowptr_s[ox + 1] - e0) * B4;
       for (int j = lane; 2 * j < chunks; j += 32) {
         const int q0 = 2 * j, pp0 = q0 / B4, pp1 = (q0 + 1) / B4;
-        const uint32_t c0 = (uint32_t)((ent_s[e0 + pp0].x * p.nky * B4 + (q0 - pp0 * B4)) * NPtot);
+        const uint32_t c0 = (uint32_t)((ent_s[e0 + pp0].x * p.nky * B4 + (q0 - pp0 * B4)) * p.NP);
         uint32_t c1 = c0 + (uint32_t)p.NP;
-        if (q0 + 1 < chunks) c1 = (uint32_t)((ent_s[e0 + pp1].x * p.nky * B4 + (q0 + 1 - pp1 * B4)) * NPtot);
+        if (q0 + 1 < chunks) c1 = (uint32_t)((ent_s[e0 + pp1].x * p.nky * B4 + (q0 + 1 - pp1 * B4)) * p.NP);
         kstep_s[kofs_s[ox] + j] = make_uint2(c0, c1 - c0);
       }
     }
@@ -290,10 +354,10 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map) {
 
   if (warp < kEpilogueWarps) {
     // =========================== epilogue ===========================
-    int g = 0;  // K-blocks (accumulation intervals) consumed so far
+    int g = 0;  // accumulation intervals consumed so far
     PROF_BEGIN();
     TileWalker tc_;
-    for (tc_.init(p); tc_.tile < p.tiles; tc_.next(p)) {
+    for (tc_.init(p, order_s); tc_.tile < p.tiles; tc_.next(p)) {
       // tcgen05.ld is warp-collective: keep every exit decision warp-uniform
       if (__any_sync(0xffffffffu, *abort_flag)) break;
       const int Kr = (rowptr_s[tc_.ox + 1] - rowptr_s[tc_.ox]) * p.Bp;
@@ -308,7 +372,7 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map) {
           sum[c][4 * i4] = b.x, sum[c][4 * i4 + 1] = b.y, sum[c][4 * i4 + 2] = b.z, sum[c][4 * i4 + 3] = b.w;
         }
       bool failed = false;
-      for (int k0 = 0; k0 < Kr; k0 += p.KB, ++g) {
+      for (int k0 = 0; k0 < Kr; k0 += p.KB * p.PI, ++g) {
         const int acc = g & 1;
         PROF_WAIT_START();
         const bool ok = tc::mbar_wait(&ctl->dfull[acc], (uint32_t)((g >> 1) & 1), kSpinLimit);
@@ -356,16 +420,17 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map) {
   } else if (warp < kMmaWarp) {
     // =========================== converters ===========================
     const int pwarp = warp - kEpilogueWarps;
-    int it = 0;
+    int it = 0, ring_s = 0;
+    uint32_t ring_use = 0;
     bool failed = false;
     PROF_BEGIN();
     TileWalker tc_;
-    for (tc_.init(p); tc_.tile < p.tiles && !*abort_flag && !failed; tc_.next(p)) {
+    for (tc_.init(p, order_s); tc_.tile < p.tiles && !*abort_flag && !failed; tc_.next(p)) {
       const int Kr = (rowptr_s[tc_.ox + 1] - rowptr_s[tc_.ox]) * p.Bp;
       const int lead = (tc_.yt * kTileM + p.ws0) & 3;  // the copy started at the 16-byte boundary below
-      for (int k0 = 0; k0 < Kr; k0 += p.KB, ++it) {
-        const int s = it % p.stages;
-        const uint32_t use = (uint32_t)(it / p.stages);
+      for (int k0 = 0; k0 < Kr; k0 += p.KB, ++it, RING_NEXT()) {
+        const int s = ring_s;
+        const uint32_t use = ring_use;
         PROF_WAIT_START();
         const bool okw = tc::mbar_wait(&ctl->raw_full[s], use & 1, kSpinLimit);
         PROF_WAIT_END();
@@ -407,7 +472,8 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map) {
     if (pwarp == 0) { PROF_END(1); }
   } else if (warp == kCopyWarp) {
     // =========================== copy issuer ===========================
-    int it = 0;
+    int it = 0, ring_s = 0;
+    uint32_t ring_use = 0;
     bool failed = false;
     const float4 *src_hi = reinterpret_cast<const float4 *>(p.w_hi);
     const float4 *src_lo = reinterpret_cast<const float4 *>(p.w_lo);
@@ -416,15 +482,15 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map) {
         (uint32_t)p.RWt * 16u + (p.w_res_bytes ? 0u : 2u * (uint32_t)p.nky * w_chunk_bytes);
     PROF_BEGIN();
     TileWalker tc_;
-    for (tc_.init(p); tc_.tile < p.tiles && !failed; tc_.next(p)) {
+    for (tc_.init(p, order_s); tc_.tile < p.tiles && !failed; tc_.next(p)) {
       if (__any_sync(0xffffffffu, *abort_flag)) break;
       const int e0 = rowptr_s[tc_.ox];
       const int Kr = (rowptr_s[tc_.ox + 1] - e0) * p.Bp;
       const int ws = tc_.yt * kTileM + p.ws0;
       const int x0 = ws - (ws & 3);
-      for (int k0 = 0; k0 < Kr; k0 += p.KB, ++it) {
-        const int s = it % p.stages;
-        const uint32_t use = (uint32_t)(it / p.stages);
+      for (int k0 = 0; k0 < Kr; k0 += p.KB, ++it, RING_NEXT()) {
+        const int s = ring_s;
+        const uint32_t use = ring_use;
         PROF_WAIT_START();
         const bool ok = tc::mbar_wait(&ctl->empty[s], (use & 1) ^ 1, kSpinLimit);
         PROF_WAIT_END();
@@ -440,19 +506,39 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map) {
         const int chunks_here = (min(p.KB, Kr - k0) + 3) >> 2;
         if (lane == 0) tc::mbar_arrive_expect_tx(&ctl->raw_full[s], (uint32_t)chunks_here * bytes_per_chunk);
         __syncwarp();
+        // lane = chunk: 4 consecutive channels b0..b0+3 of one table entry.  The
+        // chunks of one entry are consecutive in the packed weights and in the
+        // stage, so the first lane of each run copies the whole run.
+        const int r = k0 + 4 * lane;
+        const int pp = lane < chunks_here ? r / p.Bp : -1 - lane;
+        const int prev = __shfl_up_sync(0xffffffffu, pp, 1);
+        const bool run_start = lane < chunks_here && (lane == 0 || prev != pp);
+        const unsigned starts = __ballot_sync(0xffffffffu, run_start);
         if (lane < chunks_here) {
-          // lane = chunk: 4 consecutive channels b0..b0+3 of one table entry
-          const int r = k0 + 4 * lane;
-          const int pp = r / p.Bp, b0 = r - pp * p.Bp;
+          const int b0 = r - pp * p.Bp;
           const int2 e = ent_s[e0 + pp];
-          tc::tma_load_4d(raw + (size_t)lane * p.raw_chunk_floats, &in_map, x0, e.y, tc_.n, b0, &ctl->raw_full[s]);
-          long long src = ((long long)(e.x * p.nky) * B4 + (b0 >> 2)) * NPtot + tc_.at * p.NP;
-          int dst = (lane >> 1) * (2 * p.NP) + (lane & 1) * p.NP;
-          for (int t = 0; t < p.nky && !p.w_res_bytes; ++t) {
-            tc::bulk_load(w_hi + dst, src_hi + src, w_chunk_bytes, &ctl->raw_full[s]);
-            tc::bulk_load(w_lo + dst, src_lo + src, w_chunk_bytes, &ctl->raw_full[s]);
-            src += (long long)B4 * NPtot;
-            dst += JB * 2 * p.NP;
+          if (!p.wide_box) {
+            tc::tma_load_4d(raw + (size_t)lane * p.raw_chunk_floats, &in_map, x0, e.y, tc_.n, b0, &ctl->raw_full[s]);
+          } else if (lane == 0) {
+            tc::tma_load_4d(raw, &in_map_wide, x0, e.y, tc_.n, b0, &ctl->raw_full[s]);
+          }
+          if (p.kblock_pack) {
+            // the stage's weights (hi, then lo; every tap) are one contiguous run
+            if (lane == 0) {
+              const long long blk = ((long long)(tc_.at * p.nkx + e.x) * (p.Bp / p.KB) + b0 / p.KB);
+              tc::bulk_load(w_hi, src_hi + blk * (2 * p.w_stage_bytes / 16), 2 * p.w_stage_bytes, &ctl->raw_full[s]);
+            }
+          } else if (run_start && !p.w_res_bytes) {
+            const unsigned later = lane == 31 ? 0u : starts & ~((2u << lane) - 1u);
+            const int run = (later ? __ffs(later) - 1 : chunks_here) - lane;
+            long long src = (long long)tc_.at * tile_chunks + ((long long)(e.x * p.nky) * B4 + (b0 >> 2)) * p.NP;
+            int dst = (lane >> 1) * (2 * p.NP) + (lane & 1) * p.NP;
+            for (int t = 0; t < p.nky; ++t) {
+              tc::bulk_load(w_hi + dst, src_hi + src, (uint32_t)run * w_chunk_bytes, &ctl->raw_full[s]);
+              tc::bulk_load(w_lo + dst, src_lo + src, (uint32_t)run * w_chunk_bytes, &ctl->raw_full[s]);
+              src += (long long)B4 * p.NP;
+              dst += JB * 2 * p.NP;
+            }
           }
         }
       }
@@ -464,21 +550,30 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map) {
       const uint32_t idesc = tc::idesc_tf32(kTileM, p.NP);
       const uint32_t a_lbo = (uint32_t)p.RW * 16u;
       const uint32_t b_lbo = (uint32_t)p.NP * 16u;
-      int it = 0;  // K-blocks issued so far: stage = it % stages, accumulator = it & 1
+      int it = 0, ring_s = 0;  // K-blocks issued so far; slot in the stage ring
+      uint32_t ring_use = 0;
+      int g = 0;   // accumulation intervals started so far: accumulator = g & 1
       bool failed = false;
       PROF_BEGIN();
       TileWalker tc_;
-      for (tc_.init(p); tc_.tile < p.tiles && !*abort_flag && !failed; tc_.next(p)) {
+      for (tc_.init(p, order_s); tc_.tile < p.tiles && !*abort_flag && !failed; tc_.next(p)) {
         const int Kr = (rowptr_s[tc_.ox + 1] - rowptr_s[tc_.ox]) * p.Bp;
-        for (int k0 = 0; k0 < Kr; k0 += p.KB, ++it) {
-          const int s = it % p.stages;
-          const uint32_t use = (uint32_t)(it / p.stages);
-          const int acc = it & 1;
+        uint32_t accumulate = 0;
+        int left = 0;  // K-blocks left in the open accumulation interval
+        for (int k0 = 0, kb = 0; k0 < Kr; k0 += p.KB, ++it, ++kb, RING_NEXT()) {
+          const int s = ring_s;
+          const uint32_t use = ring_use;
+          const bool opens = left == 0;  // first K-block of an accumulation interval
+          if (opens) left = p.PI;
+          --left;
+          if (opens && kb) ++g;
+          const int acc = g & 1;
           PROF_WAIT_START();
           // full[s] completes only after every converter has seen raw_full[s]
           const bool okf = tc::mbar_wait(&ctl->full[s], use & 1, kSpinLimit) &&
-                           tc::mbar_wait(&ctl->dempty[acc], (uint32_t)(((it >> 1) & 1) ^ 1), kSpinLimit);
+                           (!opens || tc::mbar_wait(&ctl->dempty[acc], (uint32_t)(((g >> 1) & 1) ^ 1), kSpinLimit));
           PROF_WAIT_END();
+          if (opens) accumulate = 0;
           if (!okf) {
             raise_timeout(ctl, 4);
             failed = true;
@@ -494,13 +589,12 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map) {
           const uint64_t db_lo0 = tc::smem_desc(st + 2 * p.a_stage_bytes + p.w_stage_bytes, b_lbo, 128u);
           const int rows_here = min(p.KB, Kr - k0);
           const int jb_here = (rows_here + 7) >> 3;
-          uint32_t accumulate = 0;
           if (p.w_res_bytes) {
             // resident weights: the two 16-byte K-chunks of a k-step are the chunks
             // of two consecutive (entry, channel group) rows; their distance goes
             // into the descriptor
-            const uint32_t wr = tc::smem_u32(w_res) + (uint32_t)(tc_.at * p.NP) * 16u;
-            const uint32_t tap_stride = (uint32_t)(B4 * NPtot);  // 16-byte units between taps
+            const uint32_t wr = tc::smem_u32(w_res) + (uint32_t)(tc_.at * tile_chunks) * 16u;
+            const uint32_t tap_stride = (uint32_t)(B4 * p.NP);  // 16-byte units between taps
             const uint2 *ks = kstep_s + kofs_s[tc_.ox] + (k0 >> 3);
             for (int j = 0; j < jb_here; ++j) {
               const uint2 k = ks[j];
@@ -531,8 +625,9 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map) {
           }
           }
           tc::tc_commit(&ctl->empty[s]);
-          tc::tc_commit(&ctl->dfull[acc]);
+          if (left == 0 || k0 + p.KB >= Kr) tc::tc_commit(&ctl->dfull[acc]);
         }
+        if (Kr > 0) ++g;
       }
       PROF_END(2);
     }
@@ -573,8 +668,8 @@ bool plan_tc_direct(const DirectProblem<float> &p, TcPlan &plan) {
     return false;
   TcParams &q = plan.params;
   q.bias = p.accumulate ? nullptr : p.bias, q.out = p.out;
-  q.row_ptr = p.table.row_ptr, q.entries = p.table.entries, q.num_entries = (int)p.table.num_entries;
-  q.N = p.N, q.A = p.A, q.B = p.B, q.Bp = (p.B + 3) / 4 * 4, q.nky = p.nky, q.nox = p.nox, q.noy = p.noy;
+  q.row_ptr = p.table.row_ptr, q.entries = p.table.entries, q.order = p.table.order, q.num_entries = (int)p.table.num_entries;
+  q.N = p.N, q.A = p.A, q.B = p.B, q.Bp = (p.B + 3) / 4 * 4, q.nkx = p.nkx, q.nky = p.nky, q.nox = p.nox, q.noy = p.noy;
   q.out_sn = p.out_sn, q.out_sa = p.out_sa;
   q.absBy = absBy;
   q.ws0 = p.Cy + std::min(0, p.By * (p.nky - 1));
@@ -586,7 +681,7 @@ bool plan_tc_direct(const DirectProblem<float> &p, TcPlan &plan) {
   q.raw_chunk_floats = (4 * q.RWt + 31) / 32 * 32;
   q.y_tiles = (p.noy + kTileM - 1) / kTileM;
   const long long tiles = (long long)p.N * p.nox * q.y_tiles * q.a_tiles;
-  if (tiles >= (1LL << 31)) return false;
+  if (tiles >= (1LL << 30)) return false;
   q.tiles = (int)tiles;
   int cols = 32;
   while (cols < 2 * q.NP) cols *= 2;
@@ -617,6 +712,22 @@ bool plan_tc_direct(const DirectProblem<float> &p, TcPlan &plan) {
   // short K-blocks leave room for a deeper ring
   while (stages < kMaxStages && (size_t)(stages + 1) * q.KB * per_row <= budget) ++stages;
   q.stages = stages;
+  q.PI = std::max(1, 96 / (3 * p.nky * (q.KB / 8)));
+  // when every stage lies inside one table entry, one wide box replaces its KB / 4
+  // row copies; the chunks must then sit back to back: rows of RW + 8 positions
+  q.wide_box = 0;
+  q.kblock_pack = 0;
+  if (q.KB >= 8 && q.Bp % q.KB == 0) {
+    const int rwt = q.RW + 8;
+    const size_t grown = (size_t)q.stages * q.KB * (size_t)(rwt - q.raw_chunk_floats / 4) * 4;
+    const size_t now = kStageOffset + 2 * (size_t)q.w_res_bytes + (size_t)q.stages * q.KB * per_row;
+    if (now + grown <= 227 * 1024) {
+      q.wide_box = 1;
+      q.RWt = rwt;
+      q.raw_chunk_floats = 4 * rwt;
+      q.kblock_pack = q.w_res_bytes ? 0 : 1;
+    }
+  }
   q.a_stage_bytes = (uint32_t)(q.KB / 4 * q.RW * 16);
   q.w_stage_bytes = q.w_res_bytes ? 0u : (uint32_t)(p.nky * (q.KB / 8) * q.NP * 32);
   q.raw_stage_bytes = (uint32_t)(q.KB / 4 * q.raw_chunk_floats * 4);
@@ -659,13 +770,13 @@ size_t direct_tc_workspace_bytes(const DirectProblem<float> &p) {
 // problem is outside what this kernel covers; the caller then uses the CUDA-core path.
 int launch_direct_tc(const DirectProblem<float> &p, void *workspace, size_t workspace_bytes, cudaStream_t stream) {
   TcPlan plan;
-  if (!plan_tc_direct(p, plan)) return MELLIN_ERR_UNSUPPORTED;
+  if (!plan_tc_direct(p, plan) || p.table.order == nullptr) return MELLIN_ERR_UNSUPPORTED;
   const size_t part = (plan.pack_floats * sizeof(float) + 255) / 256 * 256;
   if (workspace == nullptr || workspace_bytes < 2 * part || reinterpret_cast<uintptr_t>(workspace) % 16 != 0)
     return fail(MELLIN_ERR_WORKSPACE, "workspace too small or misaligned: need " + std::to_string(2 * part) +
                                           " bytes (16-byte aligned), got " + std::to_string(workspace_bytes));
   // the activations as a 4-D tensor (position, Mellin row, batch, channel) with their real strides
-  CUtensorMap in_map;
+  CUtensorMap in_map, in_map_wide;
   {
     EncodeTiledFn encode = tensor_map_encoder();
     if (encode == nullptr) return fail(MELLIN_ERR_LAUNCH, "cuTensorMapEncodeTiled is not available from this driver");
@@ -678,6 +789,14 @@ int launch_direct_tc(const DirectProblem<float> &p, void *workspace, size_t work
                               estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
                               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return MELLIN_ERR_UNSUPPORTED;  // strides the copy engine cannot express
+    in_map_wide = in_map;
+    if (plan.params.wide_box) {
+      const cuuint32_t wide[4] = {(cuuint32_t)plan.params.RWt, 1u, 1u, (cuuint32_t)plan.params.KB};
+      const CUresult rw = encode(&in_map_wide, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(p.in), dims,
+                                 strides, wide, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                 CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      if (rw != CUDA_SUCCESS) return MELLIN_ERR_UNSUPPORTED;
+    }
   }
   float *w_hi = static_cast<float *>(workspace);
   float *w_lo = reinterpret_cast<float *>(static_cast<unsigned char *>(workspace) + part);
@@ -685,8 +804,9 @@ int launch_direct_tc(const DirectProblem<float> &p, void *workspace, size_t work
     const int threads = 256;
     const long long total = (long long)plan.pack_floats;
     const int blocks = (int)std::min<long long>((total + threads - 1) / threads, 4096);
-    pack_weights_kernel<<<blocks, threads, 0, stream>>>(p.w, p.w_sa, p.w_sb, p.A, p.B, p.nkx, p.nky,
-                                                        plan.params.NP * plan.params.a_tiles, p.By, w_hi, w_lo);
+    pack_weights_kernel<<<blocks, threads, 0, stream>>>(p.w, p.w_sa, p.w_sb, p.A, p.B, p.nkx, p.nky, plan.params.NP,
+                                                        plan.params.a_tiles, p.By,
+                                                        plan.params.kblock_pack ? plan.params.KB : 0, w_hi, w_lo);
     cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) return fail(MELLIN_ERR_LAUNCH, std::string("pack_weights_kernel: ") + cudaGetErrorString(err));
     count_launch();
@@ -695,7 +815,7 @@ int launch_direct_tc(const DirectProblem<float> &p, void *workspace, size_t work
   plan.params.w_lo = w_lo;
   const char *prof = getenv("MELLIN_TC_PROFILE");
   plan.params.profile = (prof != nullptr && prof[0] == '1') ? 1 : 0;
-  void (*kernel)(TcParams, const CUtensorMap) = nullptr;
+  void (*kernel)(TcParams, const CUtensorMap, const CUtensorMap) = nullptr;
   switch (plan.params.NP / 16) {
     case 1: kernel = tc_direct_kernel<1>; break;
     case 2: kernel = tc_direct_kernel<2>; break;
@@ -708,7 +828,7 @@ int launch_direct_tc(const DirectProblem<float> &p, void *workspace, size_t work
   }
   cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem);
   if (err != cudaSuccess) return fail(MELLIN_ERR_LAUNCH, std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(err));
-  kernel<<<plan.grid, kThreads, plan.smem, stream>>>(plan.params, in_map);
+  kernel<<<plan.grid, kThreads, plan.smem, stream>>>(plan.params, in_map, in_map_wide);
   err = cudaGetLastError();
   if (err != cudaSuccess) return fail(MELLIN_ERR_LAUNCH, std::string("tc_direct_kernel: ") + cudaGetErrorString(err));
   count_launch();
