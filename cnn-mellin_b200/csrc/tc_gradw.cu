@@ -324,8 +324,11 @@ tc_gradw_kernel(const GwParams p, const __grid_constant__ CUtensorMap go_map, co
             x_lo[x_chunk * (kXSlab / 16) + t * kNB + x_row] = l;
           }
         }
-        tc::mbar_arrive(&ctl->raw_empty[r]);
+        // The proxy fence orders this thread's shared-memory accesses (its reads of
+        // the raw slot as well as its operand writes) before what the copy engine
+        // and the tensor core do once the two barriers below let them go on.
         tc::fence_proxy_async();
+        tc::mbar_arrive(&ctl->raw_empty[r]);
         tc::mbar_arrive(&ctl->full[s]);
       }
     }
