@@ -781,7 +781,8 @@ int launch_direct<double>(const DirectProblem<double> &p, cudaStream_t stream) {
 
 template <>
 size_t gradw_workspace_bytes<float>(const GradWProblem<float> &p) {
-  const size_t rows = std::max(gradw_rows_workspace_floats(p, nullptr), gradw_tc_workspace_floats(p, nullptr)) * sizeof(float);
+  const size_t rows = std::max(std::max(gradw_rows_workspace_floats(p, nullptr), gradw_tc_workspace_floats(p, nullptr)) * sizeof(float),
+                               std::max(gradw_batch_inner_workspace_bytes(p), gradw_repitch_workspace_bytes(p)));
   GradWTiling t;
   int RM = 0, RN = 0;
   if (!plan_gradw(p, t, RM, RN)) return rows;
@@ -822,6 +823,15 @@ int launch_gradw<float>(const GradWProblem<float> &p, void *workspace, size_t wo
         return rc;
       }
     }
+  }
+  if (tensor_cores_enabled() && p.noy == 1) {
+    // wide 1-D Mellin operator: the batch becomes the linear axis
+    const int rc = launch_gradw_batch_inner(p, workspace, workspace_bytes, stream);
+    if (rc != MELLIN_ERR_UNSUPPORTED) return rc;
+  }
+  if (tensor_cores_enabled() && (p.noy % 4 != 0 || p.niy % 4 != 0)) {
+    const int rc = launch_gradw_repitched(p, workspace, workspace_bytes, stream);
+    if (rc != MELLIN_ERR_UNSUPPORTED) return rc;
   }
   if (tensor_cores_enabled()) {
     // wide layers: positions are the reduction axis of a tensor-core GEMM

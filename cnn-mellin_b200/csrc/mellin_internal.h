@@ -102,6 +102,18 @@ int tc_take_error(int *code);
 size_t gradw_tc_workspace_floats(const GradWProblem<float> &p, size_t *bias_offset);
 int launch_gradw_tc(const GradWProblem<float> &p, float *part_w, float *part_b, cudaStream_t stream);
 int tc_gradw_take_error(int *code);
+// 1-D Mellin operators through the tensor-core kernels, the batch standing in
+// for the linear axis (batch_inner.cu); 0 bytes / MELLIN_ERR_UNSUPPORTED when not covered
+size_t direct_batch_inner_workspace_bytes(const DirectProblem<float> &p);
+int launch_direct_batch_inner(const DirectProblem<float> &p, void *workspace, size_t workspace_bytes,
+                              cudaStream_t stream);
+size_t gradw_batch_inner_workspace_bytes(const GradWProblem<float> &p);
+int launch_gradw_batch_inner(const GradWProblem<float> &p, void *workspace, size_t workspace_bytes,
+                             cudaStream_t stream);
+// tensor-core weight gradient for linear extents that are not multiples of 4: zero-padded copies first
+size_t gradw_repitch_workspace_bytes(const GradWProblem<float> &p);
+int launch_gradw_repitched(const GradWProblem<float> &p, void *workspace, size_t workspace_bytes,
+                           cudaStream_t stream);
 bool tensor_cores_enabled();
 int set_tensor_cores(int enable);
 template <typename T> size_t gradw_workspace_bytes(const GradWProblem<T> &p);

@@ -94,6 +94,7 @@ struct TcParams {
   int raw_chunk_floats;  // pitch of a raw 4-row chunk in shared memory (128-byte aligned); its rows are RWt apart
   int KB;        // rows per stage (multiple of 8)
   int PI;        // stages per accumulation interval: PI * KB / 8 * 3 * nky <= 96 chained MMAs
+  int table_in_smem;  // 1: row offsets, entries and row order are cached in shared memory
   int wide_box;  // 1: one TMA box brings all KB rows of a stage (they belong to one table entry)
   int kblock_pack;  // 1: weights packed stage by stage, [a tile][kx][b / KB][hi, lo][tap][(b % KB) / 4][NP][b % 4]
   int stages;
@@ -285,9 +286,15 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map,
   const int tile_chunks = p.nkx * p.nky * B4 * p.NP;  // 16-byte chunks of one output-channel tile's weights
 
   // ---- one-time set-up ------------------------------------------------------------
-  for (int i = tid; i <= p.nox; i += kThreads) rowptr_s[i] = p.row_ptr[i];
-  for (int i = tid; i < p.nox; i += kThreads) order_s[i] = p.order[i];
-  for (int i = tid; i < p.num_entries; i += kThreads) ent_s[i] = p.entries[i];
+  // small tables are cached in shared memory, large ones are read in place
+  const int *rowptr = p.table_in_smem ? rowptr_s : p.row_ptr;
+  const int *order = p.table_in_smem ? order_s : p.order;
+  const int2 *ent = p.table_in_smem ? ent_s : p.entries;
+  if (p.table_in_smem) {
+    for (int i = tid; i <= p.nox; i += kThreads) rowptr_s[i] = p.row_ptr[i];
+    for (int i = tid; i < p.nox; i += kThreads) order_s[i] = p.order[i];
+    for (int i = tid; i < p.num_entries; i += kThreads) ent_s[i] = p.entries[i];
+  }
   for (int i = tid; i < NPtot; i += kThreads) bias_s[i] = (p.bias != nullptr && i < p.A) ? p.bias[i] : 0.f;
   {
     // weight chunks of padding rows are never copied: clear the stages once so
@@ -357,10 +364,10 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map,
     int g = 0;  // accumulation intervals consumed so far
     PROF_BEGIN();
     TileWalker tc_;
-    for (tc_.init(p, order_s); tc_.tile < p.tiles; tc_.next(p)) {
+    for (tc_.init(p, order); tc_.tile < p.tiles; tc_.next(p)) {
       // tcgen05.ld is warp-collective: keep every exit decision warp-uniform
       if (__any_sync(0xffffffffu, *abort_flag)) break;
-      const int Kr = (rowptr_s[tc_.ox + 1] - rowptr_s[tc_.ox]) * p.Bp;
+      const int Kr = (rowptr[tc_.ox + 1] - rowptr[tc_.ox]) * p.Bp;
       const int oy = tc_.yt * kTileM + warp * 32 + lane;
       const int a0 = tc_.at * p.NP;
       float sum[NPC][16];
@@ -425,8 +432,8 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map,
     bool failed = false;
     PROF_BEGIN();
     TileWalker tc_;
-    for (tc_.init(p, order_s); tc_.tile < p.tiles && !*abort_flag && !failed; tc_.next(p)) {
-      const int Kr = (rowptr_s[tc_.ox + 1] - rowptr_s[tc_.ox]) * p.Bp;
+    for (tc_.init(p, order); tc_.tile < p.tiles && !*abort_flag && !failed; tc_.next(p)) {
+      const int Kr = (rowptr[tc_.ox + 1] - rowptr[tc_.ox]) * p.Bp;
       const int lead = (tc_.yt * kTileM + p.ws0) & 3;  // the copy started at the 16-byte boundary below
       for (int k0 = 0; k0 < Kr; k0 += p.KB, ++it, RING_NEXT()) {
         const int s = ring_s;
@@ -482,10 +489,10 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map,
         (uint32_t)p.RWt * 16u + (p.w_res_bytes ? 0u : 2u * (uint32_t)p.nky * w_chunk_bytes);
     PROF_BEGIN();
     TileWalker tc_;
-    for (tc_.init(p, order_s); tc_.tile < p.tiles && !failed; tc_.next(p)) {
+    for (tc_.init(p, order); tc_.tile < p.tiles && !failed; tc_.next(p)) {
       if (__any_sync(0xffffffffu, *abort_flag)) break;
-      const int e0 = rowptr_s[tc_.ox];
-      const int Kr = (rowptr_s[tc_.ox + 1] - e0) * p.Bp;
+      const int e0 = rowptr[tc_.ox];
+      const int Kr = (rowptr[tc_.ox + 1] - e0) * p.Bp;
       const int ws = tc_.yt * kTileM + p.ws0;
       const int x0 = ws - (ws & 3);
       for (int k0 = 0; k0 < Kr; k0 += p.KB, ++it, RING_NEXT()) {
@@ -516,7 +523,7 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map,
         const unsigned starts = __ballot_sync(0xffffffffu, run_start);
         if (lane < chunks_here) {
           const int b0 = r - pp * p.Bp;
-          const int2 e = ent_s[e0 + pp];
+          const int2 e = ent[e0 + pp];
           if (!p.wide_box) {
             tc::tma_load_4d(raw + (size_t)lane * p.raw_chunk_floats, &in_map, x0, e.y, tc_.n, b0, &ctl->raw_full[s]);
           } else if (lane == 0) {
@@ -556,8 +563,8 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map,
       bool failed = false;
       PROF_BEGIN();
       TileWalker tc_;
-      for (tc_.init(p, order_s); tc_.tile < p.tiles && !*abort_flag && !failed; tc_.next(p)) {
-        const int Kr = (rowptr_s[tc_.ox + 1] - rowptr_s[tc_.ox]) * p.Bp;
+      for (tc_.init(p, order); tc_.tile < p.tiles && !*abort_flag && !failed; tc_.next(p)) {
+        const int Kr = (rowptr[tc_.ox + 1] - rowptr[tc_.ox]) * p.Bp;
         uint32_t accumulate = 0;
         int left = 0;  // K-blocks left in the open accumulation interval
         for (int k0 = 0, kb = 0; k0 < Kr; k0 += p.KB, ++it, ++kb, RING_NEXT()) {
@@ -657,9 +664,9 @@ struct TcPlan {
 
 bool plan_tc_direct(const DirectProblem<float> &p, TcPlan &plan) {
   if (p.Dy != 1 || p.Ay != 1) return false;
-  if (p.A < 1 || p.A > kMaxBias || p.B < 1 || p.nky < 1 || p.nkx < 1 || p.noy < 32 || p.nox < 1 || p.N < 1)
+  if (p.A < 1 || p.A > kMaxBias || p.B < 1 || p.nky < 1 || p.nkx < 1 || p.noy < 16 || p.nox < 1 || p.N < 1)
     return false;
-  if (p.table.max_row < 1 || p.nox > kMaxTableRows || p.table.num_entries > kMaxTableEntries) return false;
+  if (p.table.max_row < 1) return false;
   const int absBy = p.By < 0 ? -p.By : p.By;
   const long long halo = (long long)absBy * (p.nky - 1);
   if (halo > 120) return false;
@@ -668,6 +675,7 @@ bool plan_tc_direct(const DirectProblem<float> &p, TcPlan &plan) {
     return false;
   TcParams &q = plan.params;
   q.bias = p.accumulate ? nullptr : p.bias, q.out = p.out;
+  q.table_in_smem = (p.nox <= kMaxTableRows && p.table.num_entries <= kMaxTableEntries) ? 1 : 0;
   q.row_ptr = p.table.row_ptr, q.entries = p.table.entries, q.order = p.table.order, q.num_entries = (int)p.table.num_entries;
   q.N = p.N, q.A = p.A, q.B = p.B, q.Bp = (p.B + 3) / 4 * 4, q.nkx = p.nkx, q.nky = p.nky, q.nox = p.nox, q.noy = p.noy;
   q.out_sn = p.out_sn, q.out_sa = p.out_sa;
@@ -693,7 +701,9 @@ bool plan_tc_direct(const DirectProblem<float> &p, TcPlan &plan) {
   const size_t w_all = plan.pack_floats * sizeof(float) + 2048;  // + room for the dummy second chunk of an odd tail
   q.w_pack_bytes = (uint32_t)(plan.pack_floats * sizeof(float));
   const long long ksteps = (p.table.num_entries * (long long)(q.Bp / 4) + 1) / 2 + p.nox;  // upper bound
-  q.w_res_bytes = (2 * w_all <= 72 * 1024 && ksteps <= kMaxKSteps) ? (uint32_t)((w_all + 127) / 128 * 128) : 0u;
+  q.w_res_bytes = (q.table_in_smem && 2 * w_all <= 72 * 1024 && ksteps <= kMaxKSteps)
+                      ? (uint32_t)((w_all + 127) / 128 * 128)
+                      : 0u;
   // bytes per row: raw copy, A (hi+lo) and, unless resident, W (hi+lo)
   const size_t per_row =
       (size_t)q.raw_chunk_floats + 8u * q.RW + (q.w_res_bytes ? 0u : 8u * (size_t)p.nky * q.NP);
@@ -708,6 +718,13 @@ bool plan_tc_direct(const DirectProblem<float> &p, TcPlan &plan) {
   kb = std::min<long long>(std::min<long long>(kb, max_rows), kMaxKB);
   // at most 96 chained MMAs (3 per tap per 8 rows) per K-block, see the note on accumulation above
   kb = std::min<long long>(kb, std::max<long long>(8, 96 / (3 * p.nky) * 8));
+  // a stage that stays inside one table entry can be fetched by one wide box and one weight copy
+  if (q.Bp >= 8 && q.Bp % kb != 0)
+    for (long long k = kb; k >= 8; k -= 8)
+      if (q.Bp % k == 0) {
+        kb = k;
+        break;
+      }
   q.KB = (int)kb;
   // short K-blocks leave room for a deeper ring
   while (stages < kMaxStages && (size_t)(stages + 1) * q.KB * per_row <= budget) ++stages;

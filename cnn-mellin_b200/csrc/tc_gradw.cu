@@ -54,7 +54,7 @@ constexpr int kKB = 16;        // positions per stage
 constexpr int kRawStages = 6;   // TMA boxes in flight (at most): deep, to cover the copy latency
 constexpr int kOpStages = 3;    // converted operand sets
 constexpr int kPromote = 8;    // stages per level-1 interval: 2 k-steps x 3 MMAs x 8 = 48 chained MMAs
-constexpr int kMaxRows = 16;   // Mellin taps
+constexpr int kMaxRows = 64;   // Mellin taps
 constexpr int kMaxTaps = 3;
 constexpr uint32_t kSpinLimit = 1u << 20;
 constexpr int kL2Col = 256;    // first TMEM column of the level-2 sums
@@ -71,7 +71,8 @@ struct GwParams {
   float *part_w;           // [slice][tap slot][B][A], slices of tap kx at prefix[kx] ...
   float *part_b;           // [slice][A] or null
   int N, A, B, nkx, nky, noy;
-  int absBy, xs0;          // tap spacing; first x position of position block 0 (Cy + min(0, By (nky - 1)))
+  int absBy, xs0;          // tap spacing; first x position of position block 0 for this launch's first tap slot
+  int g0, nky_total;       // this launch covers tap slots g0 .. g0 + nky - 1 (ascending input offset) of nky_total
   int By;
   int RXW;                 // positions per raw x row
   int a_tiles, b_tiles;
@@ -480,8 +481,9 @@ __global__ void tc_gradw_reduce_kernel(const GwParams p, float *__restrict__ gw,
       const int kx = (int)(j / per_tap);
       const long long r = j % per_tap;
       const int a = (int)(r % p.A), b = (int)((r / p.A) % p.B), t = (int)(r / ((long long)p.A * p.B));
-      const int ky = p.By < 0 ? p.nky - 1 - t : t;
-      out = (((long long)a * p.B + b) * p.nkx + kx) * p.nky + ky;
+      const int slot = p.g0 + t;
+      const int ky = p.By < 0 ? p.nky_total - 1 - slot : slot;
+      out = (((long long)a * p.B + b) * p.nkx + kx) * p.nky_total + ky;
       for (int z = prefix[kx] + zs; z < prefix[kx + 1]; z += 8) s += p.part_w[z * per_tap + r];
     }
   } else {
@@ -507,11 +509,12 @@ struct GwPlan {
   int blocks = 0, max_slices = 0;
 };
 
-bool plan_tc_gradw(const GradWProblem<float> &p, GwPlan &plan) {
+// Plans the launch for tap slots g0 .. g0 + nky - 1 (nky <= 3) of the problem's p.nky taps.
+bool plan_tc_gradw(const GradWProblem<float> &p, int g0, int nky, GwPlan &plan) {
   if (p.Dy != 1 || p.Ay != 1) return false;
-  if (p.A < 32 || p.B < 16 || p.nky < 1 || p.nky > kMaxTaps || p.nkx < 1 || p.nkx > kMaxRows || p.N < 1 || p.nox < 1 || p.noy < 16) return false;
+  if (p.A < 32 || p.B < 16 || nky < 1 || nky > kMaxTaps || g0 < 0 || g0 + nky > p.nky || p.nkx < 1 || p.nkx > kMaxRows || p.N < 1 || p.nox < 1 || p.noy < 16) return false;
   const int absBy = p.By < 0 ? -p.By : p.By;
-  const int halo = absBy * (p.nky - 1);
+  const int halo = absBy * (nky - 1);
   if (halo > 28) return false;
   // TMA: 16-byte aligned bases and strides
   if (p.noy % 4 != 0 || p.niy % 4 != 0 || reinterpret_cast<uintptr_t>(p.go) % 16 != 0 ||
@@ -520,9 +523,10 @@ bool plan_tc_gradw(const GradWProblem<float> &p, GwPlan &plan) {
   GwParams &q = plan.params;
   q.profile = 0;
   q.row_ptr = p.table.row_ptr, q.entries = p.table.entries;
-  q.N = p.N, q.A = p.A, q.B = p.B, q.nkx = p.nkx, q.nky = p.nky, q.noy = p.noy;
+  q.N = p.N, q.A = p.A, q.B = p.B, q.nkx = p.nkx, q.nky = nky, q.noy = p.noy;
+  q.g0 = g0, q.nky_total = p.nky;
   q.absBy = absBy, q.By = p.By;
-  q.xs0 = p.Cy + std::min(0, p.By * (p.nky - 1));
+  q.xs0 = p.Cy + std::min(0, p.By * (p.nky - 1)) + g0 * absBy;
   q.RXW = (kKB + halo + 3 + 3) / 4 * 4;
   q.a_tiles = (p.A + kTM - 1) / kTM;
   q.b_tiles = (p.B + kNB - 1) / kNB;
@@ -530,11 +534,11 @@ bool plan_tc_gradw(const GradWProblem<float> &p, GwPlan &plan) {
   q.chunks = (q.stages_per_row + 2 * kPromote - 1) / (2 * kPromote);
   q.chunk_stages = (q.stages_per_row + q.chunks - 1) / q.chunks;
   const int tiles = q.a_tiles * q.b_tiles;
-  q.target_slices = std::max(p.nkx, (2 * sm_count() + tiles - 1) / tiles);
+  q.target_slices = std::max(2 * p.nkx, (2 * sm_count() + tiles - 1) / tiles);
   q.go_raw_bytes = kTM * kKB * 4;
   q.x_raw_bytes = (uint32_t)((kNB * q.RXW * 4 + 127) / 128 * 128);
   q.go_op_bytes = (kKB / 4) * kGoSlab;
-  q.x_op_bytes = (kKB / 4) * x_slab(p.nky);
+  q.x_op_bytes = (kKB / 4) * x_slab(nky);
   const size_t fixed = kHeaderBytes + (size_t)kOpStages * (2 * q.go_op_bytes + 2 * (size_t)q.x_op_bytes);
   q.raw_stages = kRawStages;
   while (q.raw_stages > 3 && fixed + (size_t)q.raw_stages * (q.go_raw_bytes + q.x_raw_bytes) > 227 * 1024) --q.raw_stages;
@@ -579,39 +583,54 @@ bool make_map(CUtensorMap *map, const float *base, int inner, int rows, int chan
 
 size_t gradw_tc_workspace_floats(const GradWProblem<float> &p, size_t *bias_offset) {
   GwPlan plan;
-  if (!plan_tc_gradw(p, plan)) return 0;
-  size_t w_part = (size_t)plan.max_slices * p.nky * p.B * p.A;
+  const int nky = std::min(p.nky, kMaxTaps);  // more taps run as several launches over the same scratch
+  if (!plan_tc_gradw(p, 0, nky, plan)) return 0;
+  size_t w_part = (size_t)plan.max_slices * nky * p.B * p.A;
   w_part = (w_part + 63) / 64 * 64;
   if (bias_offset) *bias_offset = w_part;
   return w_part + (size_t)plan.max_slices * p.A;
 }
 
 // Partial sums, then their reduction into p.gw (and p.gb when part_b is given).
+// More than three linear taps run as one launch pair per three taps.
 // MELLIN_ERR_UNSUPPORTED when the problem is outside this kernel's coverage.
 int launch_gradw_tc(const GradWProblem<float> &p, float *part_w, float *part_b, cudaStream_t stream) {
-  GwPlan plan;
-  if (!plan_tc_gradw(p, plan) || p.table.row_ptr == nullptr ) return MELLIN_ERR_UNSUPPORTED;
-  CUtensorMap go_map, x_map;
-  if (!make_map(&go_map, p.go, p.noy, p.nox, p.A, p.N, kKB, kTM) ||
-      !make_map(&x_map, p.in, p.niy, p.nix, p.B, p.N, plan.params.RXW, kNB))
-    return MELLIN_ERR_UNSUPPORTED;
-  plan.params.part_w = part_w;
+  if (p.table.row_ptr == nullptr) return MELLIN_ERR_UNSUPPORTED;
+  {
+    // every slice must be plannable before the first one is launched
+    GwPlan probe;
+    for (int g0 = 0; g0 < p.nky; g0 += kMaxTaps)
+      if (!plan_tc_gradw(p, g0, std::min(kMaxTaps, p.nky - g0), probe)) return MELLIN_ERR_UNSUPPORTED;
+  }
   const char *prof = getenv("MELLIN_TC_PROFILE");
-  plan.params.profile = (prof != nullptr && prof[0] == '1') ? 1 : 0;
-  plan.params.part_b = part_b;
-  auto kernel = p.nky == 1 ? tc_gradw_kernel<1> : p.nky == 2 ? tc_gradw_kernel<2> : tc_gradw_kernel<3>;
-  cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem);
-  if (err != cudaSuccess) return fail(MELLIN_ERR_LAUNCH, std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(err));
-  kernel<<<plan.blocks, kThreads, plan.smem, stream>>>(plan.params, go_map, x_map);
-  err = cudaGetLastError();
-  if (err != cudaSuccess) return fail(MELLIN_ERR_LAUNCH, std::string("tc_gradw_kernel: ") + cudaGetErrorString(err));
-  count_launch();
-  const long long w_blocks = ((long long)p.A * p.B * p.nkx * p.nky + 31) / 32;
-  const long long b_blocks = part_b != nullptr ? (p.A + 31) / 32 : 0;
-  tc_gradw_reduce_kernel<<<(unsigned)(w_blocks + b_blocks), 256, 0, stream>>>(plan.params, p.gw, p.gb, w_blocks);
-  err = cudaGetLastError();
-  if (err != cudaSuccess) return fail(MELLIN_ERR_LAUNCH, std::string("tc_gradw_reduce_kernel: ") + cudaGetErrorString(err));
-  count_launch();
+  for (int g0 = 0; g0 < p.nky; g0 += kMaxTaps) {
+    const int nky = std::min(kMaxTaps, p.nky - g0);
+    GwPlan plan;
+    plan_tc_gradw(p, g0, nky, plan);
+    CUtensorMap go_map, x_map;
+    if (!make_map(&go_map, p.go, p.noy, p.nox, p.A, p.N, kKB, kTM) ||
+        !make_map(&x_map, p.in, p.niy, p.nix, p.B, p.N, plan.params.RXW, kNB))
+      return g0 == 0 ? MELLIN_ERR_UNSUPPORTED : fail(MELLIN_ERR_LAUNCH, "tc_gradw: tensor map encoding failed");
+    plan.params.part_w = part_w;
+    plan.params.profile = (prof != nullptr && prof[0] == '1') ? 1 : 0;
+    plan.params.part_b = g0 == 0 ? part_b : nullptr;  // the bias gradient rides on the first launch
+    auto kernel = nky == 1 ? tc_gradw_kernel<1> : nky == 2 ? tc_gradw_kernel<2> : tc_gradw_kernel<3>;
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem);
+    if (err != cudaSuccess)
+      return fail(MELLIN_ERR_LAUNCH, std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(err));
+    kernel<<<plan.blocks, kThreads, plan.smem, stream>>>(plan.params, go_map, x_map);
+    err = cudaGetLastError();
+    if (err != cudaSuccess) return fail(MELLIN_ERR_LAUNCH, std::string("tc_gradw_kernel: ") + cudaGetErrorString(err));
+    count_launch();
+    // one block per 32 partial-sum addresses of this slice's (kx, slot, b, a) space
+    const long long w_blocks = ((long long)p.A * p.B * p.nkx * nky + 31) / 32;
+    const long long b_blocks = plan.params.part_b != nullptr ? (p.A + 31) / 32 : 0;
+    tc_gradw_reduce_kernel<<<(unsigned)(w_blocks + b_blocks), 256, 0, stream>>>(plan.params, p.gw, p.gb, w_blocks);
+    err = cudaGetLastError();
+    if (err != cudaSuccess)
+      return fail(MELLIN_ERR_LAUNCH, std::string("tc_gradw_reduce_kernel: ") + cudaGetErrorString(err));
+    count_launch();
+  }
   return MELLIN_OK;
 }
 

@@ -188,6 +188,14 @@ RANDOM_CASES = [
     (3, 20, 40, (12, 36), (3, 2), (1, 1), (1, 1), (0, 0), (1, 1), (2, 1)),       # partial channel tiles
     (2, 70, 130, (10, 52), (4, 3), (1, 1), (1, 2), (0, 2), (1, 1), (1, 2)),      # two tiles each way, dilated taps
     (1, 16, 32, (30, 200), (5, 1), (1, 1), (1, 1), (0, 0), (1, 1), ("same", 0)),  # one linear tap, long reduction
+    # wide 1-D Mellin operators with a batch of >= 32: the batch stands in for the linear axis
+    (32, 16, 32, (300, 1), (16, 1), (1, 1), (1, 1), (0, 0), (1, 1), ("same", 0)),
+    (36, 20, 40, (200, 1), (12, 1), (2, 1), (2, 1), (1, 0), (1, 1), (50, 0)),     # s, d, p on the Mellin axis; ragged tiles
+    (64, 32, 48, (700, 1), (64, 1), (1, 1), (1, 1), (0, 0), (1, 1), (0, 0)),      # table too long for shared memory
+    (16, 16, 32, (120, 1), (7, 1), (1, 1), (1, 1), (0, 0), (1, 1), ("same", 0)),   # smallest batch that takes this path
+    # wide linear 1-D operators (singleton Mellin axis): weight gradient in slices of three taps
+    (2, 16, 32, (1, 400), (1, 8), (1, 1), (1, 1), (0, 0), (1, 1), (0, 0)),
+    (3, 24, 40, (1, 240), (1, 7), (1, 1), (1, 2), (0, 3), (1, 1), (0, 5)),          # dilated taps, padding both sides
 ]
 
 
