@@ -230,4 +230,44 @@ int launch_gradw_repitched(const GradWProblem<float> &p, void *workspace, size_t
   return launch_gradw_tc(q, pw, p.gb != nullptr ? pw + bias_off : nullptr, stream);
 }
 
+namespace {
+
+bool dense_input(const DirectProblem<float> &p) {
+  return p.in_sb == (long long)p.nix * p.niy && p.in_sn == (long long)p.B * p.nix * p.niy;
+}
+
+DirectProblem<float> padded_direct(const DirectProblem<float> &p, const float *xp) {
+  DirectProblem<float> q = p;
+  q.in = xp;
+  q.niy = (p.niy + 3) / 4 * 4;
+  q.in_sb = (long long)p.nix * q.niy;
+  q.in_sn = (long long)p.B * p.nix * q.niy;
+  return q;
+}
+
+}  // namespace
+
+size_t direct_repitch_workspace_bytes(const DirectProblem<float> &p) {
+  if (!tensor_cores_enabled() || p.accumulate || p.niy % 4 == 0 || p.niy < 1 || p.A <= 4) return 0;
+  const size_t tc = direct_tc_workspace_bytes(padded_direct(p, nullptr));
+  if (tc == 0) return 0;
+  return round256((size_t)p.N * p.B * p.nix * ((p.niy + 3) / 4 * 4) * sizeof(float)) + tc;
+}
+
+// forward / grad-input on tensor cores for inputs whose linear extent is not a multiple of 4
+int launch_direct_repitched(const DirectProblem<float> &p, void *workspace, size_t workspace_bytes,
+                            cudaStream_t stream) {
+  const size_t need = direct_repitch_workspace_bytes(p);
+  if (need == 0 || !dense_input(p) || workspace == nullptr || workspace_bytes < need ||
+      reinterpret_cast<uintptr_t>(workspace) % 256 != 0)
+    return MELLIN_ERR_UNSUPPORTED;
+  const int pitch = (p.niy + 3) / 4 * 4;
+  float *xp = static_cast<float *>(workspace);
+  const size_t xp_bytes = round256((size_t)p.N * p.B * p.nix * pitch * sizeof(float));
+  const int rc = repitch(p.in, (long long)p.N * p.B * p.nix, p.niy, pitch, xp, stream);
+  if (rc) return rc;
+  return launch_direct_tc(padded_direct(p, xp), static_cast<unsigned char *>(workspace) + xp_bytes,
+                          workspace_bytes - xp_bytes, stream);
+}
+
 }  // namespace mellin

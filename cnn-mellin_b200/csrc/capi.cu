@@ -64,6 +64,11 @@ int dispatch_direct(const DirectProblem<float> &p, void *workspace, size_t works
       const int rc = launch_direct_batch_inner(p, workspace, workspace_bytes, stream);
       if (rc != MELLIN_ERR_UNSUPPORTED) return rc;
     }
+    if (p.niy % 4 != 0) {
+      // rows whose pitch the TMA loads cannot address: a zero-padded copy first
+      const int rc = launch_direct_repitched(p, workspace, workspace_bytes, stream);
+      if (rc != MELLIN_ERR_UNSUPPORTED) return rc;
+    }
     const size_t need = direct_tc_workspace_bytes(p);
     if (need > 0 && workspace_bytes >= need) {
       const int rc = launch_direct_tc(p, workspace, workspace_bytes, stream);
@@ -322,7 +327,10 @@ static size_t direct_workspace_query(const Geometry2D &q, bool input_gradient) {
   p.Dy = input_gradient ? (int)q.sy : (int)q.uy;
   p.table.max_row = (int)q.nfx;  // upper bound: one entry per kernel tap
   const size_t rows = p.A <= 4 ? direct_rows_workspace_bytes(p) : 0;
-  return std::max(std::max(rows, direct_tc_workspace_bytes(p)), direct_batch_inner_workspace_bytes(p));
+  // the query describes dense tensors
+  p.in_sb = (long long)p.nix * p.niy, p.in_sn = (long long)p.B * p.nix * p.niy;
+  return std::max(std::max(rows, direct_tc_workspace_bytes(p)),
+                  std::max(direct_batch_inner_workspace_bytes(p), direct_repitch_workspace_bytes(p)));
 }
 size_t mellin_mcorrlcorr_forward_workspace_bytes(MELLIN_LAYER_GEOMETRY) {
   return direct_workspace_query(GEOM_FROM_LAYER, false);

@@ -114,6 +114,9 @@ int launch_gradw_batch_inner(const GradWProblem<float> &p, void *workspace, size
 size_t gradw_repitch_workspace_bytes(const GradWProblem<float> &p);
 int launch_gradw_repitched(const GradWProblem<float> &p, void *workspace, size_t workspace_bytes,
                            cudaStream_t stream);
+size_t direct_repitch_workspace_bytes(const DirectProblem<float> &p);
+int launch_direct_repitched(const DirectProblem<float> &p, void *workspace, size_t workspace_bytes,
+                            cudaStream_t stream);
 bool tensor_cores_enabled();
 int set_tensor_cores(int enable);
 template <typename T> size_t gradw_workspace_bytes(const GradWProblem<T> &p);

@@ -13,7 +13,13 @@
 //     (ext/torch.cpp:211-231, 282-300), and skips gradients autograd does not
 //     ask for (the reference always computes all three);
 //   * there is no CPU implementation: CPU tensors are rejected by the
-//     dispatcher.
+//     dispatcher;
+//   * float16 tensors (what the Autocast registrations below produce, as the
+//     reference's do, ext/torch.cpp:403-450) are widened to float32 around the
+//     float32 kernels and the result narrowed again: float16 storage, float32
+//     arithmetic and accumulation, like the reference's Half kernels
+//     (mconv_cuda.cuh:135-139), at the price of the conversion passes.
+#include <ATen/autocast_mode.h>
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/library.h>
@@ -55,8 +61,8 @@ void check_size(const char *c, const Tensor &t, const char *name, int pos, int64
 
 void check_cuda_float(const char *c, const Tensor &t, const char *name) {
   TORCH_CHECK(t.is_cuda(), c, ": '", name, "' must be a CUDA tensor (this build has no CPU path)");
-  TORCH_CHECK(t.scalar_type() == at::kFloat || t.scalar_type() == at::kDouble, c, ": '", name,
-              "' must be float32 or float64, got ", t.scalar_type());
+  TORCH_CHECK(t.scalar_type() == at::kFloat || t.scalar_type() == at::kDouble || t.scalar_type() == at::kHalf, c,
+              ": '", name, "' must be float16, float32 or float64, got ", t.scalar_type());
 }
 
 Pair pair_of(at::IntArrayRef v, const char *c, const char *name) {
@@ -137,6 +143,11 @@ enum class Op { Corr, Conv };
 Tensor conv_like(const char *c, Op op, int64_t dim, const Tensor &input, const Tensor &weight, const OptTensor &bias,
                  Pair s, Pair d, Pair p, Pair u, Pair r) {
   c10::cuda::CUDAGuard guard(weight.device());
+  if (weight.scalar_type() == at::kHalf && input.scalar_type() == at::kHalf &&
+      (!bias || bias->scalar_type() == at::kHalf)) {
+    const OptTensor wide_bias = bias ? OptTensor(bias->to(at::kFloat)) : OptTensor();
+    return conv_like(c, op, dim, input.to(at::kFloat), weight.to(at::kFloat), wide_bias, s, d, p, u, r).to(at::kHalf);
+  }
   ConvArgs a = check_conv(c, dim, input, weight, bias);
   int64_t nhx, nhy = 1;
   if (op == Op::Corr) {
@@ -214,6 +225,8 @@ Tensor mconvlconv_cuda(const Tensor &input, const Tensor &weight, const OptTenso
 Tensor gather_cols(const char *c, int64_t dim, const Tensor &input, Pair nf, Pair s, Pair d, Pair p, Pair u, Pair r) {
   c10::cuda::CUDAGuard guard(input.device());
   check_cuda_float(c, input, "input");
+  if (input.scalar_type() == at::kHalf)  // a pure gather: exact in any width
+    return gather_cols(c, dim, input.to(at::kFloat), nf, s, d, p, u, r).to(at::kHalf);
   check_dim(c, input, "input", 1, dim);
   Operand g = as_operand(input);
   const int64_t batch = input.size(0), c_in = input.size(1), ngx = input.size(2), ngy = dim == 4 ? input.size(3) : 1;
@@ -238,6 +251,8 @@ Tensor gather_cols(const char *c, int64_t dim, const Tensor &input, Pair nf, Pai
 Tensor scatter_cols(const char *c, int64_t dim, const Tensor &input, Pair ng, Pair s, Pair d, Pair p, Pair u) {
   c10::cuda::CUDAGuard guard(input.device());
   check_cuda_float(c, input, "input");
+  if (input.scalar_type() == at::kHalf)
+    return scatter_cols(c, dim, input.to(at::kFloat), ng, s, d, p, u).to(at::kHalf);
   check_dim(c, input, "input", 1, dim);
   Operand gg = as_operand(input);
   const int64_t batch = input.size(0), c_in = input.size(1), nfx = input.size(2);
@@ -329,6 +344,14 @@ std::vector<Tensor> layer_backward(const Tensor &grad_out_in, const Tensor &inpu
                                    bool need_bias) {
   const bool one_d = input_in.dim() == 3;
   c10::cuda::CUDAGuard guard(weight_in.device());
+  if (weight_in.scalar_type() == at::kHalf) {
+    std::vector<Tensor> wide = layer_backward(grad_out_in.to(at::kFloat), input_in.to(at::kFloat),
+                                              weight_in.to(at::kFloat), has_bias, s, d, p, u, need_input, need_weight,
+                                              need_bias);
+    for (Tensor &t : wide)
+      if (t.defined()) t = t.to(at::kHalf);
+    return wide;
+  }
   Tensor go = grad_out_in.contiguous(), x = input_in.contiguous(), w = weight_in.contiguous();
   LayerGeometry q{x.size(0), x.size(1), w.size(0), w.size(2), one_d ? 1 : w.size(3), x.size(2),
                   one_d ? 1 : x.size(3), go.size(2), one_d ? 1 : go.size(3), s, d, p, u};
@@ -491,6 +514,67 @@ TORCH_LIBRARY_IMPL(mellin, CUDA, m) {
   m.impl("col2snd", col2snd_cuda);
   m.impl("spec2col", spec2col_cuda);
   m.impl("col2spec", col2spec_cuda);
+}
+
+// Under torch.autocast the operators run in float16, like torch's own
+// convolutions: cast the tensor arguments and call the operator again below
+// the Autocast key.
+Tensor to_half(const Tensor &t) { return at::autocast::cached_cast(at::kHalf, t); }
+OptTensor to_half(const OptTensor &t) { return t ? OptTensor(to_half(*t)) : OptTensor(); }
+
+Tensor mcorr1d_autocast(const Tensor &input, const Tensor &weight, const OptTensor &bias, int64_t s, int64_t d,
+                        int64_t p, int64_t u, int64_t r) {
+  c10::impl::ExcludeDispatchKeyGuard below(c10::DispatchKey::Autocast);
+  return call_mcorr1d(to_half(input), to_half(weight), to_half(bias), s, d, p, u, r);
+}
+Tensor mconv1d_autocast(const Tensor &input, const Tensor &weight, const OptTensor &bias, int64_t s, int64_t d,
+                        int64_t p, int64_t u, int64_t r) {
+  c10::impl::ExcludeDispatchKeyGuard below(c10::DispatchKey::Autocast);
+  return typed_op<Tensor(const Tensor &, const Tensor &, const OptTensor &, int64_t, int64_t, int64_t, int64_t,
+                         int64_t)>("mellin::mconv1d")
+      .call(to_half(input), to_half(weight), to_half(bias), s, d, p, u, r);
+}
+Tensor mcorrlcorr_autocast(const Tensor &input, const Tensor &weight, const OptTensor &bias, at::IntArrayRef s,
+                           at::IntArrayRef d, at::IntArrayRef p, at::IntArrayRef u, at::IntArrayRef r) {
+  c10::impl::ExcludeDispatchKeyGuard below(c10::DispatchKey::Autocast);
+  return call_mcorrlcorr(to_half(input), to_half(weight), to_half(bias), s, d, p, u, r);
+}
+Tensor mconvlconv_autocast(const Tensor &input, const Tensor &weight, const OptTensor &bias, at::IntArrayRef s,
+                           at::IntArrayRef d, at::IntArrayRef p, at::IntArrayRef u, at::IntArrayRef r) {
+  c10::impl::ExcludeDispatchKeyGuard below(c10::DispatchKey::Autocast);
+  return typed_op<Tensor(const Tensor &, const Tensor &, const OptTensor &, at::IntArrayRef, at::IntArrayRef,
+                         at::IntArrayRef, at::IntArrayRef, at::IntArrayRef)>("mellin::mconvlconv")
+      .call(to_half(input), to_half(weight), to_half(bias), s, d, p, u, r);
+}
+Tensor snd2col_autocast(const Tensor &input, int64_t kernel_width, int64_t s, int64_t d, int64_t p, int64_t u,
+                        int64_t r) {
+  c10::impl::ExcludeDispatchKeyGuard below(c10::DispatchKey::Autocast);
+  return call_snd2col(to_half(input), kernel_width, s, d, p, u, r);
+}
+Tensor col2snd_autocast(const Tensor &input, int64_t snd_width, int64_t s, int64_t d, int64_t p, int64_t u) {
+  c10::impl::ExcludeDispatchKeyGuard below(c10::DispatchKey::Autocast);
+  return call_col2snd(to_half(input), snd_width, s, d, p, u);
+}
+Tensor spec2col_autocast(const Tensor &input, at::IntArrayRef kernel_size, at::IntArrayRef s, at::IntArrayRef d,
+                         at::IntArrayRef p, at::IntArrayRef u, at::IntArrayRef r) {
+  c10::impl::ExcludeDispatchKeyGuard below(c10::DispatchKey::Autocast);
+  return call_spec2col(to_half(input), kernel_size, s, d, p, u, r);
+}
+Tensor col2spec_autocast(const Tensor &input, at::IntArrayRef spec_size, at::IntArrayRef s, at::IntArrayRef d,
+                         at::IntArrayRef p, at::IntArrayRef u) {
+  c10::impl::ExcludeDispatchKeyGuard below(c10::DispatchKey::Autocast);
+  return call_col2spec(to_half(input), spec_size, s, d, p, u);
+}
+
+TORCH_LIBRARY_IMPL(mellin, Autocast, m) {
+  m.impl("mconv1d", mconv1d_autocast);
+  m.impl("mcorr1d", mcorr1d_autocast);
+  m.impl("mconvlconv", mconvlconv_autocast);
+  m.impl("mcorrlcorr", mcorrlcorr_autocast);
+  m.impl("snd2col", snd2col_autocast);
+  m.impl("col2snd", col2snd_autocast);
+  m.impl("spec2col", spec2col_autocast);
+  m.impl("col2spec", col2spec_autocast);
 }
 
 TORCH_LIBRARY_IMPL(mellin, Autograd, m) {

@@ -93,7 +93,9 @@ struct TcParams {
   int RWt;       // positions copied per raw row: RW + 4 (room for the 16-byte alignment lead)
   int raw_chunk_floats;  // pitch of a raw 4-row chunk in shared memory (128-byte aligned); its rows are RWt apart
   int KB;        // rows per stage (multiple of 8)
-  int PI;        // stages per accumulation interval: PI * KB / 8 * 3 * nky <= 96 chained MMAs
+  int PI;        // stages per accumulation interval: PI * KB / 8 * 3 * TG <= 96 chained MMAs
+  int TG, G;     // linear taps per stage and number of such tap groups: a block of KB rows is staged G times,
+                 // each time with the weights of TG taps (weights of many taps do not fit a stage)
   int table_in_smem;  // 1: row offsets, entries and row order are cached in shared memory
   int wide_box;  // 1: one TMA box brings all KB rows of a stage (they belong to one table entry)
   int kblock_pack;  // 1: weights packed stage by stage, [a tile][kx][b / KB][hi, lo][tap][(b % KB) / 4][NP][b % 4]
@@ -117,13 +119,13 @@ __device__ __forceinline__ float tf32_hi(float x) { return __uint_as_float(__flo
 // channels for one output channel, tap slots in increasing input-offset order,
 // output channels beyond A and reduced channels beyond B zero-filled.
 __global__ void pack_weights_kernel(const float *__restrict__ w, long long w_sa, long long w_sb, int A, int B, int nkx,
-                                    int nky, int NP, int a_tiles, int By, int KB, float *__restrict__ hi,
-                                    float *__restrict__ lo) {
+                                    int nky, int NP, int a_tiles, int By, int KB, int TG, int G,
+                                    float *__restrict__ hi, float *__restrict__ lo) {
   const int B4 = (B + 3) / 4;
   if (KB > 0) {
-    // stage-by-stage layout: [a tile][kx][b / KB][hi, lo][tap][(b % KB) / 4][NP][b % 4] in `hi`
+    // stage-by-stage layout: [a tile][kx][b / KB][tap group][hi, lo][tap in group][(b % KB) / 4][NP][b % 4] in `hi`
     const int blocks_b = B4 * 4 / KB, C = KB / 4;
-    const long long total = (long long)a_tiles * nkx * blocks_b * 2 * nky * C * NP * 4;
+    const long long total = (long long)a_tiles * nkx * blocks_b * G * 2 * TG * C * NP * 4;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
       const int bl = (int)(i & 3);
@@ -132,17 +134,19 @@ __global__ void pack_weights_kernel(const float *__restrict__ w, long long w_sa,
       r /= NP;
       const int c = (int)(r % C);
       r /= C;
-      const int t = (int)(r % nky);
-      r /= nky;
+      int t = (int)(r % TG);
+      r /= TG;
       const int part = (int)(r & 1);
       r >>= 1;
+      t += (int)(r % G) * TG;
+      r /= G;
       const int b = ((int)(r % blocks_b) * C + c) * 4 + bl;
       r /= blocks_b;
       const int kx = (int)(r % nkx);
       a += (int)(r / nkx) * NP;
       const int ky = By < 0 ? nky - 1 - t : t;
       float v = 0.f;
-      if (a < A && b < B) v = w[a * w_sa + b * w_sb + (long long)kx * nky + ky];
+      if (a < A && b < B && t < nky) v = w[a * w_sa + b * w_sb + (long long)kx * nky + ky];
       const float h = tf32_hi(v);
       hi[i] = part ? v - h : h;
     }
@@ -379,7 +383,8 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map,
           sum[c][4 * i4] = b.x, sum[c][4 * i4 + 1] = b.y, sum[c][4 * i4 + 2] = b.z, sum[c][4 * i4 + 3] = b.w;
         }
       bool failed = false;
-      for (int k0 = 0; k0 < Kr; k0 += p.KB * p.PI, ++g) {
+      const int stages_here = (Kr + p.KB - 1) / p.KB * p.G;
+      for (int v0 = 0; v0 < stages_here; v0 += p.PI, ++g) {
         const int acc = g & 1;
         PROF_WAIT_START();
         const bool ok = tc::mbar_wait(&ctl->dfull[acc], (uint32_t)((g >> 1) & 1), kSpinLimit);
@@ -435,7 +440,8 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map,
     for (tc_.init(p, order); tc_.tile < p.tiles && !*abort_flag && !failed; tc_.next(p)) {
       const int Kr = (rowptr[tc_.ox + 1] - rowptr[tc_.ox]) * p.Bp;
       const int lead = (tc_.yt * kTileM + p.ws0) & 3;  // the copy started at the 16-byte boundary below
-      for (int k0 = 0; k0 < Kr; k0 += p.KB, ++it, RING_NEXT()) {
+      for (int k0 = 0; k0 < Kr && !failed; k0 += p.KB)
+      for (int tg = 0; tg < p.G; ++tg, ++it, RING_NEXT()) {
         const int s = ring_s;
         const uint32_t use = ring_use;
         PROF_WAIT_START();
@@ -486,7 +492,7 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map,
     const float4 *src_lo = reinterpret_cast<const float4 *>(p.w_lo);
     const uint32_t w_chunk_bytes = (uint32_t)p.NP * 16u;
     const uint32_t bytes_per_chunk =
-        (uint32_t)p.RWt * 16u + (p.w_res_bytes ? 0u : 2u * (uint32_t)p.nky * w_chunk_bytes);
+        (uint32_t)p.RWt * 16u + (p.w_res_bytes ? 0u : 2u * (uint32_t)p.TG * w_chunk_bytes);
     PROF_BEGIN();
     TileWalker tc_;
     for (tc_.init(p, order); tc_.tile < p.tiles && !failed; tc_.next(p)) {
@@ -495,7 +501,8 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map,
       const int Kr = (rowptr[tc_.ox + 1] - e0) * p.Bp;
       const int ws = tc_.yt * kTileM + p.ws0;
       const int x0 = ws - (ws & 3);
-      for (int k0 = 0; k0 < Kr; k0 += p.KB, ++it, RING_NEXT()) {
+      for (int k0 = 0; k0 < Kr && !failed; k0 += p.KB)
+      for (int tg = 0; tg < p.G; ++tg, ++it, RING_NEXT()) {
         const int s = ring_s;
         const uint32_t use = ring_use;
         PROF_WAIT_START();
@@ -532,7 +539,7 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map,
           if (p.kblock_pack) {
             // the stage's weights (hi, then lo; every tap) are one contiguous run
             if (lane == 0) {
-              const long long blk = ((long long)(tc_.at * p.nkx + e.x) * (p.Bp / p.KB) + b0 / p.KB);
+              const long long blk = ((long long)(tc_.at * p.nkx + e.x) * (p.Bp / p.KB) + b0 / p.KB) * p.G + tg;
               tc::bulk_load(w_hi, src_hi + blk * (2 * p.w_stage_bytes / 16), 2 * p.w_stage_bytes, &ctl->raw_full[s]);
             }
           } else if (run_start && !p.w_res_bytes) {
@@ -567,7 +574,9 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map,
         const int Kr = (rowptr[tc_.ox + 1] - rowptr[tc_.ox]) * p.Bp;
         uint32_t accumulate = 0;
         int left = 0;  // K-blocks left in the open accumulation interval
-        for (int k0 = 0, kb = 0; k0 < Kr; k0 += p.KB, ++it, ++kb, RING_NEXT()) {
+        int kb = 0;
+        for (int k0 = 0; k0 < Kr && !failed; k0 += p.KB)
+        for (int tg = 0; tg < p.G; ++tg, ++it, ++kb, RING_NEXT()) {
           const int s = ring_s;
           const uint32_t use = ring_use;
           const bool opens = left == 0;  // first K-block of an accumulation interval
@@ -618,10 +627,11 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map,
               }
             }
           } else {
+          const int taps_here = min(p.TG, p.nky - tg * p.TG);
           for (int j = 0; j < jb_here; ++j) {
-            uint32_t a_off = (uint32_t)(2 * j * p.RW);       // 16-byte units
+            uint32_t a_off = (uint32_t)(2 * j * p.RW + tg * p.TG * p.absBy);  // 16-byte units
             uint32_t b_off = (uint32_t)(j * 2 * p.NP);
-            for (int t = 0; t < p.nky; ++t) {
+            for (int t = 0; t < taps_here; ++t) {
               tc::mma_tf32(d_addr, da_lo0 + a_off, db_hi0 + b_off, idesc, accumulate);
               tc::mma_tf32(d_addr, da_hi0 + a_off, db_lo0 + b_off, idesc, 1u);
               tc::mma_tf32(d_addr, da_hi0 + a_off, db_hi0 + b_off, idesc, 1u);
@@ -632,7 +642,7 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map,
           }
           }
           tc::tc_commit(&ctl->empty[s]);
-          if (left == 0 || k0 + p.KB >= Kr) tc::tc_commit(&ctl->dfull[acc]);
+          if (left == 0 || (k0 + p.KB >= Kr && tg == p.G - 1)) tc::tc_commit(&ctl->dfull[acc]);
         }
         if (Kr > 0) ++g;
       }
@@ -704,9 +714,14 @@ bool plan_tc_direct(const DirectProblem<float> &p, TcPlan &plan) {
   q.w_res_bytes = (q.table_in_smem && 2 * w_all <= 72 * 1024 && ksteps <= kMaxKSteps)
                       ? (uint32_t)((w_all + 127) / 128 * 128)
                       : 0u;
+  // Streamed weights: a stage carries at most four linear taps; layers with more
+  // stage every block of rows once per group of taps.
+  q.TG = (q.w_res_bytes || p.nky <= 5) ? p.nky : 4;
+  q.G = (p.nky + q.TG - 1) / q.TG;
+  plan.pack_floats = (size_t)p.nkx * q.G * q.TG * q.Bp * q.NP * q.a_tiles;
   // bytes per row: raw copy, A (hi+lo) and, unless resident, W (hi+lo)
   const size_t per_row =
-      (size_t)q.raw_chunk_floats + 8u * q.RW + (q.w_res_bytes ? 0u : 8u * (size_t)p.nky * q.NP);
+      (size_t)q.raw_chunk_floats + 8u * q.RW + (q.w_res_bytes ? 0u : 8u * (size_t)q.TG * q.NP);
   const size_t budget = 227 * 1024 - kStageOffset - 1024 - 2 * (size_t)q.w_res_bytes;
   int stages = 3;
   long long kb = (long long)(budget / stages / per_row) / 8 * 8;
@@ -717,7 +732,7 @@ bool plan_tc_direct(const DirectProblem<float> &p, TcPlan &plan) {
   if (kb < 8) return false;
   kb = std::min<long long>(std::min<long long>(kb, max_rows), kMaxKB);
   // at most 96 chained MMAs (3 per tap per 8 rows) per K-block, see the note on accumulation above
-  kb = std::min<long long>(kb, std::max<long long>(8, 96 / (3 * p.nky) * 8));
+  kb = std::min<long long>(kb, std::max<long long>(8, 96 / (3 * q.TG) * 8));
   // a stage that stays inside one table entry can be fetched by one wide box and one weight copy
   if (q.Bp >= 8 && q.Bp % kb != 0)
     for (long long k = kb; k >= 8; k -= 8)
@@ -729,7 +744,7 @@ bool plan_tc_direct(const DirectProblem<float> &p, TcPlan &plan) {
   // short K-blocks leave room for a deeper ring
   while (stages < kMaxStages && (size_t)(stages + 1) * q.KB * per_row <= budget) ++stages;
   q.stages = stages;
-  q.PI = std::max(1, 96 / (3 * p.nky * (q.KB / 8)));
+  q.PI = std::max(1, 96 / (3 * q.TG * (q.KB / 8)));
   // when every stage lies inside one table entry, one wide box replaces its KB / 4
   // row copies; the chunks must then sit back to back: rows of RW + 8 positions
   q.wide_box = 0;
@@ -746,7 +761,8 @@ bool plan_tc_direct(const DirectProblem<float> &p, TcPlan &plan) {
     }
   }
   q.a_stage_bytes = (uint32_t)(q.KB / 4 * q.RW * 16);
-  q.w_stage_bytes = q.w_res_bytes ? 0u : (uint32_t)(p.nky * (q.KB / 8) * q.NP * 32);
+  if (q.G > 1 && !q.kblock_pack) return false;  // tap groups exist in the stage-major weight layout only
+  q.w_stage_bytes = q.w_res_bytes ? 0u : (uint32_t)(q.TG * (q.KB / 8) * q.NP * 32);
   q.raw_stage_bytes = (uint32_t)(q.KB / 4 * q.raw_chunk_floats * 4);
   plan.smem = kStageOffset + 2 * (size_t)q.w_res_bytes +
               (size_t)stages * (2 * (q.a_stage_bytes + q.w_stage_bytes) + q.raw_stage_bytes);
@@ -823,7 +839,8 @@ int launch_direct_tc(const DirectProblem<float> &p, void *workspace, size_t work
     const int blocks = (int)std::min<long long>((total + threads - 1) / threads, 4096);
     pack_weights_kernel<<<blocks, threads, 0, stream>>>(p.w, p.w_sa, p.w_sb, p.A, p.B, p.nkx, p.nky, plan.params.NP,
                                                         plan.params.a_tiles, p.By,
-                                                        plan.params.kblock_pack ? plan.params.KB : 0, w_hi, w_lo);
+                                                        plan.params.kblock_pack ? plan.params.KB : 0, plan.params.TG,
+                                                        plan.params.G, w_hi, w_lo);
     cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) return fail(MELLIN_ERR_LAUNCH, std::string("pack_weights_kernel: ") + cudaGetErrorString(err));
     count_launch();

@@ -224,3 +224,67 @@ def test_argument_errors(mconv):
         mconv.mcorrlcorr(torch.zeros(1, 1, 2, 2, device="cuda"), torch.zeros(1, 1, 2, 2, device="cuda"), s=(1, 2, 3))
     with pytest.raises(NotImplementedError):
         mconv.mcorr1d(torch.zeros(1, 1, 20), torch.zeros(1, 1, 12))  # CPU tensors: no such backend here
+
+
+# ---- float16 / autocast (reference: tests/test_mconv.py:814-891) -------------------
+def test_autocast_mcorrlcorr_func(mconv):
+    """Under autocast the operator returns float16 and agrees with the float32
+    result to float16 precision; inputs are exactly representable in float16."""
+    n, c_in, c_out, t_in, f_in, t_kern, f_kern = 16, 24, 40, 48, 32, 6, 3
+    x = torch.rand(n, c_in, t_in, f_in, device="cuda", dtype=torch.half).float()
+    w = torch.rand(c_out, c_in, t_kern, f_kern, device="cuda", dtype=torch.half).float()
+    b = torch.rand(c_out, device="cuda", dtype=torch.half).float()
+    expected = mconv.mcorrlcorr(x, w, b).half()
+    with torch.autocast("cuda"):
+        got = mconv.mcorrlcorr(x, w, b)
+    assert got.dtype == torch.half
+    assert torch.allclose(expected, got, rtol=1e-2, atol=1e-2)
+    # float32 accumulation: the float16 result is the rounded float32 one
+    assert torch.equal(expected, got)
+
+
+def test_autocast_mcorr1d_func(mconv):
+    n, c_in, c_out, t_in, t_kern = 32, 16, 32, 128, 16
+    x = torch.rand(n, c_in, t_in, device="cuda", dtype=torch.half).float()
+    w = torch.rand(c_out, c_in, t_kern, device="cuda", dtype=torch.half).float()
+    b = torch.rand(c_out, device="cuda", dtype=torch.half).float()
+    expected = mconv.mcorr1d(x, w, b).half()
+    with torch.autocast("cuda"):
+        got = mconv.mcorr1d(x, w, b)
+    assert got.dtype == torch.half
+    assert torch.allclose(expected, got, rtol=1e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("kind", ["mcorr1d", "mcorrlcorr"])
+def test_autocast_layers_train_with_a_grad_scaler(mconv, kind):
+    torch.manual_seed(4)
+    if kind == "mcorr1d":
+        layer = mconv.MCorr1d(12, 8, 8).cuda()
+        x = torch.randn(16, 12, 16, device="cuda")
+    else:
+        layer = mconv.MCorrLCorr(12, 8, (4, 2)).cuda()
+        x = torch.randn(16, 12, 16, 8, device="cuda")
+    before = layer.weight.detach().clone()
+    optimizer = torch.optim.Adam(layer.parameters())
+    scaler = torch.amp.GradScaler("cuda")
+    optimizer.zero_grad()
+    with torch.autocast("cuda"):
+        out = layer(x)  # float16 from the fused operator; the narrow-kernel "mm" route adds a float32 bias
+        assert out.dtype in (torch.half, torch.float32)
+        loss = out.sum()
+    scaler.scale(loss).backward()
+    assert layer.weight.grad.dtype == torch.float32 and torch.isfinite(layer.weight.grad).all()
+    scaler.step(optimizer)
+    scaler.update()
+    assert not torch.equal(before, layer.weight.detach())
+
+
+def test_half_tensors_and_column_operators(mconv):
+    x = torch.randn(3, 4, 20, 6, device="cuda").half()
+    cols = mconv.spec2col(x, (3, 2))
+    assert cols.dtype == torch.half
+    assert torch.equal(cols, mconv.spec2col(x.float(), (3, 2)).half())
+    w = torch.randn(5, 4, 3, 2, device="cuda").half()
+    y = mconv.mcorrlcorr(x, w)
+    assert y.dtype == torch.half
+    assert torch.equal(y, mconv.mcorrlcorr(x.float(), w.float()).half())
