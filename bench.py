@@ -40,6 +40,12 @@ for _p in (ROOT, os.path.join(ROOT, "cnn-mellin_b200")):
         sys.path.insert(0, _p)
 
 WORKLOAD = dict(batch=32, c_in=3, c_out=64, ng=(41, 800), nf=(8, 3), s=(1, 1), d=(1, 1), p=(0, 1), u=(1, 1))
+# the other layers of the reference's three-layer stack (kernel 6x3, Mellin dilation 2), for --kernels-only captures
+PROFILE_LAYERS = {
+    "3to64": {},
+    "64to128": dict(c_in=64, c_out=128, nf=(6, 3), d=(2, 1)),
+    "128to256": dict(c_in=128, c_out=256, nf=(6, 3), d=(2, 1)),
+}
 METRIC = "mcorrlcorr_fwd_bwd_effective_bandwidth"
 UNIT = "GB/s"
 
@@ -452,8 +458,15 @@ def main():
                          "not for bench lines")
     ap.add_argument("--kernels-only", action="store_true",
                     help="skip the end-to-end and CPU-baseline legs (profiler captures)")
+    ap.add_argument("--layer", default="3to64", choices=sorted(PROFILE_LAYERS),
+                    help="with --kernels-only: time another layer of the reference's stacks (profiler captures of the "
+                         "wide-layer kernels); bench lines are always the 3to64 layer")
     args = ap.parse_args()
     WORKLOAD["batch"] = args.batch
+    if args.layer != "3to64":
+        if not args.kernels_only:
+            ap.error("--layer needs --kernels-only")
+        WORKLOAD.update(PROFILE_LAYERS[args.layer])
     if not args.kernels_only:
         args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":

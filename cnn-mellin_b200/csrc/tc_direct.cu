@@ -253,6 +253,34 @@ struct TileWalker {
   }
 };
 
+// This file is compiled twice.  As itself it is the kernel for layers whose
+// linear taps all fit one stage.  Included by tc_direct_taps.cu with
+// MELLIN_TAP_GROUPS defined it becomes the variant that stages every block of
+// rows once per group of TG taps (layers with many linear taps); every
+// difference between the two is one of the macros below, so that the common
+// kernel carries no code for the rare case (its single-thread issue loops are
+// sensitive to it: the merged source cost the 3-channel layer 12 %).
+#ifdef MELLIN_TAP_GROUPS
+#define STAGE_LOOP(...) \
+  for (int k0 = 0, tg = 0; k0 < Kr; (++tg == p.G ? (tg = 0, k0 += p.KB) : 0), ++it, __VA_ARGS__ RING_NEXT())
+#define STAGES_IN_TILE ((Kr + p.KB - 1) / p.KB * p.G)  // epilogue: stages, counted one by one
+#define STAGES_PER_PASS p.PI
+#define TAP_GROUP tg
+#define TAP_GROUPS p.G
+#define TAPS_HERE min(p.TG, p.nky - tg * p.TG)
+#define LAST_STAGE_OF_TILE (k0 + p.KB >= Kr && tg == p.G - 1)
+#define TC_FN(name) name##_taps
+#else
+#define STAGE_LOOP(...) for (int k0 = 0; k0 < Kr; k0 += p.KB, ++it, __VA_ARGS__ RING_NEXT())
+#define STAGES_IN_TILE Kr  // epilogue: rows, PI stages of KB rows per pass
+#define STAGES_PER_PASS (p.KB * p.PI)
+#define TAP_GROUP 0
+#define TAP_GROUPS 1
+#define TAPS_HERE p.nky
+#define LAST_STAGE_OF_TILE (k0 + p.KB >= Kr)
+#define TC_FN(name) name
+#endif
+
 // position in the stage ring: slot and number of completed laps
 #define RING_NEXT() (++ring_s == p.stages ? (ring_s = 0, ++ring_use) : 0u)
 
@@ -383,8 +411,8 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map,
           sum[c][4 * i4] = b.x, sum[c][4 * i4 + 1] = b.y, sum[c][4 * i4 + 2] = b.z, sum[c][4 * i4 + 3] = b.w;
         }
       bool failed = false;
-      const int stages_here = (Kr + p.KB - 1) / p.KB * p.G;
-      for (int v0 = 0; v0 < stages_here; v0 += p.PI, ++g) {
+      // one pass per accumulation interval: PI stages, each KB rows (of one tap group)
+      for (int v0 = 0; v0 < STAGES_IN_TILE; v0 += STAGES_PER_PASS, ++g) {
         const int acc = g & 1;
         PROF_WAIT_START();
         const bool ok = tc::mbar_wait(&ctl->dfull[acc], (uint32_t)((g >> 1) & 1), kSpinLimit);
@@ -440,8 +468,7 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map,
     for (tc_.init(p, order); tc_.tile < p.tiles && !*abort_flag && !failed; tc_.next(p)) {
       const int Kr = (rowptr[tc_.ox + 1] - rowptr[tc_.ox]) * p.Bp;
       const int lead = (tc_.yt * kTileM + p.ws0) & 3;  // the copy started at the 16-byte boundary below
-      for (int k0 = 0; k0 < Kr && !failed; k0 += p.KB)
-      for (int tg = 0; tg < p.G; ++tg, ++it, RING_NEXT()) {
+      STAGE_LOOP() {
         const int s = ring_s;
         const uint32_t use = ring_use;
         PROF_WAIT_START();
@@ -501,8 +528,7 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map,
       const int Kr = (rowptr[tc_.ox + 1] - e0) * p.Bp;
       const int ws = tc_.yt * kTileM + p.ws0;
       const int x0 = ws - (ws & 3);
-      for (int k0 = 0; k0 < Kr && !failed; k0 += p.KB)
-      for (int tg = 0; tg < p.G; ++tg, ++it, RING_NEXT()) {
+      STAGE_LOOP() {
         const int s = ring_s;
         const uint32_t use = ring_use;
         PROF_WAIT_START();
@@ -539,7 +565,7 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map,
           if (p.kblock_pack) {
             // the stage's weights (hi, then lo; every tap) are one contiguous run
             if (lane == 0) {
-              const long long blk = ((long long)(tc_.at * p.nkx + e.x) * (p.Bp / p.KB) + b0 / p.KB) * p.G + tg;
+              const long long blk = ((long long)(tc_.at * p.nkx + e.x) * (p.Bp / p.KB) + b0 / p.KB) * TAP_GROUPS + TAP_GROUP;
               tc::bulk_load(w_hi, src_hi + blk * (2 * p.w_stage_bytes / 16), 2 * p.w_stage_bytes, &ctl->raw_full[s]);
             }
           } else if (run_start && !p.w_res_bytes) {
@@ -575,8 +601,7 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map,
         uint32_t accumulate = 0;
         int left = 0;  // K-blocks left in the open accumulation interval
         int kb = 0;
-        for (int k0 = 0; k0 < Kr && !failed; k0 += p.KB)
-        for (int tg = 0; tg < p.G; ++tg, ++it, ++kb, RING_NEXT()) {
+        STAGE_LOOP(++kb,) {
           const int s = ring_s;
           const uint32_t use = ring_use;
           const bool opens = left == 0;  // first K-block of an accumulation interval
@@ -627,9 +652,9 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map,
               }
             }
           } else {
-          const int taps_here = min(p.TG, p.nky - tg * p.TG);
+          const int taps_here = TAPS_HERE;
           for (int j = 0; j < jb_here; ++j) {
-            uint32_t a_off = (uint32_t)(2 * j * p.RW + tg * p.TG * p.absBy);  // 16-byte units
+            uint32_t a_off = (uint32_t)(2 * j * p.RW + TAP_GROUP * p.TG * p.absBy);  // 16-byte units
             uint32_t b_off = (uint32_t)(j * 2 * p.NP);
             for (int t = 0; t < taps_here; ++t) {
               tc::mma_tf32(d_addr, da_lo0 + a_off, db_hi0 + b_off, idesc, accumulate);
@@ -642,7 +667,7 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map,
           }
           }
           tc::tc_commit(&ctl->empty[s]);
-          if (left == 0 || (k0 + p.KB >= Kr && tg == p.G - 1)) tc::tc_commit(&ctl->dfull[acc]);
+          if (left == 0 || LAST_STAGE_OF_TILE) tc::tc_commit(&ctl->dfull[acc]);
         }
         if (Kr > 0) ++g;
       }
@@ -714,9 +739,14 @@ bool plan_tc_direct(const DirectProblem<float> &p, TcPlan &plan) {
   q.w_res_bytes = (q.table_in_smem && 2 * w_all <= 72 * 1024 && ksteps <= kMaxKSteps)
                       ? (uint32_t)((w_all + 127) / 128 * 128)
                       : 0u;
-  // Streamed weights: a stage carries at most four linear taps; layers with more
-  // stage every block of rows once per group of taps.
-  q.TG = (q.w_res_bytes || p.nky <= 5) ? p.nky : 4;
+#ifdef MELLIN_TAP_GROUPS
+  // Streamed weights of many linear taps: a stage carries four of them, and every
+  // block of rows is staged once per group of four.
+  if (q.w_res_bytes || p.nky <= 5) return false;  // the single-group kernel covers these
+  q.TG = 4;
+#else
+  q.TG = p.nky;
+#endif
   q.G = (p.nky + q.TG - 1) / q.TG;
   plan.pack_floats = (size_t)p.nkx * q.G * q.TG * q.Bp * q.NP * q.a_tiles;
   // bytes per row: raw copy, A (hi+lo) and, unless resident, W (hi+lo)
@@ -793,16 +823,30 @@ EncodeTiledFn tensor_map_encoder() {
 
 }  // namespace
 
-size_t direct_tc_workspace_bytes(const DirectProblem<float> &p) {
+#ifndef MELLIN_TAP_GROUPS
+// the same kernel built for layers with many linear taps (tc_direct_taps.cu)
+size_t direct_tc_workspace_bytes_taps(const DirectProblem<float> &p);
+int launch_direct_tc_taps(const DirectProblem<float> &p, void *workspace, size_t workspace_bytes, cudaStream_t stream);
+int tc_take_error_taps(int *code);
+#endif
+
+size_t TC_FN(direct_tc_workspace_bytes)(const DirectProblem<float> &p) {
   TcPlan plan;
+#ifndef MELLIN_TAP_GROUPS
+  if (p.nky > 5 && !plan_tc_direct(p, plan)) return direct_tc_workspace_bytes_taps(p);
+#endif
   if (!plan_tc_direct(p, plan)) return 0;
   return 2 * ((plan.pack_floats * sizeof(float) + 255) / 256 * 256);
 }
 
 // Returns MELLIN_ERR_UNSUPPORTED (without recording an error message) when the
 // problem is outside what this kernel covers; the caller then uses the CUDA-core path.
-int launch_direct_tc(const DirectProblem<float> &p, void *workspace, size_t workspace_bytes, cudaStream_t stream) {
+int TC_FN(launch_direct_tc)(const DirectProblem<float> &p, void *workspace, size_t workspace_bytes,
+                            cudaStream_t stream) {
   TcPlan plan;
+#ifndef MELLIN_TAP_GROUPS
+  if (p.nky > 5 && !plan_tc_direct(p, plan)) return launch_direct_tc_taps(p, workspace, workspace_bytes, stream);
+#endif
   if (!plan_tc_direct(p, plan) || p.table.order == nullptr) return MELLIN_ERR_UNSUPPORTED;
   const size_t part = (plan.pack_floats * sizeof(float) + 255) / 256 * 256;
   if (workspace == nullptr || workspace_bytes < 2 * part || reinterpret_cast<uintptr_t>(workspace) % 16 != 0)
@@ -869,17 +913,23 @@ int launch_direct_tc(const DirectProblem<float> &p, void *workspace, size_t work
   return MELLIN_OK;
 }
 
-int tc_read_prof(long long *out) {
+int TC_FN(tc_read_prof)(long long *out) {
   return cudaMemcpyFromSymbol(out, g_tc_prof, 16 * sizeof(long long)) == cudaSuccess ? 0 : 2;
 }
 
 // Reads and clears the device-side timeout flag of the current device
 // (synchronises the device).
-int tc_take_error(int *code) {
+int TC_FN(tc_take_error)(int *code) {
   int zero = 0;
   cudaError_t err = cudaMemcpyFromSymbol(code, g_tc_error, sizeof(int));
   if (err == cudaSuccess) err = cudaMemcpyToSymbol(g_tc_error, &zero, sizeof(int));
   if (err != cudaSuccess) return fail(MELLIN_ERR_LAUNCH, std::string("device status: ") + cudaGetErrorString(err));
+#ifndef MELLIN_TAP_GROUPS
+  int other = 0;
+  const int rc = tc_take_error_taps(&other);
+  if (rc) return rc;
+  if (*code == 0) *code = other;
+#endif
   return MELLIN_OK;
 }
 
