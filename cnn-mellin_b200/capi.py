@@ -28,7 +28,8 @@ LAYER = ["mellin_mcorrlcorr_forward", "mellin_mcorrlcorr_grad_input", "mellin_mc
 MISC = ["mellin_abi_version", "mellin_last_error", "mellin_launch_count", "mellin_clear_tables",
         "mellin_set_tensor_cores", "mellin_device_status", "mellin_mcorrlcorr_forward_workspace_bytes",
         "mellin_mcorrlcorr_grad_input_workspace_bytes", "mellin_mcorrlcorr_grad_weight_noalloc_f32",
-        "mellin_mcorrlcorr_grad_weight_workspace_bytes", "mellin_index_map_build"]
+        "mellin_mcorrlcorr_grad_weight_workspace_bytes", "mellin_index_map_build", "mellin_tc_profile",
+        "mellin_tc_gradw_profile"]
 
 
 def exported_symbols():

@@ -297,8 +297,8 @@ int64_t mellin_lcorr_support_size(int64_t ng, int64_t s, int64_t p, int64_t u) {
 DEFINE_OPS(float, f32)
 DEFINE_OPS(double, f64)
 
-int mellin_debug_tc_prof(long long *out) { return mellin::tc_read_prof(out); }
-int mellin_debug_tc_gradw_prof(long long *out) { return mellin::tc_gradw_read_prof(out); }
+int mellin_tc_profile(long long *out) { return mellin::tc_read_prof(out); }
+int mellin_tc_gradw_profile(long long *out) { return mellin::tc_gradw_read_prof(out); }
 int mellin_set_tensor_cores(int enable) { return set_tensor_cores(enable); }
 int mellin_device_status(int *code) {
   if (code == nullptr) return fail(MELLIN_ERR_BAD_ARGUMENT, "device_status: null pointer");

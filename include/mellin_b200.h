@@ -205,6 +205,18 @@ int mellin_set_tensor_cores(int enable);
  * clears it. */
 int mellin_device_status(int *code);
 
+/* Per-role cycle counters of block 0 of the last tensor-core forward /
+ * grad-input launch (mellin_tc_profile) or weight-gradient launch
+ * (mellin_tc_gradw_profile) made while the environment variable
+ * MELLIN_TC_PROFILE was "1": out[2 * r] = cycles role r spent waiting on
+ * barriers, out[2 * r + 1] = cycles it spent working; r = 0 epilogue,
+ * 1 converter, 2 MMA issuer, 3 copy issuer (the weight-gradient kernel adds
+ * r = 4, its second converter group, out[12] = MMA cycles spent waiting for
+ * the level-1 accumulators, out[13] = stages).  16 values.  Tuning aid with
+ * no reference counterpart. */
+int mellin_tc_profile(long long *out);
+int mellin_tc_gradw_profile(long long *out);
+
 /* Drop every cached index table of the current device (frees device memory). */
 int mellin_clear_tables(void);
 

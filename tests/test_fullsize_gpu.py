@@ -169,3 +169,114 @@ def test_wide_layer_gradients_are_bit_repeatable():
             for got, ref in zip((y, gx, gw, gb), first):
                 assert torch.equal(got, ref)
     assert capi.device_status() == 0
+
+
+# ---- 1-D operators at the large-shape sweep's size -------------------------------------
+@pytest.mark.parametrize("s,d", [(1, 1), (2, 2)])
+def test_mellin_1d_sampled_elements_at_sweep_size(s, d):
+    """Batch 64, 256 -> 256 channels, length 16384, kernel 64, same-size output:
+    10000 outputs, 10000 input gradients and 200 weight gradients, each checked
+    against a float64 sum taken straight from the definition
+    h[n, co, hx] = b[co] + sum_{ci, fx} w[co, ci, fx] x[n, ci, (hx + s)(fx + d) - 1]."""
+    n, c, length, k = 64, 256, 16384, 64
+    gen = torch.Generator(device="cuda").manual_seed(50 + s)
+    x = torch.randn(n, c, length, 1, device="cuda", generator=gen)
+    w = torch.randn(c, c, k, 1, device="cuda", generator=gen) / float(np.sqrt(c * k))
+    b = torch.randn(c, device="cuda", generator=gen)
+    go = torch.randn(n, c, length, 1, device="cuda", generator=gen)
+    sv, dv, pv, uv = (s, 1), (d, 1), (0, 0), (1, 1)
+    y = torch.empty_like(go)
+    capi.forward(x, w, b, y, sv, dv, pv, uv)
+    fx = torch.arange(k, device="cuda")
+
+    def samples(count, *highs):
+        return [torch.randint(0, h, (count,), device="cuda", generator=gen) for h in highs]
+
+    # forward
+    worst, scale = 0.0, float(y.abs().max())
+    for _ in range(10):
+        sn, sco, shx = samples(1000, n, c, length)
+        idx = (shx[:, None] + s) * (fx[None, :] + d) - 1                    # (S, k)
+        ok = idx < length
+        xs = x[sn[:, None], :, idx.clamp(max=length - 1), 0].double()        # (S, k, c)
+        xs = xs * ok[:, :, None]
+        ws = w[sco, :, :, 0].double().transpose(1, 2)                        # (S, k, c)
+        ref = (xs * ws).sum(dim=(1, 2)) + b[sco].double()
+        worst = max(worst, float((ref - y[sn, sco, shx, 0].double()).abs().max()))
+    assert worst <= F32_TOL * scale
+
+    # input gradient: (hx + s)(fx + d) = ix + 1
+    gx = torch.empty_like(x)
+    capi.grad_input(w, go, gx, sv, dv, pv, uv)
+    worst, scale = 0.0, float(gx.abs().max())
+    for _ in range(10):
+        sn, sci, six = samples(1000, n, c, length)
+        q = six[:, None] + 1
+        div = fx[None, :] + d
+        hx = torch.div(q, div, rounding_mode="floor") - s
+        ok = (q % div == 0) & (hx >= 0) & (hx < length)
+        gs = go[sn[:, None], :, hx.clamp(0, length - 1), 0].double() * ok[:, :, None]   # (S, k, co)
+        ws = w[:, sci, :, 0].double().permute(1, 2, 0)                                    # (S, k, co)
+        ref = (gs * ws).sum(dim=(1, 2))
+        worst = max(worst, float((ref - gx[sn, sci, six, 0].double()).abs().max()))
+    assert worst <= F32_TOL * scale
+
+    # weight gradient
+    gw = torch.empty_like(w)
+    gb = torch.empty(c, device="cuda")
+    capi.grad_weight(x, go, gw, gb, sv, dv, pv, uv)
+    hx_all = torch.arange(length, device="cuda")
+    worst, scale = 0.0, float(gw.abs().max())
+    sco, sci, sfx = samples(200, c, c, k)
+    for co, ci, f in zip(sco.tolist(), sci.tolist(), sfx.tolist()):
+        idx = (hx_all + s) * (f + d) - 1
+        ok = idx < length
+        ref = float((go[:, co, :, 0][:, ok].double() * x[:, ci, :, 0][:, idx[ok]].double()).sum())
+        worst = max(worst, abs(ref - float(gw[co, ci, f, 0])))
+    assert worst <= F32_TOL * scale
+    bias_exact = go.double().sum(dim=(0, 2, 3))
+    assert float((gb.double() - bias_exact).abs().max()) <= F32_TOL * float(bias_exact.abs().max())
+    assert capi.device_status() == 0
+
+
+def test_linear_1d_sampled_elements_at_sweep_size():
+    """The linear 1-D operator of the sweep (singleton Mellin axis, 64 taps, batch
+    16 of 64 to bound the test's memory): sampled outputs and gradients against
+    float64 sums h[n, co, hy] = b[co] + sum_{ci, fy} w[co, ci, fy] x[n, ci, hy + fy]."""
+    n, c, length, k = 16, 256, 16384, 64
+    nh = length - k + 1
+    gen = torch.Generator(device="cuda").manual_seed(77)
+    x = torch.randn(n, c, 1, length, device="cuda", generator=gen)
+    w = torch.randn(c, c, 1, k, device="cuda", generator=gen) / float(np.sqrt(c * k))
+    b = torch.randn(c, device="cuda", generator=gen)
+    go = torch.randn(n, c, 1, nh, device="cuda", generator=gen)
+    one, zero = (1, 1), (0, 0)
+    y = torch.empty_like(go)
+    capi.forward(x, w, b, y, one, one, zero, one)
+    gx = torch.empty_like(x)
+    capi.grad_input(w, go, gx, one, one, zero, one)
+    gw = torch.empty_like(w)
+    gb = torch.empty(c, device="cuda")
+    capi.grad_weight(x, go, gw, gb, one, one, zero, one)
+    fy = torch.arange(k, device="cuda")
+    sn = torch.randint(0, n, (2000,), device="cuda", generator=gen)
+    sc = torch.randint(0, c, (2000,), device="cuda", generator=gen)
+    shy = torch.randint(0, nh, (2000,), device="cuda", generator=gen)
+    xs = x[sn[:, None], :, 0, shy[:, None] + fy[None, :]].double()          # (S, k, ci)
+    ref = (xs * w[sc, :, 0, :].double().transpose(1, 2)).sum(dim=(1, 2)) + b[sc].double()
+    assert float((ref - y[sn, sc, 0, shy].double()).abs().max()) <= F32_TOL * float(y.abs().max())
+    siy = torch.randint(0, length, (2000,), device="cuda", generator=gen)
+    hy = siy[:, None] - fy[None, :]
+    ok = (hy >= 0) & (hy < nh)
+    gs = go[sn[:, None], :, 0, hy.clamp(0, nh - 1)].double() * ok[:, :, None]  # (S, k, co)
+    ref = (gs * w[:, sc, 0, :].double().permute(1, 2, 0)).sum(dim=(1, 2))
+    assert float((ref - gx[sn, sc, 0, siy].double()).abs().max()) <= F32_TOL * float(gx.abs().max())
+    worst = 0.0
+    for co, ci, f in zip(sc[:100].tolist(), sn[:100].tolist(), shy[:100].tolist()):
+        ci, f = (ci * 16 + co) % c, f % k
+        ref = float((go[:, co, 0, :].double() * x[:, ci, 0, f:f + nh].double()).sum())
+        worst = max(worst, abs(ref - float(gw[co, ci, 0, f])))
+    assert worst <= F32_TOL * float(gw.abs().max())
+    bias_exact = go.double().sum(dim=(0, 2, 3))
+    assert float((gb.double() - bias_exact).abs().max()) <= F32_TOL * float(bias_exact.abs().max())
+    assert capi.device_status() == 0
