@@ -68,6 +68,7 @@ direct_rows_kernel(const DirectProblem<float> p, const RowsPlan t, const __grid_
   const int ox = bid % p.nox;
   const int n = bid / p.nox;
   const int y0 = yt * kTY - t.shift;  // may be negative for the first tile: those outputs are masked
+  const bool second_window = y0 + 128 < p.noy;  // outputs y0 + 128 .. of this tile exist
 
   if (tid == 0) {
     for (int w = 0; w < kWarps; ++w)
@@ -169,9 +170,15 @@ direct_rows_kernel(const DirectProblem<float> p, const RowsPlan t, const __grid_
 #pragma unroll
         for (int k = 0; k < NKY; ++k)
 #pragma unroll
-          for (int g = 0; g < 2; ++g)
+          for (int j = 0; j < 4; ++j) acc[a][j] = fmaf(wv[a * NKY + k], xw[0][j + k], acc[a][j]);
+      if (second_window) {  // block-uniform: false only where the last tile's second half lies past the signal
 #pragma unroll
-            for (int j = 0; j < 4; ++j) acc[a][4 * g + j] = fmaf(wv[a * NKY + k], xw[g][j + k], acc[a][4 * g + j]);
+        for (int a = 0; a < A; ++a)
+#pragma unroll
+          for (int k = 0; k < NKY; ++k)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[a][4 + j] = fmaf(wv[a * NKY + k], xw[1][j + k], acc[a][4 + j]);
+      }
     }
     __syncwarp();
     if (++ck == per_entry) {

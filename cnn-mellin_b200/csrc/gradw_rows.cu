@@ -135,8 +135,11 @@ gradw_rows_kernel(const GradWProblem<float> p, const RowsTiling t, float *__rest
 
     const float *gos = smem + (it % kStages) * kStageFloats + co_l * kGoPitch;
     const float *xs = smem + (it % kStages) * kStageFloats + kTA * kGoPitch;
+    // The four position slices interleave in steps of 8 positions, so that a
+    // ragged last tile (800 = 6 * 128 + 32) costs only the steps that hold data.
+    const int valid = p.noy - ((int)tile % t.y_tiles) * kTK;
 #pragma unroll 1
-    for (int yo = q * (kTK / 4); yo < (q + 1) * (kTK / 4); yo += 8) {
+    for (int yo = 8 * q; yo < kTK && yo < valid; yo += 32) {
       const float4 ga = *reinterpret_cast<const float4 *>(gos + yo);
       const float4 gb4 = *reinterpret_cast<const float4 *>(gos + yo + 4);
       const float g[8] = {ga.x, ga.y, ga.z, ga.w, gb4.x, gb4.y, gb4.z, gb4.w};
