@@ -18,7 +18,10 @@
 #include <string>
 
 #include "../../include/mellin_b200.h"
+#include <cuda.h>
+
 #include "mellin_internal.h"
+#include "tc_ptx.cuh"
 
 namespace mellin {
 
@@ -214,6 +217,168 @@ gradw_rows_kernel(const GradWProblem<float> p, const RowsTiling t, float *__rest
   }
 }
 
+// ---- the same kernel fed by TMA ---------------------------------------------------
+// One thread issues a tile's copies (one 64 x 132 box of grad_y, one box of
+// B x 136 positions per table entry) and everybody else only waits on the
+// stage's mbarrier: the per-thread address arithmetic of the cp.async version
+// was a quarter of its non-FMA instructions.  TMA boxes start at multiples of 4
+// positions, so an input window begins LEAD positions into its row
+// (LEAD = (Cy + min(0, By (nky - 1))) mod 4, a constant of the layer).
+constexpr int kSlotAlign = 128;
+__host__ __device__ constexpr int x_slot_floats(int b) { return (b * kXPitch * 4 + kSlotAlign - 1) / kSlotAlign * kSlotAlign / 4; }
+
+struct TileMeta {
+  unsigned mask;  // Mellin taps present in this tile's row
+  int valid;      // positions of the tile that lie inside the signal
+};
+
+template <int B, int NKY, int LEAD>
+__global__ void __launch_bounds__(kThreads, 2)
+gradw_rows_tma_kernel(const GradWProblem<float> p, const RowsTiling t, float *__restrict__ part_w,
+                      float *__restrict__ part_b, const __grid_constant__ CUtensorMap go_map,
+                      const __grid_constant__ CUtensorMap x_map) {
+  constexpr int BN = B * NKY;
+  constexpr int kSlot = x_slot_floats(B);
+  constexpr int kStageFloats = kTA * kGoPitch + kMaxKx * kSlot;
+  constexpr int kWin = (LEAD + 8 + NKY - 1 + 3) / 4;  // float4 loads per window
+  extern __shared__ __align__(1024) float tile_smem[];
+  float *smem = tile_smem;
+  __shared__ uint64_t full[kStages];
+  __shared__ TileMeta meta[kStages];
+
+  const int tid = threadIdx.x;
+  const int co_l = tid & (kTA - 1), q = tid >> 6;
+  const int a0 = blockIdx.y * kTA;
+  const int z = blockIdx.x;
+
+  float acc[kMaxKx][BN];
+  float bsum = 0.f;
+#pragma unroll
+  for (int k = 0; k < kMaxKx; ++k)
+#pragma unroll
+    for (int i = 0; i < BN; ++i) acc[k][i] = 0.f;
+
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) tc::mbar_init(&full[s], 1);
+    tc::fence_mbar_init();
+  }
+  __syncthreads();
+
+  auto issue = [&](long long tile, int stage) {  // thread 0 only
+    if (tile >= t.tiles) return;
+    const int tl = (int)tile;
+    const int yt = tl % t.y_tiles;
+    const int r = tl / t.y_tiles;
+    const int ox = r % p.nox, n = r / p.nox;
+    const int y0 = yt * kTK;
+    float *gos = smem + stage * kStageFloats;
+    float *xs = gos + kTA * kGoPitch;
+    const int e0 = p.table_h.row_ptr[ox];
+    const int np = p.table_h.row_ptr[ox + 1] - e0;
+    tc::mbar_arrive_expect_tx(&full[stage], (uint32_t)((kTA * kGoPitch + np * B * kXPitch) * sizeof(float)));
+    tc::tma_load_4d(gos, &go_map, y0, ox, a0, n, &full[stage]);
+    unsigned mask = 0;
+    const int x0 = y0 + t.ws0 - LEAD;  // a multiple of 4
+    for (int pp = 0; pp < np; ++pp) {
+      const int2 e = p.table_h.entries[e0 + pp];
+      mask |= 1u << e.x;
+      tc::tma_load_4d(xs + e.x * kSlot, &x_map, x0, e.y, 0, n, &full[stage]);
+    }
+    meta[stage].mask = mask;
+    meta[stage].valid = p.noy - y0;
+  };
+
+  long long tile = z;
+  if (tid == 0) {
+#pragma unroll
+    for (int s = 0; s < kStages - 1; ++s) issue(tile + (long long)s * t.Z, s);
+  }
+
+  for (int it = 0; tile < t.tiles; tile += t.Z, ++it) {
+    const int stage = it % kStages;
+    if (tid == 0) issue(tile + (long long)(kStages - 1) * t.Z, (it + kStages - 1) % kStages);
+    // every thread sees thread 0's meta[] writes: they precede its arrive on the barrier
+    if (!tc::mbar_wait(&full[stage], (uint32_t)((it / kStages) & 1), 1u << 22)) break;  // never spins forever
+    const unsigned mask = meta[stage].mask;
+    const int valid = meta[stage].valid;
+
+    const float *gos = smem + stage * kStageFloats + co_l * kGoPitch;
+    const float *xs = smem + stage * kStageFloats + kTA * kGoPitch;
+#pragma unroll 1
+    for (int yo = 8 * q; yo < kTK && yo < valid; yo += 32) {
+      const float4 ga = *reinterpret_cast<const float4 *>(gos + yo);
+      const float4 gb4 = *reinterpret_cast<const float4 *>(gos + yo + 4);
+      const float g[8] = {ga.x, ga.y, ga.z, ga.w, gb4.x, gb4.y, gb4.z, gb4.w};
+      bsum += ((g[0] + g[1]) + (g[2] + g[3])) + ((g[4] + g[5]) + (g[6] + g[7]));
+#pragma unroll
+      for (int kx = 0; kx < kMaxKx; ++kx) {
+        if (!((mask >> kx) & 1u)) continue;
+#pragma unroll
+        for (int b = 0; b < B; ++b) {
+          const float4 *xp = reinterpret_cast<const float4 *>(xs + kx * kSlot + b * kXPitch + yo);
+          float xw[4 * kWin];
+#pragma unroll
+          for (int i = 0; i < kWin; ++i) {
+            const float4 v = xp[i];
+            xw[4 * i] = v.x, xw[4 * i + 1] = v.y, xw[4 * i + 2] = v.z, xw[4 * i + 3] = v.w;
+          }
+#pragma unroll
+          for (int k = 0; k < NKY; ++k) {
+            float s = acc[kx][b * NKY + k];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) s = fmaf(g[j], xw[LEAD + j + k], s);
+            acc[kx][b * NKY + k] = s;
+          }
+        }
+      }
+    }
+    // this stage is refilled by the copy engine after the barrier: order the reads before it
+    tc::fence_proxy_async();
+    __syncthreads();
+  }
+  __syncthreads();
+
+  // ---- combine the four position slices and write this block's partial sums ----
+  float *red = smem;  // [4][64][BN]
+  const long long gw_elems = (long long)p.A * p.B * p.nkx * p.nky;
+  float *pw = part_w + (long long)z * gw_elems;
+  for (int kx = 0; kx < p.nkx && kx < kMaxKx; ++kx) {
+    float mine[BN];
+#pragma unroll
+    for (int i = 0; i < BN; ++i) mine[i] = 0.f;
+#pragma unroll
+    for (int k = 0; k < kMaxKx; ++k)
+      if (k == kx) {
+#pragma unroll
+        for (int i = 0; i < BN; ++i) mine[i] = acc[k][i];
+      }
+#pragma unroll
+    for (int i = 0; i < BN; ++i) red[(q * kTA + co_l) * BN + i] = mine[i];
+    __syncthreads();
+    if (q == 0) {
+      const int a = a0 + co_l;
+      if (a < p.A) {
+#pragma unroll
+        for (int i = 0; i < BN; ++i) {
+          const float s = (red[co_l * BN + i] + red[(kTA + co_l) * BN + i]) +
+                          (red[(2 * kTA + co_l) * BN + i] + red[(3 * kTA + co_l) * BN + i]);
+          const int b = i / NKY, k = i % NKY;
+          const int ky = p.By < 0 ? NKY - 1 - k : k;
+          pw[(((long long)a * p.B + b) * p.nkx + kx) * p.nky + ky] = s;
+        }
+      }
+    }
+    __syncthreads();
+  }
+  if (part_b != nullptr) {
+    red[q * kTA + co_l] = bsum;
+    __syncthreads();
+    const int a = a0 + co_l;
+    if (q == 0 && a < p.A)
+      part_b[(long long)z * p.A + a] = (red[co_l] + red[kTA + co_l]) + (red[2 * kTA + co_l] + red[3 * kTA + co_l]);
+  }
+}
+
 bool plan_rows(const GradWProblem<float> &p, RowsTiling &t) {
   if (p.Dy != 1 || p.Ay != 1) return false;
   if (p.nkx < 1 || p.nkx > kMaxKx || p.B < 1 || p.B > 4 || p.nky < 1 || p.nky > 3) return false;
@@ -230,8 +395,70 @@ bool plan_rows(const GradWProblem<float> &p, RowsTiling &t) {
   return t.smem <= 200 * 1024;
 }
 
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// (position, Mellin row, channel, utterance) view of a dense activation tensor
+bool make_map(CUtensorMap *map, const float *base, int inner, int rows, int chans, int batch, int box_inner,
+              int box_chans) {
+  static EncodeTiledFn encode = nullptr;
+  if (encode == nullptr) {
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      return false;
+    encode = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  const cuuint64_t dims[4] = {(cuuint64_t)inner, (cuuint64_t)rows, (cuuint64_t)chans, (cuuint64_t)batch};
+  const cuuint64_t strides[3] = {(cuuint64_t)inner * 4, (cuuint64_t)inner * rows * 4, (cuuint64_t)inner * rows * chans * 4};
+  const cuuint32_t box[4] = {(cuuint32_t)box_inner, 1u, (cuuint32_t)box_chans, 1u};
+  const cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+  return encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(base), dims, strides, box, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int B, int NKY>
+int launch_rows_tma(const GradWProblem<float> &p, const RowsTiling &t, float *pw, float *pb, cudaStream_t stream) {
+  // TMA needs 16-byte aligned bases and row pitches
+  if (p.niy % 4 != 0 || p.noy % 4 != 0 || reinterpret_cast<uintptr_t>(p.in) % 16 != 0 ||
+      reinterpret_cast<uintptr_t>(p.go) % 16 != 0)
+    return MELLIN_ERR_UNSUPPORTED;
+  CUtensorMap go_map, x_map;
+  if (!make_map(&go_map, p.go, p.noy, p.nox, p.A, p.N, kGoPitch, kTA) ||
+      !make_map(&x_map, p.in, p.niy, p.nix, p.B, p.N, kXPitch, B))
+    return MELLIN_ERR_UNSUPPORTED;
+  void (*kernel)(GradWProblem<float>, RowsTiling, float *, float *, const CUtensorMap, const CUtensorMap) = nullptr;
+  switch (((t.ws0 % 4) + 4) % 4) {
+    case 0: kernel = gradw_rows_tma_kernel<B, NKY, 0>; break;
+    case 1: kernel = gradw_rows_tma_kernel<B, NKY, 1>; break;
+    case 2: kernel = gradw_rows_tma_kernel<B, NKY, 2>; break;
+    default: kernel = gradw_rows_tma_kernel<B, NKY, 3>; break;
+  }
+  const size_t smem = (size_t)kStages * (kTA * kGoPitch + kMaxKx * x_slot_floats(B)) * sizeof(float);
+  cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (err != cudaSuccess) return fail(MELLIN_ERR_LAUNCH, std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(err));
+  kernel<<<dim3(t.Z, t.a_tiles), kThreads, smem, stream>>>(p, t, pw, pb, go_map, x_map);
+  err = cudaGetLastError();
+  if (err != cudaSuccess)
+    return fail(MELLIN_ERR_LAUNCH, std::string("gradw_rows_tma_kernel: ") + cudaGetErrorString(err));
+  count_launch();
+  return MELLIN_OK;
+}
+
 template <int B>
 int dispatch_rows_nky(const GradWProblem<float> &p, const RowsTiling &t, float *pw, float *pb, cudaStream_t stream) {
+  {
+    int rc = MELLIN_ERR_UNSUPPORTED;
+    switch (p.nky) {
+      case 1: rc = launch_rows_tma<B, 1>(p, t, pw, pb, stream); break;
+      case 2: rc = launch_rows_tma<B, 2>(p, t, pw, pb, stream); break;
+      default: rc = launch_rows_tma<B, 3>(p, t, pw, pb, stream); break;
+    }
+    if (rc != MELLIN_ERR_UNSUPPORTED) return rc;
+  }
   void (*kernel)(GradWProblem<float>, RowsTiling, float *, float *) = nullptr;
   switch (p.nky) {
     case 1: kernel = gradw_rows_kernel<B, 1>; break;
