@@ -1,12 +1,13 @@
 """Regenerate the golden fixtures under tests/golden/ from a checkout of the
 reference (sdrobert/cnn-mellin).
 
-Run in a container that has the reference checked out (default location
-``/root/reference``, override with ``MELLIN_REFERENCE``)::
+Run where the reference is checked out; ``MELLIN_REFERENCE`` names the
+checkout when it is not at the default location coded below::
 
     python tests/golden/make_golden.py
 
-It writes two files next to itself, both committed:
+It writes three files next to itself, all committed (``--stack-only`` rewrites
+only the last):
 
 ``kat_fixtures.json``
     Every known-answer case of the reference's ``c/tests/test_*_buffers.h``
@@ -27,6 +28,13 @@ It writes two files next to itself, both committed:
 
 Neither the tests nor the benchmark ever read the reference checkout; they
 read only these two files.
+
+``ref_stack3.npz``
+    Three stacked same-size layers (3 -> 8 -> 12 -> 16 channels, kernel 6x3,
+    Mellin dilation 1, 2, 2) with ReLU and per-utterance length masks before
+    every layer, forward and every gradient through the reference's extension
+    in float32 and float64: the reference's three-layer benchmark stack at
+    reduced width.
 """
 import json
 import os
@@ -178,10 +186,58 @@ def ext_cases():
     return out
 
 
+# three stacked layers with ReLU and length masks, the shape of the reference's
+# three-layer benchmark stack at reduced width: channels, kernel, Mellin dilation
+STACK = dict(batch=4, bins=41, frames=48, channels=(3, 8, 12, 16), kernel=(6, 3), dilation=((1, 1), (2, 1), (2, 1)),
+             lens=(48, 37, 29, 20))
+
+
+def stack_forward(mcorrlcorr, valid_size, x, weights, biases, mask):
+    """y = mask * relu(layer3(mask * relu(layer2(mask * relu(layer1(mask * x)))))), every layer same-size."""
+    h = x
+    for w, b, d in zip(weights, biases, STACK["dilation"]):
+        r = (STACK["bins"] - valid_size(STACK["kernel"][0], STACK["bins"], 1, d[0], 0, 1), 1)
+        h = mcorrlcorr(h * mask, w, b, (1, 1), d, (0, 1), (1, 1), r).relu()
+    return h * mask
+
+
+def stack_case():
+    sys.path.insert(0, REFERENCE)
+    if not hasattr(np, "product"):
+        np.product = np.prod
+    import torch
+    import mconv
+
+    rng = np.random.default_rng(7000)
+    ch, k = STACK["channels"], STACK["kernel"]
+    x = rng.standard_normal((STACK["batch"], ch[0], STACK["bins"], STACK["frames"])).astype(np.float32)
+    ws = [(rng.standard_normal((ch[i + 1], ch[i]) + k) * (2.0 / (ch[i] * k[0] * k[1])) ** 0.5).astype(np.float32)
+          for i in range(3)]
+    bs = [(0.1 * rng.standard_normal(ch[i + 1])).astype(np.float32) for i in range(3)]
+    mask = (np.arange(STACK["frames"])[None, :] < np.asarray(STACK["lens"])[:, None]).astype(np.float32)
+    mask = mask[:, None, None, :]
+    go = rng.standard_normal((STACK["batch"], ch[3], STACK["bins"], STACK["frames"])).astype(np.float32)
+    out = {"x": x, "go": go, "mask": mask}
+    for i in range(3):
+        out["w%d" % i], out["b%d" % i] = ws[i], bs[i]
+    for dt, tag in ((torch.float32, "f32"), (torch.float64, "f64")):
+        leaves = [torch.from_numpy(a).to(dt).requires_grad_(True) for a in [x] + ws + bs]
+        y = stack_forward(mconv._ext_mcorrlcorr, mconv.mcorr_valid_size, leaves[0], leaves[1:4], leaves[4:7],
+                          torch.from_numpy(mask).to(dt))
+        grads = torch.autograd.grad(y, leaves, torch.from_numpy(go).to(dt))
+        out["y." + tag] = y.detach().numpy()
+        for name, g in zip(["gx", "gw0", "gw1", "gw2", "gb0", "gb1", "gb2"], grads):
+            out["%s.%s" % (name, tag)] = g.numpy()
+    return out
+
+
 def main():
-    with open(os.path.join(HERE, "kat_fixtures.json"), "w") as fp:
-        json.dump(kat_fixtures(), fp, indent=0, separators=(",", ":"))
-    np.savez_compressed(os.path.join(HERE, "ref_ext_cases.npz"), **ext_cases())
+    if "--stack-only" not in sys.argv:
+        with open(os.path.join(HERE, "kat_fixtures.json"), "w") as fp:
+            json.dump(kat_fixtures(), fp, indent=0, separators=(",", ":"))
+        np.savez_compressed(os.path.join(HERE, "ref_ext_cases.npz"), **ext_cases())
+    os.environ.setdefault("TORCH_EXTENSIONS_DIR", os.path.join(HERE, "..", "..", "_work", "torch_ext"))
+    np.savez_compressed(os.path.join(HERE, "ref_stack3.npz"), **stack_case())
 
 
 if __name__ == "__main__":

@@ -288,3 +288,27 @@ def test_half_tensors_and_column_operators(mconv):
     y = mconv.mcorrlcorr(x, w, _impl="direct")  # the fused operator: float32 arithmetic on widened operands
     assert y.dtype == torch.half
     assert torch.equal(y, mconv.mcorrlcorr(x.float(), w.float(), _impl="direct").half())
+
+
+# ---- three stacked layers with ReLU and length masks against the reference extension ----
+def test_three_layer_stack_matches_the_reference_extension(mconv):
+    """The reference's three-layer stack at reduced width (tests/golden/make_golden.py,
+    ``stack_case``): output and every gradient within the float32 tolerance of the
+    reference extension's float64 run, or no further from it than its float32 run."""
+    import os
+
+    data = np.load(os.path.join(os.path.dirname(__file__), "golden", "ref_stack3.npz"))
+    dilation = ((1, 1), (2, 1), (2, 1))
+    leaves = [torch.from_numpy(data[k]).cuda().requires_grad_(True) for k in ("x", "w0", "w1", "w2", "b0", "b1", "b2")]
+    mask = torch.from_numpy(data["mask"]).cuda()
+    h = leaves[0]
+    for w, b, d in zip(leaves[1:4], leaves[4:7], dilation):
+        r = (41 - mconv.mcorr_valid_size(6, 41, 1, d[0], 0, 1), 1)
+        h = mconv.mcorrlcorr(h * mask, w, b, (1, 1), d, (0, 1), r, _impl="direct").relu()
+    y = h * mask
+    grads = torch.autograd.grad(y, leaves, torch.from_numpy(data["go"]).cuda())
+    got = dict(zip(["gx", "gw0", "gw1", "gw2", "gb0", "gb1", "gb2"], grads), y=y.detach())
+    for name, value in got.items():
+        exact, ref32 = data[name + ".f64"], data[name + ".f32"]
+        mine = helpers.rel_err(value.cpu().numpy(), exact)
+        assert mine <= max(1e-5, helpers.rel_err(ref32, exact)), (name, mine)
