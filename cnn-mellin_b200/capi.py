@@ -24,7 +24,8 @@ OP1D = ["mellin_mconv1d", "mellin_mcorr1d"]
 OP2D = ["mellin_mconvlconv", "mellin_mcorrlcorr"]
 COL1D = ["mellin_snd2col", "mellin_col2snd"]
 COL2D = ["mellin_spec2col", "mellin_col2spec"]
-LAYER = ["mellin_mcorrlcorr_forward", "mellin_mcorrlcorr_grad_input", "mellin_mcorrlcorr_grad_weight"]
+LAYER = ["mellin_mcorrlcorr_forward", "mellin_mcorrlcorr_forward_masked", "mellin_mcorrlcorr_grad_input",
+         "mellin_mcorrlcorr_grad_weight"]
 MISC = ["mellin_abi_version", "mellin_last_error", "mellin_launch_count", "mellin_clear_tables",
         "mellin_set_tensor_cores", "mellin_device_status", "mellin_mcorrlcorr_forward_workspace_bytes",
         "mellin_mcorrlcorr_grad_input_workspace_bytes", "mellin_mcorrlcorr_grad_weight_noalloc_f32",
@@ -204,6 +205,19 @@ def forward(x, w, bias, y, s, d, p, u, workspace=None):
     workspace, nbytes = _scratch(need, y, workspace)
     fn = getattr(lib(), "mellin_mcorrlcorr_forward" + _sfx(y))
     _check(fn(_p(x), _p(w), _p(bias), *geom, _p(y), _p(workspace), ctypes.c_size_t(nbytes), _stream()))
+    return y
+
+
+def forward_masked(x, w, bias, lens, relu, y, s, d, p, u, workspace=None):
+    """y = (position < lens[n]) * act(bias + mcorrlcorr(x, w)); lens: int32 device tensor or None."""
+    import torch
+
+    geom = _geometry(x.shape, w.shape, y.shape, s, d, p, u)
+    need = int(lib().mellin_mcorrlcorr_forward_workspace_bytes(*geom)) if y.dtype == torch.float32 else 0
+    workspace, nbytes = _scratch(need, y, workspace)
+    fn = getattr(lib(), "mellin_mcorrlcorr_forward_masked" + _sfx(y))
+    _check(fn(_p(x), _p(w), _p(bias), _p(lens), _INT(1 if relu else 0), *geom, _p(y), _p(workspace),
+              ctypes.c_size_t(nbytes), _stream()))
     return y
 
 

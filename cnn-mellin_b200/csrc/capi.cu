@@ -51,8 +51,49 @@ int check_geometry(const char *who, const Geometry2D &q, int64_t linear_divisor)
   return MELLIN_OK;
 }
 
+// out = oy < lens[n] ? act(out) : 0 on a dense (N, A, nox, noy) tensor: the fused
+// epilogue as a separate pass, for the paths that do not carry it themselves
+template <typename T>
+__global__ void mask_relu_kernel(T *__restrict__ out, const int *__restrict__ lens, int relu, long long total,
+                                 long long per_utterance, int noy) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int n = (int)(i / per_utterance), oy = (int)(i % noy);
+    T v = out[i];
+    if (relu && v < T(0)) v = T(0);
+    if (lens != nullptr && oy >= lens[n]) v = T(0);
+    out[i] = v;
+  }
+}
+
+template <typename T>
+int launch_mask_relu(const DirectProblem<T> &p, cudaStream_t stream) {
+  const long long per_utterance = (long long)p.A * p.nox * p.noy, total = per_utterance * p.N;
+  if (total == 0) return MELLIN_OK;
+  const int blocks = (int)std::min<long long>((total + 255) / 256, 148 * 16);
+  mask_relu_kernel<T><<<blocks, 256, 0, stream>>>(p.out, p.lens, p.relu, total, per_utterance, p.noy);
+  const cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return fail(MELLIN_ERR_LAUNCH, std::string("mask_relu_kernel: ") + cudaGetErrorString(err));
+  count_launch();
+  return MELLIN_OK;
+}
+
 // tensor cores when enabled, covered and given scratch; CUDA cores otherwise
 int dispatch_direct(const DirectProblem<float> &p, void *workspace, size_t workspace_bytes, cudaStream_t stream) {
+  if (p.lens != nullptr || p.relu) {
+    // fused length mask / ReLU: the tensor-core kernel that carries it, else the plain operator and one more pass
+    if (p.lens != nullptr && !p.accumulate && tensor_cores_enabled() && workspace != nullptr && p.A > 4) {
+      const size_t need = direct_tc_workspace_bytes_masked(p);
+      if (need > 0 && workspace_bytes >= need) {
+        const int rc = launch_direct_tc_masked(p, workspace, workspace_bytes, stream);
+        if (rc != MELLIN_ERR_UNSUPPORTED) return rc;
+      }
+    }
+    DirectProblem<float> plain = p;
+    plain.lens = nullptr, plain.relu = 0;
+    const int rc = dispatch_direct(plain, workspace, workspace_bytes, stream);
+    return rc ? rc : launch_mask_relu(p, stream);
+  }
   if (p.A <= 4) {
     // a handful of output channels: the row-streaming CUDA-core kernel
     const int rc = launch_direct_rows(p, workspace, workspace_bytes, stream);
@@ -78,12 +119,14 @@ int dispatch_direct(const DirectProblem<float> &p, void *workspace, size_t works
   return launch_direct<float>(p, stream);
 }
 int dispatch_direct(const DirectProblem<double> &p, void *, size_t, cudaStream_t stream) {
-  return launch_direct<double>(p, stream);
+  const int rc = launch_direct<double>(p, stream);
+  return (rc || (p.lens == nullptr && !p.relu)) ? rc : launch_mask_relu(p, stream);
 }
 
 template <typename T>
 int op2d(const char *who, Relation rel, const T *f, const T *g, const Geometry2D &q, int tf, int tg, int th,
-         T *h, const T *bias, bool accumulate, void *workspace, size_t workspace_bytes, void *stream) {
+         T *h, const T *bias, bool accumulate, void *workspace, size_t workspace_bytes, void *stream,
+         const int *lens = nullptr, int relu = 0) {
   int rc = check_geometry(who, q, q.uy);
   if (rc) return rc;
   const int64_t out_elems = q.batch * q.c_out * q.nhx * q.nhy;
@@ -112,6 +155,7 @@ int op2d(const char *who, Relation rel, const T *f, const T *g, const Geometry2D
   p.Cy = rel == Relation::Corr ? -(int)q.py : (int)q.py;
   p.Dy = (int)q.uy;
   p.accumulate = accumulate;
+  p.lens = lens, p.relu = relu;
   return dispatch_direct(p, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
@@ -280,6 +324,12 @@ int64_t mellin_lcorr_support_size(int64_t ng, int64_t s, int64_t p, int64_t u) {
                                       T *y, void *workspace, size_t workspace_bytes, void *stream) {  \
     return op2d<T>("mcorrlcorr_forward", Relation::Corr, w, x, GEOM_FROM_LAYER, 0, 0, 0, y, bias,     \
                    false, workspace, workspace_bytes, stream);                                        \
+  }                                                                                                   \
+  int mellin_mcorrlcorr_forward_masked_##sfx(const T *x, const T *w, const T *bias, const int *lens,   \
+                                             int relu, MELLIN_LAYER_GEOMETRY, T *y, void *workspace,  \
+                                             size_t workspace_bytes, void *stream) {                  \
+    return op2d<T>("mcorrlcorr_forward_masked", Relation::Corr, w, x, GEOM_FROM_LAYER, 0, 0, 0, y,    \
+                   bias, false, workspace, workspace_bytes, stream, lens, relu ? 1 : 0);              \
   }                                                                                                   \
   int mellin_mcorrlcorr_grad_input_##sfx(const T *w, const T *grad_y, MELLIN_LAYER_GEOMETRY,          \
                                          T *grad_x, void *workspace, size_t workspace_bytes,          \

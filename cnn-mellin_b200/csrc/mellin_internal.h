@@ -56,6 +56,9 @@ struct DirectProblem {
   long long out_sn = 0, out_sa = 0;  // element strides of out[n], out[.., a]
   int Ay = 1, By = 1, Cy = 0, Dy = 1;
   bool accumulate = false;
+  // fused epilogue (layer-level forward only): out = (oy < lens[n]) ? act(value) : 0
+  const int *lens = nullptr;  // device array of N lengths along the linear axis, or null
+  int relu = 0;
 };
 
 // Weight gradient of a correlation layer:
@@ -97,6 +100,9 @@ int launch_direct_rows(const DirectProblem<float> &p, void *workspace, size_t wo
 size_t direct_tc_workspace_bytes(const DirectProblem<float> &p);
 int launch_direct_tc(const DirectProblem<float> &p, void *workspace, size_t workspace_bytes, cudaStream_t stream);
 int tc_take_error(int *code);
+// tensor-core forward with the fused length mask / ReLU epilogue (tc_direct_masked.cu)
+size_t direct_tc_workspace_bytes_masked(const DirectProblem<float> &p);
+int launch_direct_tc_masked(const DirectProblem<float> &p, void *workspace, size_t workspace_bytes, cudaStream_t stream);
 // tensor-core weight gradient for wide layers (tc_gradw.cu): floats of partial
 // sums (0 when not covered), launch, and the device-side timeout flag
 size_t gradw_tc_workspace_floats(const GradWProblem<float> &p, size_t *bias_offset);

@@ -141,12 +141,13 @@ struct LayerGeometry {
 enum class Op { Corr, Conv };
 
 Tensor conv_like(const char *c, Op op, int64_t dim, const Tensor &input, const Tensor &weight, const OptTensor &bias,
-                 Pair s, Pair d, Pair p, Pair u, Pair r) {
+                 Pair s, Pair d, Pair p, Pair u, Pair r, const Tensor *lens = nullptr, bool relu = false) {
   c10::cuda::CUDAGuard guard(weight.device());
   if (weight.scalar_type() == at::kHalf && input.scalar_type() == at::kHalf &&
       (!bias || bias->scalar_type() == at::kHalf)) {
     const OptTensor wide_bias = bias ? OptTensor(bias->to(at::kFloat)) : OptTensor();
-    return conv_like(c, op, dim, input.to(at::kFloat), weight.to(at::kFloat), wide_bias, s, d, p, u, r).to(at::kHalf);
+    return conv_like(c, op, dim, input.to(at::kFloat), weight.to(at::kFloat), wide_bias, s, d, p, u, r, lens, relu)
+        .to(at::kHalf);
   }
   ConvArgs a = check_conv(c, dim, input, weight, bias);
   int64_t nhx, nhy = 1;
@@ -169,7 +170,21 @@ Tensor conv_like(const char *c, Op op, int64_t dim, const Tensor &input, const T
     LayerGeometry q{a.batch, a.c_in, a.c_out, a.nfx, a.nfy, a.ngx, a.ngy, nhx, nhy, s, d, p, u};
     Tensor b = bias ? bias->contiguous() : Tensor();
     int rc;
-    if (f64) {
+    if (lens != nullptr) {
+      // fused length mask / ReLU epilogue
+      TORCH_CHECK(lens->is_cuda() && lens->scalar_type() == at::kInt && lens->dim() == 1 && lens->size(0) == a.batch &&
+                      lens->is_contiguous(),
+                  c, ": 'lens' must be a contiguous int32 CUDA tensor with one length per utterance");
+      const size_t bytes = f64 ? 0 : mellin_mcorrlcorr_forward_workspace_bytes(LAYER_ARGS(q));
+      Tensor ws = at::empty({static_cast<int64_t>(bytes ? bytes : 16)}, weight.options().dtype(at::kByte));
+      rc = f64 ? mellin_mcorrlcorr_forward_masked_f64(a.g.dense.data_ptr<double>(), a.f.dense.data_ptr<double>(),
+                                                      bias ? b.data_ptr<double>() : nullptr, lens->data_ptr<int>(),
+                                                      relu, LAYER_ARGS(q), out.data_ptr<double>(), nullptr, 0, stream)
+               : mellin_mcorrlcorr_forward_masked_f32(a.g.dense.data_ptr<float>(), a.f.dense.data_ptr<float>(),
+                                                      bias ? b.data_ptr<float>() : nullptr, lens->data_ptr<int>(),
+                                                      relu, LAYER_ARGS(q), out.data_ptr<float>(), ws.data_ptr(), bytes,
+                                                      stream);
+    } else if (f64) {
       rc = mellin_mcorrlcorr_forward_f64(a.g.dense.data_ptr<double>(), a.f.dense.data_ptr<double>(),
                                          bias ? b.data_ptr<double>() : nullptr, LAYER_ARGS(q), out.data_ptr<double>(),
                                          nullptr, 0, stream);
@@ -184,6 +199,7 @@ Tensor conv_like(const char *c, Op op, int64_t dim, const Tensor &input, const T
     return out;
   }
 
+  TORCH_CHECK(lens == nullptr, c, ": the masked operator takes contiguous, untransposed operands");
   Tensor out = build_output(weight, bias, size);
   int rc;
 #define CALL_OP(fn, T)                                                                                      \
@@ -213,6 +229,14 @@ Tensor mcorrlcorr_cuda(const Tensor &input, const Tensor &weight, const OptTenso
   return conv_like(c, Op::Corr, 4, input, weight, bias, pair_of(s, c, "s"), pair_of(d, c, "d"), pair_of(p, c, "p"),
                    pair_of(u, c, "u"), pair_of(r, c, "r"));
 }
+Tensor mcorrlcorr_masked_cuda(const Tensor &input, const Tensor &weight, const OptTensor &bias, const Tensor &lens,
+                             bool relu, at::IntArrayRef s, at::IntArrayRef d, at::IntArrayRef p, at::IntArrayRef u,
+                             at::IntArrayRef r) {
+  const char *c = "mcorrlcorr_masked_cuda";
+  return conv_like(c, Op::Corr, 4, input.contiguous(), weight.contiguous(), bias, pair_of(s, c, "s"),
+                   pair_of(d, c, "d"), pair_of(p, c, "p"), pair_of(u, c, "u"), pair_of(r, c, "r"), &lens, relu);
+}
+
 Tensor mconvlconv_cuda(const Tensor &input, const Tensor &weight, const OptTensor &bias, at::IntArrayRef s,
                        at::IntArrayRef d, at::IntArrayRef p, at::IntArrayRef u, at::IntArrayRef r) {
   const char *c = "mconvlconv_cuda";
@@ -436,6 +460,55 @@ class MCorrLCorrFunction : public torch::autograd::Function<MCorrLCorrFunction> 
   }
 };
 
+Tensor call_mcorrlcorr_masked(const Tensor &i, const Tensor &w, const OptTensor &b, const Tensor &lens, bool relu,
+                              at::IntArrayRef s, at::IntArrayRef d, at::IntArrayRef p, at::IntArrayRef u,
+                              at::IntArrayRef r) {
+  return typed_op<Tensor(const Tensor &, const Tensor &, const OptTensor &, const Tensor &, bool, at::IntArrayRef,
+                         at::IntArrayRef, at::IntArrayRef, at::IntArrayRef, at::IntArrayRef)>(
+             "mellin::mcorrlcorr_masked")
+      .call(i, w, b, lens, relu, s, d, p, u, r);
+}
+
+// y = mask * act(layer(x)): dy/dz = mask * act'(z); for ReLU both factors are (y > 0)
+class MCorrLCorrMaskedFunction : public torch::autograd::Function<MCorrLCorrMaskedFunction> {
+ public:
+  static Tensor forward(torch::autograd::AutogradContext *ctx, const Tensor &input, const Tensor &weight,
+                        const OptTensor &bias, const Tensor &lens, bool relu, at::IntArrayRef s, at::IntArrayRef d,
+                        at::IntArrayRef p, at::IntArrayRef u, at::IntArrayRef r) {
+    ctx->saved_data["has_bias"] = bias.has_value();
+    ctx->saved_data["relu"] = relu;
+    ctx->saved_data["s"] = s.vec(), ctx->saved_data["d"] = d.vec();
+    ctx->saved_data["p"] = p.vec(), ctx->saved_data["u"] = u.vec();
+    Tensor y;
+    {
+      at::AutoDispatchBelowADInplaceOrView guard;
+      y = call_mcorrlcorr_masked(input, weight, bias, lens, relu, s, d, p, u, r);
+    }
+    ctx->save_for_backward({input, weight, lens, y});
+    return y;
+  }
+  static torch::autograd::tensor_list backward(torch::autograd::AutogradContext *ctx,
+                                               torch::autograd::tensor_list grads) {
+    auto saved = ctx->get_saved_variables();
+    const char *c = "mcorrlcorr_masked backward";
+    const bool has_bias = ctx->saved_data["has_bias"].toBool();
+    const Tensor &lens = saved[2], &y = saved[3];
+    Tensor go;
+    if (ctx->saved_data["relu"].toBool()) {
+      go = grads[0] * (y > 0);
+    } else {
+      Tensor mask = at::arange(y.size(3), lens.options()).unsqueeze(0) < lens.unsqueeze(1);  // (N, positions)
+      go = grads[0] * mask.unsqueeze(1).unsqueeze(1);
+    }
+    auto out = layer_backward(go, saved[0], saved[1], has_bias, pair_of(ctx->saved_data["s"].toIntVector(), c, "s"),
+                              pair_of(ctx->saved_data["d"].toIntVector(), c, "d"),
+                              pair_of(ctx->saved_data["p"].toIntVector(), c, "p"),
+                              pair_of(ctx->saved_data["u"].toIntVector(), c, "u"), ctx->needs_input_grad(0),
+                              ctx->needs_input_grad(1), has_bias && ctx->needs_input_grad(2));
+    return {out[0], out[1], out[2], Tensor(), Tensor(), Tensor(), Tensor(), Tensor(), Tensor(), Tensor()};
+  }
+};
+
 class Snd2ColFunction : public torch::autograd::Function<Snd2ColFunction> {
  public:
   static Tensor forward(torch::autograd::AutogradContext *ctx, const Tensor &input, int64_t kernel_width, int64_t s,
@@ -480,6 +553,11 @@ Tensor mcorrlcorr_autograd(const Tensor &input, const Tensor &weight, const OptT
                            at::IntArrayRef d, at::IntArrayRef p, at::IntArrayRef u, at::IntArrayRef r) {
   return MCorrLCorrFunction::apply(input, weight, bias, s, d, p, u, r);
 }
+Tensor mcorrlcorr_masked_autograd(const Tensor &input, const Tensor &weight, const OptTensor &bias, const Tensor &lens,
+                                 bool relu, at::IntArrayRef s, at::IntArrayRef d, at::IntArrayRef p, at::IntArrayRef u,
+                                 at::IntArrayRef r) {
+  return MCorrLCorrMaskedFunction::apply(input, weight, bias, lens, relu, s, d, p, u, r);
+}
 Tensor snd2col_autograd(const Tensor &input, int64_t kernel_width, int64_t s, int64_t d, int64_t p, int64_t u,
                         int64_t r) {
   return Snd2ColFunction::apply(input, kernel_width, s, d, p, u, r);
@@ -503,6 +581,8 @@ TORCH_LIBRARY(mellin, m) {
   m.def("col2snd(Tensor input, int snd_width, int s=1, int d=1, int p=0, int u=1) -> Tensor");
   m.def("spec2col(Tensor input, int[2] kernel_size, int[2] s=1, int[2] d=1, int[2] p=0, int[2] u=1, int[2] r=0) -> Tensor");
   m.def("col2spec(Tensor input, int[2] spec_size, int[2] s=1, int[2] d=1, int[2] p=0, int[2] u=1) -> Tensor");
+  // not in the reference: mcorrlcorr with the length mask and ReLU its models apply around a layer fused in
+  m.def("mcorrlcorr_masked(Tensor input, Tensor weight, Tensor? bias, Tensor lens, bool relu=True, int[2] s=1, int[2] d=1, int[2] p=0, int[2] u=1, int[2] r=0) -> Tensor");
 }
 
 TORCH_LIBRARY_IMPL(mellin, CUDA, m) {
@@ -510,6 +590,7 @@ TORCH_LIBRARY_IMPL(mellin, CUDA, m) {
   m.impl("mcorr1d", mcorr1d_cuda);
   m.impl("mconvlconv", mconvlconv_cuda);
   m.impl("mcorrlcorr", mcorrlcorr_cuda);
+  m.impl("mcorrlcorr_masked", mcorrlcorr_masked_cuda);
   m.impl("snd2col", snd2col_cuda);
   m.impl("col2snd", col2snd_cuda);
   m.impl("spec2col", spec2col_cuda);
@@ -580,6 +661,7 @@ TORCH_LIBRARY_IMPL(mellin, Autocast, m) {
 TORCH_LIBRARY_IMPL(mellin, Autograd, m) {
   m.impl("mcorr1d", mcorr1d_autograd);
   m.impl("mcorrlcorr", mcorrlcorr_autograd);
+  m.impl("mcorrlcorr_masked", mcorrlcorr_masked_autograd);
   m.impl("snd2col", snd2col_autograd);
   m.impl("spec2col", spec2col_autograd);
 }

@@ -96,6 +96,10 @@ struct TcParams {
   int PI;        // stages per accumulation interval: PI * KB / 8 * 3 * TG <= 96 chained MMAs
   int TG, G;     // linear taps per stage and number of such tap groups: a block of KB rows is staged G times,
                  // each time with the weights of TG taps (weights of many taps do not fit a stage)
+#ifdef MELLIN_MASKED
+  const int *lens;  // per utterance: outputs at positions >= lens[n] are zero
+  int relu;
+#endif
   int table_in_smem;  // 1: row offsets, entries and row order are cached in shared memory
   int wide_box;  // 1: one TMA box brings all KB rows of a stage (they belong to one table entry)
   int kblock_pack;  // 1: weights packed stage by stage, [a tile][kx][b / KB][hi, lo][tap][(b % KB) / 4][NP][b % 4]
@@ -192,7 +196,13 @@ constexpr int kMaxKSteps = 1024;      // k-steps (8 rows) over all table rows, r
 constexpr uint32_t kKOfsOffset = kBiasOffset + kMaxBias * 4;             // int[kMaxTableRows + 1]
 constexpr uint32_t kKStepOffset = kKOfsOffset + (kMaxTableRows + 1) * 4 + 4;  // uint2[kMaxKSteps], 8-byte aligned
 constexpr uint32_t kOrderOffset = kKStepOffset + kMaxKSteps * 8;  // int[kMaxTableRows]
+#ifdef MELLIN_MASKED
+constexpr int kMaxLens = 1024;  // utterances whose lengths are cached in shared memory
+constexpr uint32_t kLensOffset = kOrderOffset + kMaxTableRows * 4;  // int[kMaxLens]
+constexpr uint32_t kStageOffset = (kLensOffset + kMaxLens * 4 + 1023) / 1024 * 1024;
+#else
 constexpr uint32_t kStageOffset = (kOrderOffset + kMaxTableRows * 4 + 1023) / 1024 * 1024;
+#endif
 
 __device__ __forceinline__ void raise_timeout(TcControl *ctl, int code) {
   atomicCAS(&g_tc_error, 0, code);
@@ -278,7 +288,27 @@ struct TileWalker {
 #define TAP_GROUPS 1
 #define TAPS_HERE p.nky
 #define LAST_STAGE_OF_TILE (k0 + p.KB >= Kr)
+#ifdef MELLIN_MASKED
+#define TC_FN(name) name##_masked
+#else
 #define TC_FN(name) name
+#endif
+#endif
+
+// A third build (tc_direct_masked.cu, MELLIN_MASKED) fuses what the reference's
+// models do around a layer (models.py:386-390, 424-434): y = mask * relu(layer(x))
+// with per-utterance lengths along the linear axis.  Tiles that start at or past
+// an utterance's length are not computed at all (their outputs are zeros).
+#ifdef MELLIN_MASKED
+#define TILE_ROWS(rows) (tc_.yt * kTileM >= lens_s[tc_.n] ? 0 : (rows))
+#define EPILOGUE_LEN                                          \
+  const float keep = oy < lens_s[tc_.n] ? 1.f : 0.f;          \
+  const float floor_ = p.relu ? 0.f : -3.0e38f;
+#define STORE_VALUE(v) (fmaxf((v), floor_) * keep)
+#else
+#define TILE_ROWS(rows) (rows)
+#define EPILOGUE_LEN
+#define STORE_VALUE(v) (v)
 #endif
 
 // position in the stage ring: slot and number of completed laps
@@ -302,6 +332,10 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map,
   TcControl *ctl = reinterpret_cast<TcControl *>(smem);
   int *rowptr_s = reinterpret_cast<int *>(smem + kRowPtrOffset);
   int *order_s = reinterpret_cast<int *>(smem + kOrderOffset);
+#ifdef MELLIN_MASKED
+  int *lens_s = reinterpret_cast<int *>(smem + kLensOffset);
+  for (int i = threadIdx.x; i < p.N; i += kThreads) lens_s[i] = p.lens[i];
+#endif
   int2 *ent_s = reinterpret_cast<int2 *>(smem + kEntriesOffset);
   float *bias_s = reinterpret_cast<float *>(smem + kBiasOffset);
   int *kofs_s = reinterpret_cast<int *>(smem + kKOfsOffset);        // first k-step of every table row
@@ -399,7 +433,7 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map,
     for (tc_.init(p, order); tc_.tile < p.tiles; tc_.next(p)) {
       // tcgen05.ld is warp-collective: keep every exit decision warp-uniform
       if (__any_sync(0xffffffffu, *abort_flag)) break;
-      const int Kr = (rowptr[tc_.ox + 1] - rowptr[tc_.ox]) * p.Bp;
+      const int Kr = TILE_ROWS((rowptr[tc_.ox + 1] - rowptr[tc_.ox]) * p.Bp);
       const int oy = tc_.yt * kTileM + warp * 32 + lane;
       const int a0 = tc_.at * p.NP;
       float sum[NPC][16];
@@ -447,11 +481,12 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map,
       if (oy < p.noy) {
         float *o = p.out + tc_.n * p.out_sn + a0 * p.out_sa + (long long)tc_.ox * p.noy + oy;
         const int a_left = p.A - a0;
+        EPILOGUE_LEN
 #pragma unroll
         for (int c = 0; c < NPC; ++c)
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            if (16 * c + i < a_left) __stcs(o, sum[c][i]);
+            if (16 * c + i < a_left) __stcs(o, STORE_VALUE(sum[c][i]));
             o += p.out_sa;
           }
       }
@@ -466,7 +501,7 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map,
     PROF_BEGIN();
     TileWalker tc_;
     for (tc_.init(p, order); tc_.tile < p.tiles && !*abort_flag && !failed; tc_.next(p)) {
-      const int Kr = (rowptr[tc_.ox + 1] - rowptr[tc_.ox]) * p.Bp;
+      const int Kr = TILE_ROWS((rowptr[tc_.ox + 1] - rowptr[tc_.ox]) * p.Bp);
       const int lead = (tc_.yt * kTileM + p.ws0) & 3;  // the copy started at the 16-byte boundary below
       STAGE_LOOP() {
         const int s = ring_s;
@@ -525,7 +560,7 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map,
     for (tc_.init(p, order); tc_.tile < p.tiles && !failed; tc_.next(p)) {
       if (__any_sync(0xffffffffu, *abort_flag)) break;
       const int e0 = rowptr[tc_.ox];
-      const int Kr = (rowptr[tc_.ox + 1] - e0) * p.Bp;
+      const int Kr = TILE_ROWS((rowptr[tc_.ox + 1] - e0) * p.Bp);
       const int ws = tc_.yt * kTileM + p.ws0;
       const int x0 = ws - (ws & 3);
       STAGE_LOOP() {
@@ -597,7 +632,7 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map,
       PROF_BEGIN();
       TileWalker tc_;
       for (tc_.init(p, order); tc_.tile < p.tiles && !*abort_flag && !failed; tc_.next(p)) {
-        const int Kr = (rowptr[tc_.ox + 1] - rowptr[tc_.ox]) * p.Bp;
+        const int Kr = TILE_ROWS((rowptr[tc_.ox + 1] - rowptr[tc_.ox]) * p.Bp);
         uint32_t accumulate = 0;
         int left = 0;  // K-blocks left in the open accumulation interval
         int kb = 0;
@@ -709,6 +744,10 @@ bool plan_tc_direct(const DirectProblem<float> &p, TcPlan &plan) {
   if (p.niy % 4 != 0 || reinterpret_cast<uintptr_t>(p.in) % 16 != 0 || p.in_sn % 4 != 0 || p.in_sb % 4 != 0)
     return false;
   TcParams &q = plan.params;
+#ifdef MELLIN_MASKED
+  if (p.lens == nullptr || p.N > kMaxLens) return false;
+  q.lens = p.lens, q.relu = p.relu;
+#endif
   q.bias = p.accumulate ? nullptr : p.bias, q.out = p.out;
   q.table_in_smem = (p.nox <= kMaxTableRows && p.table.num_entries <= kMaxTableEntries) ? 1 : 0;
   q.row_ptr = p.table.row_ptr, q.entries = p.table.entries, q.order = p.table.order, q.num_entries = (int)p.table.num_entries;
@@ -823,16 +862,20 @@ EncodeTiledFn tensor_map_encoder() {
 
 }  // namespace
 
-#ifndef MELLIN_TAP_GROUPS
+#if !defined(MELLIN_TAP_GROUPS) && !defined(MELLIN_MASKED)
+#define MELLIN_BASE_BUILD 1
+#endif
+#ifdef MELLIN_BASE_BUILD
 // the same kernel built for layers with many linear taps (tc_direct_taps.cu)
 size_t direct_tc_workspace_bytes_taps(const DirectProblem<float> &p);
 int launch_direct_tc_taps(const DirectProblem<float> &p, void *workspace, size_t workspace_bytes, cudaStream_t stream);
 int tc_take_error_taps(int *code);
+int tc_take_error_masked(int *code);
 #endif
 
 size_t TC_FN(direct_tc_workspace_bytes)(const DirectProblem<float> &p) {
   TcPlan plan;
-#ifndef MELLIN_TAP_GROUPS
+#ifdef MELLIN_BASE_BUILD
   if (p.nky > 5 && !plan_tc_direct(p, plan)) return direct_tc_workspace_bytes_taps(p);
 #endif
   if (!plan_tc_direct(p, plan)) return 0;
@@ -844,7 +887,7 @@ size_t TC_FN(direct_tc_workspace_bytes)(const DirectProblem<float> &p) {
 int TC_FN(launch_direct_tc)(const DirectProblem<float> &p, void *workspace, size_t workspace_bytes,
                             cudaStream_t stream) {
   TcPlan plan;
-#ifndef MELLIN_TAP_GROUPS
+#ifdef MELLIN_BASE_BUILD
   if (p.nky > 5 && !plan_tc_direct(p, plan)) return launch_direct_tc_taps(p, workspace, workspace_bytes, stream);
 #endif
   if (!plan_tc_direct(p, plan) || p.table.order == nullptr) return MELLIN_ERR_UNSUPPORTED;
@@ -924,9 +967,12 @@ int TC_FN(tc_take_error)(int *code) {
   cudaError_t err = cudaMemcpyFromSymbol(code, g_tc_error, sizeof(int));
   if (err == cudaSuccess) err = cudaMemcpyToSymbol(g_tc_error, &zero, sizeof(int));
   if (err != cudaSuccess) return fail(MELLIN_ERR_LAUNCH, std::string("device status: ") + cudaGetErrorString(err));
-#ifndef MELLIN_TAP_GROUPS
+#ifdef MELLIN_BASE_BUILD
   int other = 0;
-  const int rc = tc_take_error_taps(&other);
+  int rc = tc_take_error_taps(&other);
+  if (rc) return rc;
+  if (*code == 0) *code = other;
+  rc = tc_take_error_masked(&other);
   if (rc) return rc;
   if (*code == 0) *code = other;
 #endif

@@ -154,6 +154,20 @@ int mellin_mcorrlcorr_forward_f64(const double *x, const double *w, const double
                                   MELLIN_LAYER_GEOMETRY, double *y, void *workspace,
                                   size_t workspace_bytes, void *stream);
 
+/* forward with the step the reference's models apply around every layer fused
+ * in (models.py:386-390 length masks, :424-434 ReLU; no single reference
+ * function): y[n, :, :, oy] = oy < lens[n] ? act(bias + corr) : 0, act = ReLU
+ * when relu != 0, identity otherwise.  lens: device array of `batch` int32
+ * lengths along the linear axis (NULL: no mask).  On the tensor-core path the
+ * mask and the activation cost nothing and tiles past an utterance's end are
+ * not computed; elsewhere they are one more pass over y. */
+int mellin_mcorrlcorr_forward_masked_f32(const float *x, const float *w, const float *bias, const int *lens,
+                                         int relu, MELLIN_LAYER_GEOMETRY, float *y, void *workspace,
+                                         size_t workspace_bytes, void *stream);
+int mellin_mcorrlcorr_forward_masked_f64(const double *x, const double *w, const double *bias, const int *lens,
+                                         int relu, MELLIN_LAYER_GEOMETRY, double *y, void *workspace,
+                                         size_t workspace_bytes, void *stream);
+
 int mellin_mcorrlcorr_grad_input_f32(const float *w, const float *grad_y,
                                      MELLIN_LAYER_GEOMETRY, float *grad_x, void *workspace,
                                      size_t workspace_bytes, void *stream);

@@ -272,3 +272,39 @@ def test_bad_arguments_are_reported():
         capi.grad_weight(xx, gy, gw, None, 1, 1, (0, 1), 1, workspace=torch.empty(16, dtype=torch.uint8, device="cuda"))
     assert e.value.code == 3
     torch.cuda.synchronize()  # the context is still healthy
+
+
+MASKED_CASES = [
+    # n, ci, co, (bins, frames), kernel, d, lens
+    (5, 3, 64, (41, 300), (8, 3), (1, 1), [300, 257, 128, 40, 0]),      # narrow layer: resident weights
+    (4, 64, 128, (41, 272), (6, 3), (2, 1), [272, 129, 127, 1]),         # wide layer: streamed weights
+    (3, 5, 6, (9, 40), (3, 2), (1, 1), [40, 17, 3]),                     # CUDA-core kernels + the separate pass
+]
+
+
+@pytest.mark.parametrize("relu", [True, False])
+@pytest.mark.parametrize("case", MASKED_CASES, ids=lambda c: "n%d_ci%d_co%d" % c[:3])
+def test_fused_mask_and_relu_equal_the_separate_steps(engine, case, relu):
+    """forward_masked = mask * act(forward): bit-identical to the plain forward followed
+    by the mask and the activation (the fused epilogue touches no arithmetic)."""
+    n, ci, co, ng, nf, d, lens = case
+    rng = np.random.default_rng(n * 100 + ci)
+    x = dev(rng.standard_normal((n, ci) + ng).astype(np.float32))
+    w = dev((rng.standard_normal((co, ci) + nf) / np.sqrt(ci * nf[0] * nf[1])).astype(np.float32))
+    b = dev(rng.standard_normal(co).astype(np.float32))
+    lens_t = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    s, p, u = (1, 1), (0, 1), (1, 1)
+    nhy = ng[1] + 2 - nf[1] + 1
+    shape = (n, co, ng[0], nhy)
+    plain = torch.empty(shape, device="cuda")
+    capi.forward(x, w, b, plain, s, d, p, u)
+    expected = plain.relu() if relu else plain.clone()
+    mask = torch.arange(nhy, device="cuda")[None, :] < lens_t[:, None]
+    expected = expected * mask[:, None, None, :]
+    got = torch.full(shape, float("nan"), device="cuda")
+    capi.forward_masked(x, w, b, lens_t, relu, got, s, d, p, u)
+    assert torch.equal(got, expected)
+    if ci == 5:  # float64 goes through the generic kernel and the separate pass
+        got64 = torch.full(shape, float("nan"), device="cuda", dtype=torch.float64)
+        capi.forward_masked(x.double(), w.double(), b.double(), lens_t, relu, got64, s, d, p, u)
+        assert helpers.rel_err(got64.cpu().numpy(), expected.double().cpu().numpy()) <= F32_TOL

@@ -312,3 +312,47 @@ def test_three_layer_stack_matches_the_reference_extension(mconv):
         exact, ref32 = data[name + ".f64"], data[name + ".f32"]
         mine = helpers.rel_err(value.cpu().numpy(), exact)
         assert mine <= max(1e-5, helpers.rel_err(ref32, exact)), (name, mine)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+def test_fused_masked_layers_reproduce_the_reference_stack(mconv, dtype):
+    """The same three-layer stack through ``mcorrlcorr_masked`` (mask and ReLU
+    fused into each layer's kernel): output and gradients against the reference
+    extension's run of the unfused operators."""
+    import os
+
+    data = np.load(os.path.join(os.path.dirname(__file__), "golden", "ref_stack3.npz"))
+    dilation = ((1, 1), (2, 1), (2, 1))
+    names = ("x", "w0", "w1", "w2", "b0", "b1", "b2")
+    leaves = [torch.from_numpy(data[k]).cuda().to(dtype).requires_grad_(True) for k in names]
+    mask = torch.from_numpy(data["mask"]).cuda().to(dtype)
+    lens = mask[:, 0, 0, :].sum(dim=1).to(torch.int32)
+    h = leaves[0] * mask
+    for w, b, d in zip(leaves[1:4], leaves[4:7], dilation):
+        r = (41 - mconv.mcorr_valid_size(6, 41, 1, d[0], 0, 1), 1)
+        h = mconv.mcorrlcorr_masked(h, w, b, lens, True, (1, 1), d, (0, 1), r)
+    grads = torch.autograd.grad(h, leaves, torch.from_numpy(data["go"]).cuda().to(dtype))
+    got = dict(zip(["gx", "gw0", "gw1", "gw2", "gb0", "gb1", "gb2"], grads), y=h.detach())
+    for name, value in got.items():
+        exact, ref32 = data[name + ".f64"], data[name + ".f32"]
+        mine = helpers.rel_err(value.double().cpu().numpy(), exact)
+        bound = 1e-12 if dtype == torch.float64 else max(1e-5, helpers.rel_err(ref32, exact))
+        assert mine <= bound, (name, mine)
+
+
+def test_fused_masked_layer_without_relu_and_half(mconv):
+    x = torch.randn(3, 4, 9, 30, device="cuda", requires_grad=True)
+    w = torch.randn(5, 4, 3, 2, device="cuda", requires_grad=True)
+    b = torch.randn(5, device="cuda", requires_grad=True)
+    lens = torch.tensor([30, 11, 0], dtype=torch.int32, device="cuda")
+    y = mconv.mcorrlcorr_masked(x, w, b, lens, False)
+    plain = mconv.mcorrlcorr(x, w, b, _impl="direct")
+    mask = (torch.arange(plain.size(3), device="cuda")[None, :] < lens[:, None])[:, None, None, :]
+    assert torch.equal(y, plain * mask)
+    go = torch.randn_like(y)
+    got = torch.autograd.grad(y, [x, w, b], go)
+    exp = torch.autograd.grad(plain * mask, [x, w, b], go)
+    for a_, e_ in zip(got, exp):
+        assert helpers.rel_err(a_.cpu().numpy(), e_.cpu().numpy()) <= 1e-6
+    yh = mconv.mcorrlcorr_masked(x.half(), w.half(), b.half(), lens, True)
+    assert yh.dtype == torch.half and torch.equal(yh[2], torch.zeros_like(yh[2]))
