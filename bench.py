@@ -137,17 +137,34 @@ class ClockSampler:
 
 
 # ---------------------------------------------------------------------------------
+def _use_all_cores():
+    """torchrun exports OMP_NUM_THREADS=1 to its workers; the CPU arms are meant to use every host core they may."""
+    cores = len(os.sched_getaffinity(0))
+    os.environ["OMP_NUM_THREADS"] = str(cores)
+    try:  # in case the OpenMP runtime was initialised before the variable was set
+        import ctypes
+
+        ctypes.CDLL("libgomp.so.1").omp_set_num_threads(cores)
+    except OSError:
+        pass
+    return cores
+
+
 def run_reference(args):
     """The reference's CPU implementation of the same step on the host cores."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     import numpy as np
+
+    # torchrun exports OMP_NUM_THREADS=1 to its workers; this arm is meant to use every host core it may
+    cores = len(os.sched_getaffinity(0))
+    os.environ["OMP_NUM_THREADS"] = str(cores)
     from oracle.oracle import Oracle
 
     kind = "reference" if Oracle.reference_available() else "port"
     oracle = Oracle(kind)
-    cores = len(os.sched_getaffinity(0))
+    _use_all_cores()
     sample_batch = 2
     xs, ws, ys, r = geometry(sample_batch)
     w_ = WORKLOAD
@@ -189,6 +206,7 @@ def cpu_baseline_leg():
 
     kind = "reference" if Oracle.reference_available() else "port"
     oracle = Oracle(kind)
+    _use_all_cores()
     sample_batch = 2
     xs, ws, ys, r = geometry(sample_batch)
     w_ = WORKLOAD
