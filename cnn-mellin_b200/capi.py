@@ -25,6 +25,7 @@ OP2D = ["mellin_mconvlconv", "mellin_mcorrlcorr"]
 COL1D = ["mellin_snd2col", "mellin_col2snd"]
 COL2D = ["mellin_spec2col", "mellin_col2spec"]
 LAYER = ["mellin_mcorrlcorr_forward", "mellin_mcorrlcorr_forward_masked", "mellin_mcorrlcorr_grad_input",
+         "mellin_mcorrlcorr_grad_input_masked",
          "mellin_mcorrlcorr_grad_weight"]
 MISC = ["mellin_abi_version", "mellin_last_error", "mellin_launch_count", "mellin_clear_tables",
         "mellin_set_tensor_cores", "mellin_device_status", "mellin_mcorrlcorr_forward_workspace_bytes",
@@ -229,6 +230,18 @@ def grad_input(w, grad_y, grad_x, s, d, p, u, workspace=None):
     workspace, nbytes = _scratch(need, grad_x, workspace)
     fn = getattr(lib(), "mellin_mcorrlcorr_grad_input" + _sfx(grad_x))
     _check(fn(_p(w), _p(grad_y), *geom, _p(grad_x), _p(workspace), ctypes.c_size_t(nbytes), _stream()))
+    return grad_x
+
+
+def grad_input_masked(w, grad_y, lens, grad_x, s, d, p, u, workspace=None):
+    """grad_input for a grad_y that is zero from position lens[n] on."""
+    import torch
+
+    geom = _geometry(grad_x.shape, w.shape, grad_y.shape, s, d, p, u)
+    need = int(lib().mellin_mcorrlcorr_grad_input_workspace_bytes(*geom)) if grad_x.dtype == torch.float32 else 0
+    workspace, nbytes = _scratch(need, grad_x, workspace)
+    fn = getattr(lib(), "mellin_mcorrlcorr_grad_input_masked" + _sfx(grad_x))
+    _check(fn(_p(w), _p(grad_y), _p(lens), *geom, _p(grad_x), _p(workspace), ctypes.c_size_t(nbytes), _stream()))
     return grad_x
 
 

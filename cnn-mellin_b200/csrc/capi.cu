@@ -54,14 +54,14 @@ int check_geometry(const char *who, const Geometry2D &q, int64_t linear_divisor)
 // out = oy < lens[n] ? act(out) : 0 on a dense (N, A, nox, noy) tensor: the fused
 // epilogue as a separate pass, for the paths that do not carry it themselves
 template <typename T>
-__global__ void mask_relu_kernel(T *__restrict__ out, const int *__restrict__ lens, int relu, long long total,
-                                 long long per_utterance, int noy) {
+__global__ void mask_relu_kernel(T *__restrict__ out, const int *__restrict__ lens, int len_scale, int len_offset,
+                                 int relu, long long total, long long per_utterance, int noy) {
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
     const int n = (int)(i / per_utterance), oy = (int)(i % noy);
     T v = out[i];
     if (relu && v < T(0)) v = T(0);
-    if (lens != nullptr && oy >= lens[n]) v = T(0);
+    if (lens != nullptr && oy >= lens[n] * len_scale + len_offset) v = T(0);
     out[i] = v;
   }
 }
@@ -71,7 +71,8 @@ int launch_mask_relu(const DirectProblem<T> &p, cudaStream_t stream) {
   const long long per_utterance = (long long)p.A * p.nox * p.noy, total = per_utterance * p.N;
   if (total == 0) return MELLIN_OK;
   const int blocks = (int)std::min<long long>((total + 255) / 256, 148 * 16);
-  mask_relu_kernel<T><<<blocks, 256, 0, stream>>>(p.out, p.lens, p.relu, total, per_utterance, p.noy);
+  mask_relu_kernel<T><<<blocks, 256, 0, stream>>>(p.out, p.lens, p.len_scale, p.len_offset, p.relu, total,
+                                                  per_utterance, p.noy);
   const cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return fail(MELLIN_ERR_LAUNCH, std::string("mask_relu_kernel: ") + cudaGetErrorString(err));
   count_launch();
@@ -161,7 +162,7 @@ int op2d(const char *who, Relation rel, const T *f, const T *g, const Geometry2D
 
 template <typename T>
 int grad_input(const char *who, const T *w, const T *go, const Geometry2D &q, T *gx, void *workspace,
-               size_t workspace_bytes, void *stream) {
+               size_t workspace_bytes, void *stream, const int *lens = nullptr) {
   int rc = check_geometry(who, q, q.sy);
   if (rc) return rc;
   if (q.batch * q.c_in * q.ngx * q.ngy == 0) return MELLIN_OK;
@@ -184,6 +185,12 @@ int grad_input(const char *who, const T *w, const T *go, const Geometry2D &q, T 
   // s hy + d fy - p = u gy   =>   hy = (u gy - d fy + p) / s
   p.Ay = (int)q.uy, p.By = -(int)q.dy, p.Cy = (int)q.py, p.Dy = (int)q.sy;
   p.accumulate = false;
+  if (lens != nullptr && q.uy == 1 && p.A > 4) {
+    // grad_y is zero from position lens[n] on, so grad_x is zero from this position on: the last
+    // input position any output below lens[n] reads is s (len - 1) - p + d (nfy - 1)
+    p.lens = lens, p.len_scale = (int)q.sy;
+    p.len_offset = (int)(-q.sy - q.py + q.dy * (q.nfy > 0 ? q.nfy - 1 : 0) + 1);
+  }
   return dispatch_direct(p, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
@@ -336,6 +343,12 @@ int64_t mellin_lcorr_support_size(int64_t ng, int64_t s, int64_t p, int64_t u) {
                                          void *stream) {                                              \
     return grad_input<T>("mcorrlcorr_grad_input", w, grad_y, GEOM_FROM_LAYER, grad_x, workspace,      \
                          workspace_bytes, stream);                                                    \
+  }                                                                                                   \
+  int mellin_mcorrlcorr_grad_input_masked_##sfx(const T *w, const T *grad_y, const int *lens,        \
+                                                MELLIN_LAYER_GEOMETRY, T *grad_x, void *workspace,    \
+                                                size_t workspace_bytes, void *stream) {               \
+    return grad_input<T>("mcorrlcorr_grad_input_masked", w, grad_y, GEOM_FROM_LAYER, grad_x,          \
+                         workspace, workspace_bytes, stream, lens);                                   \
   }                                                                                                   \
   int mellin_mcorrlcorr_grad_weight_##sfx(const T *x, const T *grad_y, MELLIN_LAYER_GEOMETRY,         \
                                           T *grad_w, T *grad_b, void *workspace,                      \

@@ -58,6 +58,7 @@ struct DirectProblem {
   bool accumulate = false;
   // fused epilogue (layer-level forward only): out = (oy < lens[n]) ? act(value) : 0
   const int *lens = nullptr;  // device array of N lengths along the linear axis, or null
+  int len_scale = 1, len_offset = 0;  // the bound used is lens[n] * len_scale + len_offset
   int relu = 0;
 };
 

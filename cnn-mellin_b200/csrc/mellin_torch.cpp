@@ -365,13 +365,13 @@ Tensor call_col2spec(const Tensor &i, at::IntArrayRef k, at::IntArrayRef s, at::
 // 1-D tensors are viewed with a trailing singleton linear axis.
 std::vector<Tensor> layer_backward(const Tensor &grad_out_in, const Tensor &input_in, const Tensor &weight_in,
                                    bool has_bias, Pair s, Pair d, Pair p, Pair u, bool need_input, bool need_weight,
-                                   bool need_bias) {
+                                   bool need_bias, const Tensor *lens = nullptr) {
   const bool one_d = input_in.dim() == 3;
   c10::cuda::CUDAGuard guard(weight_in.device());
   if (weight_in.scalar_type() == at::kHalf) {
     std::vector<Tensor> wide = layer_backward(grad_out_in.to(at::kFloat), input_in.to(at::kFloat),
                                               weight_in.to(at::kFloat), has_bias, s, d, p, u, need_input, need_weight,
-                                              need_bias);
+                                              need_bias, lens);
     for (Tensor &t : wide)
       if (t.defined()) t = t.to(at::kHalf);
     return wide;
@@ -386,10 +386,21 @@ std::vector<Tensor> layer_backward(const Tensor &grad_out_in, const Tensor &inpu
     gi = at::empty_like(x);
     const size_t gi_bytes = f64 ? 0 : mellin_mcorrlcorr_grad_input_workspace_bytes(LAYER_ARGS(q));
     Tensor gi_ws = at::empty({static_cast<int64_t>(gi_bytes ? gi_bytes : 16)}, w.options().dtype(at::kByte));
-    int rc = f64 ? mellin_mcorrlcorr_grad_input_f64(w.data_ptr<double>(), go.data_ptr<double>(), LAYER_ARGS(q),
-                                                     gi.data_ptr<double>(), nullptr, 0, stream)
-                 : mellin_mcorrlcorr_grad_input_f32(w.data_ptr<float>(), go.data_ptr<float>(), LAYER_ARGS(q),
-                                                     gi.data_ptr<float>(), gi_ws.data_ptr(), gi_bytes, stream);
+    int rc;
+    if (lens != nullptr && !one_d) {
+      // grad_out is zero past every utterance's length: tiles that can only hold zeros are skipped
+      rc = f64 ? mellin_mcorrlcorr_grad_input_masked_f64(w.data_ptr<double>(), go.data_ptr<double>(),
+                                                         lens->data_ptr<int>(), LAYER_ARGS(q), gi.data_ptr<double>(),
+                                                         nullptr, 0, stream)
+               : mellin_mcorrlcorr_grad_input_masked_f32(w.data_ptr<float>(), go.data_ptr<float>(),
+                                                         lens->data_ptr<int>(), LAYER_ARGS(q), gi.data_ptr<float>(),
+                                                         gi_ws.data_ptr(), gi_bytes, stream);
+    } else {
+      rc = f64 ? mellin_mcorrlcorr_grad_input_f64(w.data_ptr<double>(), go.data_ptr<double>(), LAYER_ARGS(q),
+                                                   gi.data_ptr<double>(), nullptr, 0, stream)
+               : mellin_mcorrlcorr_grad_input_f32(w.data_ptr<float>(), go.data_ptr<float>(), LAYER_ARGS(q),
+                                                   gi.data_ptr<float>(), gi_ws.data_ptr(), gi_bytes, stream);
+    }
     check_status(rc, "mcorrlcorr_grad_input");
   }
   if (need_weight || (need_bias && has_bias)) {
@@ -504,7 +515,7 @@ class MCorrLCorrMaskedFunction : public torch::autograd::Function<MCorrLCorrMask
                               pair_of(ctx->saved_data["d"].toIntVector(), c, "d"),
                               pair_of(ctx->saved_data["p"].toIntVector(), c, "p"),
                               pair_of(ctx->saved_data["u"].toIntVector(), c, "u"), ctx->needs_input_grad(0),
-                              ctx->needs_input_grad(1), has_bias && ctx->needs_input_grad(2));
+                              ctx->needs_input_grad(1), has_bias && ctx->needs_input_grad(2), &lens);
     return {out[0], out[1], out[2], Tensor(), Tensor(), Tensor(), Tensor(), Tensor(), Tensor(), Tensor()};
   }
 };

@@ -97,7 +97,8 @@ struct TcParams {
   int TG, G;     // linear taps per stage and number of such tap groups: a block of KB rows is staged G times,
                  // each time with the weights of TG taps (weights of many taps do not fit a stage)
 #ifdef MELLIN_MASKED
-  const int *lens;  // per utterance: outputs at positions >= lens[n] are zero
+  const int *lens;  // per utterance: outputs at positions >= lens[n] * len_scale + len_offset are zero
+  int len_scale, len_offset;
   int relu;
 #endif
   int table_in_smem;  // 1: row offsets, entries and row order are cached in shared memory
@@ -334,7 +335,7 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map,
   int *order_s = reinterpret_cast<int *>(smem + kOrderOffset);
 #ifdef MELLIN_MASKED
   int *lens_s = reinterpret_cast<int *>(smem + kLensOffset);
-  for (int i = threadIdx.x; i < p.N; i += kThreads) lens_s[i] = p.lens[i];
+  for (int i = threadIdx.x; i < p.N; i += kThreads) lens_s[i] = p.lens[i] * p.len_scale + p.len_offset;
 #endif
   int2 *ent_s = reinterpret_cast<int2 *>(smem + kEntriesOffset);
   float *bias_s = reinterpret_cast<float *>(smem + kBiasOffset);
@@ -746,7 +747,7 @@ bool plan_tc_direct(const DirectProblem<float> &p, TcPlan &plan) {
   TcParams &q = plan.params;
 #ifdef MELLIN_MASKED
   if (p.lens == nullptr || p.N > kMaxLens) return false;
-  q.lens = p.lens, q.relu = p.relu;
+  q.lens = p.lens, q.relu = p.relu, q.len_scale = p.len_scale, q.len_offset = p.len_offset;
 #endif
   q.bias = p.accumulate ? nullptr : p.bias, q.out = p.out;
   q.table_in_smem = (p.nox <= kMaxTableRows && p.table.num_entries <= kMaxTableEntries) ? 1 : 0;

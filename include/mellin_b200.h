@@ -168,6 +168,16 @@ int mellin_mcorrlcorr_forward_masked_f64(const double *x, const double *w, const
                                          int relu, MELLIN_LAYER_GEOMETRY, double *y, void *workspace,
                                          size_t workspace_bytes, void *stream);
 
+/* grad_input for a grad_y that is zero from position lens[n] on (the gradient of
+ * a masked layer): the same result as mellin_mcorrlcorr_grad_input_*, but the
+ * tensor-core path does not compute the tiles that can only hold zeros. */
+int mellin_mcorrlcorr_grad_input_masked_f32(const float *w, const float *grad_y, const int *lens,
+                                            MELLIN_LAYER_GEOMETRY, float *grad_x, void *workspace,
+                                            size_t workspace_bytes, void *stream);
+int mellin_mcorrlcorr_grad_input_masked_f64(const double *w, const double *grad_y, const int *lens,
+                                            MELLIN_LAYER_GEOMETRY, double *grad_x, void *workspace,
+                                            size_t workspace_bytes, void *stream);
+
 int mellin_mcorrlcorr_grad_input_f32(const float *w, const float *grad_y,
                                      MELLIN_LAYER_GEOMETRY, float *grad_x, void *workspace,
                                      size_t workspace_bytes, void *stream);

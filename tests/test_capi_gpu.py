@@ -308,3 +308,22 @@ def test_fused_mask_and_relu_equal_the_separate_steps(engine, case, relu):
         got64 = torch.full(shape, float("nan"), device="cuda", dtype=torch.float64)
         capi.forward_masked(x.double(), w.double(), b.double(), lens_t, relu, got64, s, d, p, u)
         assert helpers.rel_err(got64.cpu().numpy(), expected.double().cpu().numpy()) <= F32_TOL
+
+
+@pytest.mark.parametrize("case", MASKED_CASES[:2] + [(4, 128, 64, (41, 272), (6, 3), (2, 1), [272, 130, 128, 0])],
+                         ids=lambda c: "n%d_ci%d_co%d" % c[:3])
+def test_masked_grad_input_equals_the_plain_one_on_masked_gradients(engine, case):
+    """grad_input_masked skips tiles that can only hold zeros: same bits as grad_input."""
+    n, ci, co, ng, nf, d, lens = case
+    rng = np.random.default_rng(n * 7 + co)
+    w = dev((rng.standard_normal((co, ci) + nf) / np.sqrt(ci * nf[0] * nf[1])).astype(np.float32))
+    lens_t = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    s, p, u = (1, 1), (0, 1), (1, 1)
+    nhy = ng[1] + 2 - nf[1] + 1
+    go = dev(rng.standard_normal((n, co, ng[0], nhy)).astype(np.float32))
+    go = go * (torch.arange(nhy, device="cuda")[None, :] < lens_t[:, None])[:, None, None, :]
+    plain = torch.empty((n, ci) + ng, device="cuda")
+    capi.grad_input(w, go, plain, s, d, p, u)
+    got = torch.full((n, ci) + ng, float("nan"), device="cuda")
+    capi.grad_input_masked(w, go, lens_t, got, s, d, p, u)
+    assert torch.equal(got, plain)
