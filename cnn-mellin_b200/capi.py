@@ -26,7 +26,7 @@ COL1D = ["mellin_snd2col", "mellin_col2snd"]
 COL2D = ["mellin_spec2col", "mellin_col2spec"]
 LAYER = ["mellin_mcorrlcorr_forward", "mellin_mcorrlcorr_forward_masked", "mellin_mcorrlcorr_grad_input",
          "mellin_mcorrlcorr_grad_input_masked",
-         "mellin_mcorrlcorr_grad_weight"]
+         "mellin_mcorrlcorr_grad_weight", "mellin_mcorrlcorr_grad_weight_masked"]
 MISC = ["mellin_abi_version", "mellin_last_error", "mellin_launch_count", "mellin_clear_tables",
         "mellin_set_tensor_cores", "mellin_device_status", "mellin_mcorrlcorr_forward_workspace_bytes",
         "mellin_mcorrlcorr_grad_input_workspace_bytes", "mellin_mcorrlcorr_grad_weight_noalloc_f32",
@@ -257,7 +257,8 @@ def grad_weight_workspace_bytes(x_shape, w_shape, y_shape, s, d, p, u):
     return int(lib().mellin_mcorrlcorr_grad_weight_workspace_bytes(*_geometry(x_shape, w_shape, y_shape, s, d, p, u)))
 
 
-def grad_weight(x, grad_y, grad_w, grad_b, s, d, p, u, workspace=None):
+def grad_weight(x, grad_y, grad_w, grad_b, s, d, p, u, workspace=None, lens=None):
+    """lens: int32 device tensor promising grad_y is zero from position lens[n] on (masked entry point)."""
     import torch
 
     geom = _geometry(x.shape, grad_w.shape, grad_y.shape, s, d, p, u)
@@ -265,6 +266,11 @@ def grad_weight(x, grad_y, grad_w, grad_b, s, d, p, u, workspace=None):
     if workspace is None and need:
         workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
     nbytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
+    if lens is not None:
+        fn = getattr(lib(), "mellin_mcorrlcorr_grad_weight_masked" + _sfx(grad_w))
+        _check(fn(_p(x), _p(grad_y), _p(lens), *geom, _p(grad_w), _p(grad_b), _p(workspace), ctypes.c_size_t(nbytes),
+                  _stream()))
+        return grad_w, grad_b
     fn = getattr(lib(), "mellin_mcorrlcorr_grad_weight" + _sfx(grad_w))
     _check(fn(_p(x), _p(grad_y), *geom, _p(grad_w), _p(grad_b), _p(workspace), ctypes.c_size_t(nbytes), _stream()))
     return grad_w, grad_b

@@ -127,6 +127,7 @@ DirectProblem<float> inner_direct(const DirectProblem<float> &p, const float *xt
 GradWProblem<float> inner_gradw(const GradWProblem<float> &p, const float *xt, const float *got) {
   GradWProblem<float> q = p;
   q.in = xt, q.go = got;
+  q.lens = nullptr;  // the linear axis is the batch here
   q.N = 1, q.niy = p.N, q.noy = p.N;
   q.Ay = 1, q.By = 1, q.Cy = 0, q.Dy = 1;
   return q;

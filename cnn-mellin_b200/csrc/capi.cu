@@ -214,7 +214,7 @@ int make_gradw_problem(const char *who, const Geometry2D &q, GradWProblem<T> *p,
 
 template <typename T>
 int grad_weight(const char *who, const T *x, const T *go, const Geometry2D &q, T *gw, T *gb, void *workspace,
-                size_t workspace_bytes, void *stream) {
+                size_t workspace_bytes, void *stream, const int *lens = nullptr) {
   GradWProblem<T> p;
   int rc = make_gradw_problem(who, q, &p, true);
   if (rc) return rc;
@@ -226,6 +226,7 @@ int grad_weight(const char *who, const T *x, const T *go, const Geometry2D &q, T
   if (gb != nullptr && has_terms && go == nullptr)
     return fail(MELLIN_ERR_BAD_ARGUMENT, std::string(who) + ": null grad_y");
   p.in = x, p.go = go, p.gw = gw, p.gb = gb;
+  p.lens = q.nhy > 1 ? lens : nullptr;
   if (gw_elems == 0 && (gb == nullptr || q.c_out == 0)) return MELLIN_OK;
   return launch_gradw<T>(p, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
@@ -355,6 +356,13 @@ int64_t mellin_lcorr_support_size(int64_t ng, int64_t s, int64_t p, int64_t u) {
                                           size_t workspace_bytes, void *stream) {                     \
     return grad_weight<T>("mcorrlcorr_grad_weight", x, grad_y, GEOM_FROM_LAYER, grad_w, grad_b,       \
                           workspace, workspace_bytes, stream);                                        \
+  }                                                                                                   \
+  int mellin_mcorrlcorr_grad_weight_masked_##sfx(const T *x, const T *grad_y, const int *lens,        \
+                                                 MELLIN_LAYER_GEOMETRY, T *grad_w, T *grad_b,         \
+                                                 void *workspace, size_t workspace_bytes,             \
+                                                 void *stream) {                                      \
+    return grad_weight<T>("mcorrlcorr_grad_weight_masked", x, grad_y, GEOM_FROM_LAYER, grad_w,        \
+                          grad_b, workspace, workspace_bytes, stream, lens);                          \
   }
 
 DEFINE_OPS(float, f32)

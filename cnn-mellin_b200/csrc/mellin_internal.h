@@ -75,6 +75,7 @@ struct GradWProblem {
   T *gb = nullptr;         // (A) or null
   DeviceTable table;       // rows = kx, entries (ox | flags, ix)
   DeviceTable table_h;     // the same triples by output row: rows = ox, entries (kx, ix)
+  const int *lens = nullptr;  // optional: grad_y is zero from position lens[n] on (device array of N)
   int N = 0, A = 0, B = 0;
   int nkx = 0, nky = 0, nix = 0, niy = 0, nox = 0, noy = 0;
   int Ay = 1, By = 1, Cy = 0, Dy = 1;

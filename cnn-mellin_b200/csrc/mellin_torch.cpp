@@ -409,12 +409,21 @@ std::vector<Tensor> layer_backward(const Tensor &grad_out_in, const Tensor &inpu
     const size_t bytes = f64 ? 0 : mellin_mcorrlcorr_grad_weight_workspace_bytes(LAYER_ARGS(q));
     Tensor ws;
     if (bytes) ws = at::empty({static_cast<int64_t>(bytes)}, w.options().dtype(at::kByte));
-    int rc = f64 ? mellin_mcorrlcorr_grad_weight_f64(x.data_ptr<double>(), go.data_ptr<double>(), LAYER_ARGS(q),
-                                                      gw.data_ptr<double>(), gb.defined() ? gb.data_ptr<double>() : nullptr,
-                                                      nullptr, 0, stream)
-                 : mellin_mcorrlcorr_grad_weight_f32(x.data_ptr<float>(), go.data_ptr<float>(), LAYER_ARGS(q),
-                                                      gw.data_ptr<float>(), gb.defined() ? gb.data_ptr<float>() : nullptr,
-                                                      bytes ? ws.data_ptr() : nullptr, bytes, stream);
+    int rc;
+    if (lens != nullptr && !one_d && !f64) {
+      // grad_out is zero past every utterance's length: each utterance's reduction stops there
+      rc = mellin_mcorrlcorr_grad_weight_masked_f32(x.data_ptr<float>(), go.data_ptr<float>(), lens->data_ptr<int>(),
+                                                    LAYER_ARGS(q), gw.data_ptr<float>(),
+                                                    gb.defined() ? gb.data_ptr<float>() : nullptr,
+                                                    bytes ? ws.data_ptr() : nullptr, bytes, stream);
+    } else {
+      rc = f64 ? mellin_mcorrlcorr_grad_weight_f64(x.data_ptr<double>(), go.data_ptr<double>(), LAYER_ARGS(q),
+                                                        gw.data_ptr<double>(), gb.defined() ? gb.data_ptr<double>() : nullptr,
+                                                        nullptr, 0, stream)
+                   : mellin_mcorrlcorr_grad_weight_f32(x.data_ptr<float>(), go.data_ptr<float>(), LAYER_ARGS(q),
+                                                        gw.data_ptr<float>(), gb.defined() ? gb.data_ptr<float>() : nullptr,
+                                                        bytes ? ws.data_ptr() : nullptr, bytes, stream);
+    }
     check_status(rc, "mcorrlcorr_grad_weight");
     if (!need_weight) gw = Tensor();
   }

@@ -68,6 +68,7 @@ __host__ __device__ constexpr uint32_t x_slab(int nky) { return (uint32_t)(nky *
 struct GwParams {
   const int32_t *row_ptr;  // by-kx table
   const int2 *entries;
+  const int *lens;         // per utterance: grad_y is zero from this position on (null: no such promise)
   float *part_w;           // [slice][tap slot][B][A], slices of tap kx at prefix[kx] ...
   float *part_b;           // [slice][A] or null
   int N, A, B, nkx, nky, noy;
@@ -165,7 +166,10 @@ tc_gradw_kernel(const GwParams p, const __grid_constant__ CUtensorMap go_map, co
   const bool want_bias = p.part_b != nullptr && bt == 0;
 #define ITEM_ENTRY(i) (e0 + ((i) / p.chunks) % ne)
 #define ITEM_FIRST_STAGE(i) (((i) % p.chunks) * p.chunk_stages)
-#define ITEM_END_STAGE(i) min(p.stages_per_row, ITEM_FIRST_STAGE(i) + p.chunk_stages)
+// with per-utterance lengths (grad_y is zero from position lens[n] on) a row ends at its utterance's last stage
+#define ITEM_ROW_STAGES(i) \
+  (p.lens == nullptr ? p.stages_per_row : min(p.stages_per_row, (p.lens[(i) / (ne * p.chunks)] + kKB - 1) / kKB))
+#define ITEM_END_STAGE(i) max(ITEM_FIRST_STAGE(i), min(ITEM_ROW_STAGES(i), ITEM_FIRST_STAGE(i) + p.chunk_stages))
 
   if (tid == 0) {
     for (int s = 0; s < kRawStages; ++s) {
@@ -460,6 +464,7 @@ tc_gradw_kernel(const GwParams p, const __grid_constant__ CUtensorMap go_map, co
 #undef ITEM_ENTRY
 #undef ITEM_FIRST_STAGE
 #undef ITEM_END_STAGE
+#undef ITEM_ROW_STAGES
 }
 
 // gw[a, b, kx, ky] = sum over the slices of tap kx; gb[a] = sum over all slices.
@@ -523,6 +528,7 @@ bool plan_tc_gradw(const GradWProblem<float> &p, int g0, int nky, GwPlan &plan) 
   GwParams &q = plan.params;
   q.profile = 0;
   q.row_ptr = p.table.row_ptr, q.entries = p.table.entries;
+  q.lens = p.lens;
   q.N = p.N, q.A = p.A, q.B = p.B, q.nkx = p.nkx, q.nky = nky, q.noy = p.noy;
   q.g0 = g0, q.nky_total = p.nky;
   q.absBy = absBy, q.By = p.By;

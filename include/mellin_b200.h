@@ -193,6 +193,16 @@ size_t mellin_mcorrlcorr_grad_weight_workspace_bytes(MELLIN_LAYER_GEOMETRY);
 /* grad_b may be NULL.  workspace must hold at least
  * mellin_mcorrlcorr_grad_weight_workspace_bytes(...) bytes, 256-byte aligned;
  * it may be NULL only if that answer is 0.  Its contents are clobbered. */
+/* grad_weight for a grad_y that is zero from position lens[n] on: the same
+ * result as mellin_mcorrlcorr_grad_weight_*; the tensor-core kernel stops each
+ * utterance's reduction at its length. */
+int mellin_mcorrlcorr_grad_weight_masked_f32(const float *x, const float *grad_y, const int *lens,
+                                             MELLIN_LAYER_GEOMETRY, float *grad_w, float *grad_b,
+                                             void *workspace, size_t workspace_bytes, void *stream);
+int mellin_mcorrlcorr_grad_weight_masked_f64(const double *x, const double *grad_y, const int *lens,
+                                             MELLIN_LAYER_GEOMETRY, double *grad_w, double *grad_b,
+                                             void *workspace, size_t workspace_bytes, void *stream);
+
 int mellin_mcorrlcorr_grad_weight_f32(const float *x, const float *grad_y,
                                       MELLIN_LAYER_GEOMETRY, float *grad_w, float *grad_b,
                                       void *workspace, size_t workspace_bytes, void *stream);

@@ -327,3 +327,26 @@ def test_masked_grad_input_equals_the_plain_one_on_masked_gradients(engine, case
     got = torch.full((n, ci) + ng, float("nan"), device="cuda")
     capi.grad_input_masked(w, go, lens_t, got, s, d, p, u)
     assert torch.equal(got, plain)
+
+
+@pytest.mark.parametrize("case", [MASKED_CASES[1], (4, 128, 64, (41, 272), (6, 3), (2, 1), [272, 130, 16, 0]),
+                                  (3, 20, 40, (12, 50), (3, 2), (1, 1), [49, 17, 30])],
+                         ids=lambda c: "n%d_ci%d_co%d" % c[:3])
+def test_masked_grad_weight_equals_the_plain_one_on_masked_gradients(engine, case):
+    """The masked weight gradient stops each utterance's reduction at its length: the terms it
+    leaves out are exact zeros, so it agrees with grad_weight to rounding of a different
+    summation split (the slices' work is divided differently)."""
+    n, ci, co, ng, nf, d, lens = case
+    rng = np.random.default_rng(n * 11 + co)
+    x = dev(rng.standard_normal((n, ci) + ng).astype(np.float32))
+    lens_t = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    s, p, u = (1, 1), (0, 1), (1, 1)
+    nhy = ng[1] + 2 - nf[1] + 1
+    go = dev(rng.standard_normal((n, co, ng[0], nhy)).astype(np.float32))
+    go = go * (torch.arange(nhy, device="cuda")[None, :] < lens_t[:, None])[:, None, None, :]
+    gw0, gb0 = torch.empty((co, ci) + nf, device="cuda"), torch.empty(co, device="cuda")
+    capi.grad_weight(x, go, gw0, gb0, s, d, p, u)
+    gw1, gb1 = torch.full_like(gw0, float("nan")), torch.full_like(gb0, float("nan"))
+    capi.grad_weight(x, go, gw1, gb1, s, d, p, u, lens=lens_t)
+    assert helpers.rel_err(gw1.cpu().numpy(), gw0.cpu().numpy()) <= 2e-6
+    assert helpers.rel_err(gb1.cpu().numpy(), gb0.cpu().numpy()) <= 2e-6
