@@ -240,7 +240,8 @@ gradw_rows_tma_kernel(const GradWProblem<float> p, const RowsTiling t, float *__
   constexpr int BN = B * NKY;
   constexpr int kSlot = x_slot_floats(B);
   constexpr int kStageFloats = kTA * kGoPitch + kMaxKx * kSlot;
-  constexpr int kWin = (LEAD + 8 + NKY - 1 + 3) / 4;  // float4 loads per window
+  constexpr int kStep = 16;  // positions per inner step
+  constexpr int kWin = (LEAD + kStep + NKY - 1 + 3) / 4;  // float4 loads per window
   extern __shared__ __align__(1024) float tile_smem[];
   float *smem = tile_smem;
   __shared__ uint64_t full[kStages];
@@ -305,11 +306,15 @@ gradw_rows_tma_kernel(const GradWProblem<float> p, const RowsTiling t, float *__
     const float *gos = smem + stage * kStageFloats + co_l * kGoPitch;
     const float *xs = smem + stage * kStageFloats + kTA * kGoPitch;
 #pragma unroll 1
-    for (int yo = 8 * q; yo < kTK && yo < valid; yo += 32) {
-      const float4 ga = *reinterpret_cast<const float4 *>(gos + yo);
-      const float4 gb4 = *reinterpret_cast<const float4 *>(gos + yo + 4);
-      const float g[8] = {ga.x, ga.y, ga.z, ga.w, gb4.x, gb4.y, gb4.z, gb4.w};
-      bsum += ((g[0] + g[1]) + (g[2] + g[3])) + ((g[4] + g[5]) + (g[6] + g[7]));
+    for (int yo = kStep * q; yo < kTK && yo < valid; yo += 4 * kStep) {
+      float g[kStep];
+#pragma unroll
+      for (int i = 0; i < kStep / 4; ++i) {
+        const float4 v = *reinterpret_cast<const float4 *>(gos + yo + 4 * i);
+        g[4 * i] = v.x, g[4 * i + 1] = v.y, g[4 * i + 2] = v.z, g[4 * i + 3] = v.w;
+      }
+#pragma unroll
+      for (int i = 0; i < kStep; i += 4) bsum += (g[i] + g[i + 1]) + (g[i + 2] + g[i + 3]);
 #pragma unroll
       for (int kx = 0; kx < kMaxKx; ++kx) {
         if (!((mask >> kx) & 1u)) continue;
@@ -326,7 +331,7 @@ gradw_rows_tma_kernel(const GradWProblem<float> p, const RowsTiling t, float *__
           for (int k = 0; k < NKY; ++k) {
             float s = acc[kx][b * NKY + k];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) s = fmaf(g[j], xw[LEAD + j + k], s);
+            for (int j = 0; j < kStep; ++j) s = fmaf(g[j], xw[LEAD + j + k], s);
             acc[kx][b * NKY + k] = s;
           }
         }
