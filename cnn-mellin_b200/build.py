@@ -16,15 +16,16 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIBDIR = os.path.join(HERE, "lib")
+OBJDIR = os.path.join(HERE, "build")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 CAPI_SO = os.path.join(LIBDIR, "libmellin_b200.so")
 TORCH_SO = os.path.join(LIBDIR, "mellin_torch.so")
 
 CAPI_SOURCES = ["capi.cu", "kernels.cu", "tc_direct.cu", "tc_direct_taps.cu", "tc_direct_masked.cu", "tc_gradw.cu", "batch_inner.cu", "gradw_rows.cu", "direct_rows.cu", "static_scratch.cu", "table_cache.cu", "index_map.cpp"]
-CAPI_HEADERS = ["mellin_internal.h", "index_map.h", "tc_ptx.cuh"]
+CAPI_HEADERS = ["mellin_internal.h", "index_map.h", "tc_ptx.cuh", "tuning_hooks.h"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
-    "-lineinfo", "-O3", "-std=c++17", "--use_fast_math=false",
+    "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-shared",
 ]
 
@@ -50,17 +51,34 @@ def nvcc_path():
     return cand
 
 
+def _compile_object(args):
+    src, obj, flags = args
+    _run([nvcc_path()] + flags + ["-c", src, "-o", obj])
+    return obj
+
+
 def build_capi(force=False, verbose_ptxas=False):
+    """Compile every source to its own object (in parallel) and link them."""
+    from concurrent.futures import ThreadPoolExecutor
+
     srcs = [os.path.join(CSRC, s) for s in CAPI_SOURCES]
-    deps = srcs + [os.path.join(CSRC, h) for h in CAPI_HEADERS] + [os.path.join(INCLUDE, "mellin_b200.h")]
-    if not force and _fresh(CAPI_SO, deps):
+    headers = [os.path.join(CSRC, h) for h in CAPI_HEADERS] + [os.path.join(INCLUDE, "mellin_b200.h")]
+    if not force and _fresh(CAPI_SO, srcs + headers):
         return CAPI_SO
     os.makedirs(LIBDIR, exist_ok=True)
-    flags = [f for f in NVCC_FLAGS if not f.startswith("--use_fast_math")]
-    cmd = [nvcc_path()] + flags + (["-Xptxas", "-v"] if verbose_ptxas else []) + ["-o", CAPI_SO] + srcs
-    out = _run(cmd)
-    if verbose_ptxas:
-        print(out)
+    os.makedirs(OBJDIR, exist_ok=True)
+    flags = [f for f in NVCC_FLAGS if f != "-shared"] + (["-Xptxas", "-v"] if verbose_ptxas else [])
+    jobs, objs = [], []
+    for src in srcs:
+        obj = os.path.join(OBJDIR, os.path.splitext(os.path.basename(src))[0] + ".o")
+        objs.append(obj)
+        # tc_direct_taps.cu / tc_direct_masked.cu include tc_direct.cu
+        deps = [src] + headers + ([os.path.join(CSRC, "tc_direct.cu")] if "tc_direct_" in src else [])
+        if force or not _fresh(obj, deps):
+            jobs.append((src, obj, flags))
+    with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as pool:
+        list(pool.map(_compile_object, jobs))
+    _run([nvcc_path(), "-shared", "-o", CAPI_SO] + objs + ["-gencode", "arch=compute_100a,code=sm_100a"])
     return CAPI_SO
 
 

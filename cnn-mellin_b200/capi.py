@@ -30,8 +30,8 @@ LAYER = ["mellin_mcorrlcorr_forward", "mellin_mcorrlcorr_forward_masked", "melli
 MISC = ["mellin_abi_version", "mellin_last_error", "mellin_launch_count", "mellin_clear_tables",
         "mellin_set_tensor_cores", "mellin_device_status", "mellin_mcorrlcorr_forward_workspace_bytes",
         "mellin_mcorrlcorr_grad_input_workspace_bytes", "mellin_mcorrlcorr_grad_weight_noalloc_f32",
-        "mellin_mcorrlcorr_grad_weight_workspace_bytes", "mellin_index_map_build", "mellin_tc_profile",
-        "mellin_tc_gradw_profile"]
+        "mellin_mcorrlcorr_grad_weight_workspace_bytes", "mellin_index_map_build",
+        "mellin_selftest_unarmed_wait"]
 
 
 def exported_symbols():
@@ -173,8 +173,13 @@ def set_tensor_cores(enable):
     return int(lib().mellin_set_tensor_cores(_INT(1 if enable else 0)))
 
 
+def selftest_unarmed_wait():
+    """Launch the bounded-wait self-test: device_status() must report 202 afterwards."""
+    _check(lib().mellin_selftest_unarmed_wait(_stream()))
+
+
 def device_status():
-    """Synchronise and return the tensor-core kernels' timeout code (0 = healthy)."""
+    """Synchronise and return the kernels' timeout code (0 = healthy)."""
     code = _INT(0)
     _check(lib().mellin_device_status(ctypes.byref(code)))
     return code.value

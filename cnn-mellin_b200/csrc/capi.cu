@@ -8,6 +8,7 @@
 
 #include "../../include/mellin_b200.h"
 #include "mellin_internal.h"
+#include "tuning_hooks.h"
 
 namespace mellin {
 int tc_read_prof(long long *out);
@@ -70,7 +71,7 @@ template <typename T>
 int launch_mask_relu(const DirectProblem<T> &p, cudaStream_t stream) {
   const long long per_utterance = (long long)p.A * p.nox * p.noy, total = per_utterance * p.N;
   if (total == 0) return MELLIN_OK;
-  const int blocks = (int)std::min<long long>((total + 255) / 256, 148 * 16);
+  const int blocks = (int)std::min<long long>((total + 255) / 256, (long long)sm_count() * 16);
   mask_relu_kernel<T><<<blocks, 256, 0, stream>>>(p.out, p.lens, p.len_scale, p.len_offset, p.relu, total,
                                                   per_utterance, p.noy);
   const cudaError_t err = cudaGetLastError();
@@ -368,8 +369,10 @@ int64_t mellin_lcorr_support_size(int64_t ng, int64_t s, int64_t p, int64_t u) {
 DEFINE_OPS(float, f32)
 DEFINE_OPS(double, f64)
 
+#ifdef MELLIN_TUNING_HOOKS
 int mellin_tc_profile(long long *out) { return mellin::tc_read_prof(out); }
 int mellin_tc_gradw_profile(long long *out) { return mellin::tc_gradw_read_prof(out); }
+#endif
 int mellin_set_tensor_cores(int enable) { return set_tensor_cores(enable); }
 int mellin_device_status(int *code) {
   if (code == nullptr) return fail(MELLIN_ERR_BAD_ARGUMENT, "device_status: null pointer");
@@ -377,9 +380,18 @@ int mellin_device_status(int *code) {
   if (rc) return rc;
   int gw_code = 0;
   rc = tc_gradw_take_error(&gw_code);
-  if (rc == MELLIN_OK && *code == 0 && gw_code != 0) *code = 100 + gw_code;
+  if (rc) return rc;
+  if (*code == 0 && gw_code != 0) *code = 100 + gw_code;
+  int rows_code = 0;
+  rc = gradw_rows_take_error(&rows_code);
+  if (rc) return rc;
+  if (*code == 0 && rows_code != 0) *code = 200 + rows_code;
+  rows_code = 0;
+  rc = direct_rows_take_error(&rows_code);
+  if (rc == MELLIN_OK && *code == 0 && rows_code != 0) *code = 300 + rows_code;
   return rc;
 }
+int mellin_selftest_unarmed_wait(void *stream) { return launch_unarmed_wait(static_cast<cudaStream_t>(stream)); }
 
 // Workspace queries plan with the extents only (tables are not needed: the
 // longest table row is bounded by the kernel extent along the Mellin axis).

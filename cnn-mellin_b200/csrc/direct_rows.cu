@@ -37,6 +37,11 @@ constexpr int kGroup = 4;              // consecutive reduced channels fetched b
 constexpr int kSlotFloats = kGroup * kRowFloats;
 constexpr int kStages = 2;
 constexpr int kRedPitch = 256;
+constexpr uint32_t kWaitLimit = 1u << 20;
+
+// First bounded wait that gave up since the last query (0 = none):
+// 1 = the weight records never arrived, 2 = a ring slot's rows never arrived.
+__device__ int g_direct_rows_error = 0;
 
 struct RowsPlan {
   int y_tiles = 0;
@@ -133,15 +138,24 @@ direct_rows_kernel(const DirectProblem<float> p, const RowsPlan t, const __grid_
 
 #pragma unroll
   for (int st = 0; st < kStages - 1; ++st) issue(st);
+  bool weights_ok = true;  // warp-uniform
   if (t.w_packed != nullptr) {
-    const bool ok = tc::mbar_wait(&w_full, 0, 1u << 20);
-    if (!__all_sync(0xffffffffu, ok)) return;  // cannot happen unless the copy engine faulted; never spin forever
+    const bool ok = tc::mbar_wait(&w_full, 0, kWaitLimit);
+    if (!__all_sync(0xffffffffu, ok)) {  // never spin forever: flag the failure, leave the outputs unwritten
+      if (lane == 0) atomicCAS(&g_direct_rows_error, 0, 1);
+      weights_ok = false;
+    }
   }
   int cpp = 0, ck = 0, ckx = np > 0 ? p.table.entries[e0].x : 0;
-  for (int item = 0; item < items; ++item) {
+  for (int item = 0; weights_ok && item < items; ++item) {
     issue(item + kStages - 1);
-    const bool ok = tc::mbar_wait(&slot_full[warp][item % kStages], (uint32_t)((item / kStages) & 1), 1u << 20);
-    if (!__all_sync(0xffffffffu, ok)) break;
+    const bool ok = tc::mbar_wait(&slot_full[warp][item % kStages], (uint32_t)((item / kStages) & 1), kWaitLimit);
+    if (!__all_sync(0xffffffffu, ok)) {
+      if (lane == 0) atomicCAS(&g_direct_rows_error, 0, 2);
+      // the copy issued for the next item may still be in flight into this warp's ring
+      if (item + 1 < items) tc::mbar_wait(&slot_full[warp][(item + 1) % kStages], (uint32_t)(((item + 1) / kStages) & 1), kWaitLimit);
+      break;
+    }
     const int b0 = kGroup * (warp + kWarps * ck);
 #pragma unroll
     for (int r = 0; r < kGroup; ++r) {
@@ -308,6 +322,14 @@ int dispatch_nky(const DirectProblem<float> &p, const RowsPlan &t, const CUtenso
 }
 
 }  // namespace
+
+// Reads and clears this kernel's timeout flag of the current device (synchronises it).
+int direct_rows_take_error(int *code) {
+  int zero = 0;
+  cudaError_t err = cudaMemcpyFromSymbol(code, g_direct_rows_error, sizeof(int));
+  if (err == cudaSuccess) err = cudaMemcpyToSymbol(g_direct_rows_error, &zero, sizeof(int));
+  return err == cudaSuccess ? MELLIN_OK : fail(MELLIN_ERR_LAUNCH, std::string("device status: ") + cudaGetErrorString(err));
+}
 
 // scratch for the pre-packed weight records (0 = problem not covered by this kernel)
 size_t direct_rows_workspace_bytes(const DirectProblem<float> &p) {

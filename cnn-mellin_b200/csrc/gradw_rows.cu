@@ -232,6 +232,11 @@ struct TileMeta {
   int valid;      // positions of the tile that lie inside the signal
 };
 
+// First bounded wait that gave up since the last query (0 = none): 1 = a stage's
+// copies never completed, 2 = the self-test's unarmed barrier (expected there).
+__device__ int g_rows_error = 0;
+constexpr uint32_t kWaitLimit = 1u << 22;
+
 template <int B, int NKY, int LEAD>
 __global__ void __launch_bounds__(kThreads, 2)
 gradw_rows_tma_kernel(const GradWProblem<float> p, const RowsTiling t, float *__restrict__ part_w,
@@ -246,6 +251,7 @@ gradw_rows_tma_kernel(const GradWProblem<float> p, const RowsTiling t, float *__
   float *smem = tile_smem;
   __shared__ uint64_t full[kStages];
   __shared__ TileMeta meta[kStages];
+  __shared__ volatile int abort_word;
 
   const int tid = threadIdx.x;
   const int co_l = tid & (kTA - 1), q = tid >> 6;
@@ -261,10 +267,17 @@ gradw_rows_tma_kernel(const GradWProblem<float> p, const RowsTiling t, float *__
 
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) tc::mbar_init(&full[s], 1);
+    abort_word = 0;
     tc::fence_mbar_init();
   }
   __syncthreads();
 
+  // Thread 0 publishes a tile's mask / extent in meta[stage] BEFORE it arrives on
+  // the stage's barrier: the arrive releases those writes, a waiter's successful
+  // try_wait acquires them.  (Written after the arrive they raced with the
+  // waiters -- a warp that saw the copies complete while thread 0 was still
+  // between its last copy and the two stores read the previous tile's mask and
+  // summed the wrong taps; seen on the first launch over fresh tensors.)
   auto issue = [&](long long tile, int stage) {  // thread 0 only
     if (tile >= t.tiles) return;
     const int tl = (int)tile;
@@ -275,18 +288,22 @@ gradw_rows_tma_kernel(const GradWProblem<float> p, const RowsTiling t, float *__
     float *gos = smem + stage * kStageFloats;
     float *xs = gos + kTA * kGoPitch;
     const int e0 = p.table_h.row_ptr[ox];
-    const int np = p.table_h.row_ptr[ox + 1] - e0;
-    tc::mbar_arrive_expect_tx(&full[stage], (uint32_t)((kTA * kGoPitch + np * B * kXPitch) * sizeof(float)));
-    tc::tma_load_4d(gos, &go_map, y0, ox, a0, n, &full[stage]);
+    const int np = min(p.table_h.row_ptr[ox + 1] - e0, kMaxKx);
+    int2 ent[kMaxKx];
     unsigned mask = 0;
-    const int x0 = y0 + t.ws0 - LEAD;  // a multiple of 4
-    for (int pp = 0; pp < np; ++pp) {
-      const int2 e = p.table_h.entries[e0 + pp];
-      mask |= 1u << e.x;
-      tc::tma_load_4d(xs + e.x * kSlot, &x_map, x0, e.y, 0, n, &full[stage]);
+#pragma unroll
+    for (int pp = 0; pp < kMaxKx; ++pp) {
+      ent[pp] = pp < np ? p.table_h.entries[e0 + pp] : make_int2(0, 0);
+      if (pp < np) mask |= 1u << ent[pp].x;
     }
     meta[stage].mask = mask;
     meta[stage].valid = p.noy - y0;
+    tc::mbar_arrive_expect_tx(&full[stage], (uint32_t)((kTA * kGoPitch + np * B * kXPitch) * sizeof(float)));
+    tc::tma_load_4d(gos, &go_map, y0, ox, a0, n, &full[stage]);
+    const int x0 = y0 + t.ws0 - LEAD;  // a multiple of 4
+#pragma unroll
+    for (int pp = 0; pp < kMaxKx; ++pp)
+      if (pp < np) tc::tma_load_4d(xs + ent[pp].x * kSlot, &x_map, x0, ent[pp].y, 0, n, &full[stage]);
   };
 
   long long tile = z;
@@ -295,50 +312,65 @@ gradw_rows_tma_kernel(const GradWProblem<float> p, const RowsTiling t, float *__
     for (int s = 0; s < kStages - 1; ++s) issue(tile + (long long)s * t.Z, s);
   }
 
-  for (int it = 0; tile < t.tiles; tile += t.Z, ++it) {
+  int it = 0;
+  for (; tile < t.tiles; tile += t.Z, ++it) {
     const int stage = it % kStages;
     if (tid == 0) issue(tile + (long long)(kStages - 1) * t.Z, (it + kStages - 1) % kStages);
-    // every thread sees thread 0's meta[] writes: they precede its arrive on the barrier
-    if (!tc::mbar_wait(&full[stage], (uint32_t)((it / kStages) & 1), 1u << 22)) break;  // never spins forever
-    const unsigned mask = meta[stage].mask;
-    const int valid = meta[stage].valid;
+    // A wait that gives up raises the device flag and the block-wide abort word;
+    // the thread skips the tile but still reaches the barrier below, after which
+    // every thread sees the word and leaves the loop together.
+    const bool arrived = tc::mbar_wait(&full[stage], (uint32_t)((it / kStages) & 1), kWaitLimit);
+    if (!arrived) {
+      atomicCAS(&g_rows_error, 0, 1);
+      abort_word = 1;
+    } else {
+      const unsigned mask = meta[stage].mask;
+      const int valid = meta[stage].valid;
 
-    const float *gos = smem + stage * kStageFloats + co_l * kGoPitch;
-    const float *xs = smem + stage * kStageFloats + kTA * kGoPitch;
+      const float *gos = smem + stage * kStageFloats + co_l * kGoPitch;
+      const float *xs = smem + stage * kStageFloats + kTA * kGoPitch;
 #pragma unroll 1
-    for (int yo = kStep * q; yo < kTK && yo < valid; yo += 4 * kStep) {
-      float g[kStep];
+      for (int yo = kStep * q; yo < kTK && yo < valid; yo += 4 * kStep) {
+        float g[kStep];
 #pragma unroll
-      for (int i = 0; i < kStep / 4; ++i) {
-        const float4 v = *reinterpret_cast<const float4 *>(gos + yo + 4 * i);
-        g[4 * i] = v.x, g[4 * i + 1] = v.y, g[4 * i + 2] = v.z, g[4 * i + 3] = v.w;
-      }
+        for (int i = 0; i < kStep / 4; ++i) {
+          const float4 v = *reinterpret_cast<const float4 *>(gos + yo + 4 * i);
+          g[4 * i] = v.x, g[4 * i + 1] = v.y, g[4 * i + 2] = v.z, g[4 * i + 3] = v.w;
+        }
 #pragma unroll
-      for (int i = 0; i < kStep; i += 4) bsum += (g[i] + g[i + 1]) + (g[i + 2] + g[i + 3]);
+        for (int i = 0; i < kStep; i += 4) bsum += (g[i] + g[i + 1]) + (g[i + 2] + g[i + 3]);
 #pragma unroll
-      for (int kx = 0; kx < kMaxKx; ++kx) {
-        if (!((mask >> kx) & 1u)) continue;
+        for (int kx = 0; kx < kMaxKx; ++kx) {
+          if (!((mask >> kx) & 1u)) continue;
 #pragma unroll
-        for (int b = 0; b < B; ++b) {
-          const float4 *xp = reinterpret_cast<const float4 *>(xs + kx * kSlot + b * kXPitch + yo);
-          float xw[4 * kWin];
+          for (int b = 0; b < B; ++b) {
+            const float4 *xp = reinterpret_cast<const float4 *>(xs + kx * kSlot + b * kXPitch + yo);
+            float xw[4 * kWin];
 #pragma unroll
-          for (int i = 0; i < kWin; ++i) {
-            const float4 v = xp[i];
-            xw[4 * i] = v.x, xw[4 * i + 1] = v.y, xw[4 * i + 2] = v.z, xw[4 * i + 3] = v.w;
-          }
+            for (int i = 0; i < kWin; ++i) {
+              const float4 v = xp[i];
+              xw[4 * i] = v.x, xw[4 * i + 1] = v.y, xw[4 * i + 2] = v.z, xw[4 * i + 3] = v.w;
+            }
 #pragma unroll
-          for (int k = 0; k < NKY; ++k) {
-            float s = acc[kx][b * NKY + k];
+            for (int k = 0; k < NKY; ++k) {
+              float s = acc[kx][b * NKY + k];
 #pragma unroll
-            for (int j = 0; j < kStep; ++j) s = fmaf(g[j], xw[LEAD + j + k], s);
-            acc[kx][b * NKY + k] = s;
+              for (int j = 0; j < kStep; ++j) s = fmaf(g[j], xw[LEAD + j + k], s);
+              acc[kx][b * NKY + k] = s;
+            }
           }
         }
       }
     }
     // this stage is refilled by the copy engine after the barrier: order the reads before it
     tc::fence_proxy_async();
+    __syncthreads();
+    if (abort_word) break;  // block-uniform: written before the barrier, read after it
+  }
+  if (abort_word) {
+    // copies issued for the next tile may still be in flight into this block's
+    // shared memory: give them a bounded time to land before the block exits
+    if (tid == 0 && tile + t.Z < t.tiles) tc::mbar_wait(&full[(it + 1) % kStages], (uint32_t)(((it + 1) / kStages) & 1), kWaitLimit);
     __syncthreads();
   }
   __syncthreads();
@@ -502,6 +534,31 @@ int launch_gradw_rows(const GradWProblem<float> &p, float *part_w, float *part_b
     case 3: return dispatch_rows_nky<3>(p, t, part_w, part_b, stream);
     default: return dispatch_rows_nky<4>(p, t, part_w, part_b, stream);
   }
+}
+
+// Reads and clears the row kernels' timeout flag of the current device (synchronises it).
+int gradw_rows_take_error(int *code) {
+  int zero = 0;
+  cudaError_t err = cudaMemcpyFromSymbol(code, g_rows_error, sizeof(int));
+  if (err == cudaSuccess) err = cudaMemcpyToSymbol(g_rows_error, &zero, sizeof(int));
+  return err == cudaSuccess ? MELLIN_OK : fail(MELLIN_ERR_LAUNCH, std::string("device status: ") + cudaGetErrorString(err));
+}
+
+namespace {
+// One thread waits, with a limit of 1000 polls, on a barrier that nothing arms,
+// and must come back with the flag raised instead of hanging.
+__global__ void unarmed_wait_kernel() {
+  __shared__ uint64_t bar;
+  tc::mbar_init(&bar, 1);
+  tc::fence_mbar_init();
+  if (!tc::mbar_wait(&bar, 0, 1000u)) atomicCAS(&g_rows_error, 0, 2);
+}
+}  // namespace
+
+int launch_unarmed_wait(cudaStream_t stream) {
+  unarmed_wait_kernel<<<1, 1, 0, stream>>>();
+  const cudaError_t err = cudaGetLastError();
+  return err == cudaSuccess ? MELLIN_OK : fail(MELLIN_ERR_LAUNCH, std::string("unarmed_wait_kernel: ") + cudaGetErrorString(err));
 }
 
 }  // namespace mellin

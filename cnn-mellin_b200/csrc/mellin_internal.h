@@ -102,6 +102,9 @@ int launch_direct_rows(const DirectProblem<float> &p, void *workspace, size_t wo
 size_t direct_tc_workspace_bytes(const DirectProblem<float> &p);
 int launch_direct_tc(const DirectProblem<float> &p, void *workspace, size_t workspace_bytes, cudaStream_t stream);
 int tc_take_error(int *code);
+int direct_rows_take_error(int *code);
+int gradw_rows_take_error(int *code);
+int launch_unarmed_wait(cudaStream_t stream);  // self-test of the bounded waits (gradw_rows.cu)
 // tensor-core forward with the fused length mask / ReLU epilogue (tc_direct_masked.cu)
 size_t direct_tc_workspace_bytes_masked(const DirectProblem<float> &p);
 int launch_direct_tc_masked(const DirectProblem<float> &p, void *workspace, size_t workspace_bytes, cudaStream_t stream);

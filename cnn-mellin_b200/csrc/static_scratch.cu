@@ -1,21 +1,28 @@
 // Weight-gradient entry point for callers that must not allocate device memory.
 //
 // Some hosts cannot call cudaMalloc at the point where they need this gradient:
-// code running inside a stream capture or under a framework that forbids
-// allocation in its backward pass, real-time loops whose memory is pinned down
-// at start-up, plugins that are handed a fixed arena they may not grow.  The
-// regular entry point needs two kinds of device memory besides its operands --
-// caller-provided scratch for the per-block partial sums, and index tables that
-// this library allocates and caches on first use.  The variant below needs
-// neither: both live in ONE fixed array that is part of the library image, so
-// every GPU that loads the library holds those bytes until the process exits.
+// an inference- or training-runtime plugin whose execute hook is handed a fixed
+// arena and is forbidden to grow it, a real-time loop whose memory is pinned
+// down at start-up so that no step can fail or stall on an allocation
+// (cudaMalloc and cudaFree synchronise the device), a framework that forbids
+// allocation inside its backward pass.  The regular entry point needs two kinds
+// of device memory besides its operands -- caller-provided scratch for the
+// per-block partial sums, and index tables that this library allocates and
+// caches on first use.  The variant below needs neither: both live in ONE
+// fixed array that is part of the library image, so every GPU that loads the
+// library holds those bytes until the process exits.
 //
 // Limits and rules
 //   * the partial sums of the geometry must fit kScratchBytes (8 MiB) and its
 //     index tables kTableBytes (256 KiB); otherwise the call is rejected with
 //     MELLIN_ERR_WORKSPACE and a message naming both numbers;
 //   * the first call on each device resolves the array's device address
-//     (cudaGetSymbolAddress); make that call before any stream capture;
+//     (cudaGetSymbolAddress) and synchronises the device once; make that call
+//     before any stream capture;
+//   * the index tables are copied into the array on the caller's stream whenever
+//     the Mellin-axis geometry differs from the one the previous call on this
+//     device staged (a small host-to-device copy from memory the library keeps
+//     alive); calls that repeat the geometry enqueue kernels only;
 //   * every call shares the array and finds in it whatever the previous call
 //     left there.  Nothing needs clearing -- each kernel writes every partial sum
 //     it later reads -- but two calls that overlap on the GPU (different streams,
@@ -41,9 +48,20 @@ constexpr int kMaxDevices = 64;
 std::mutex g_mutex;
 unsigned char *g_device_ptr[kMaxDevices] = {nullptr};
 
+// What the table region of each device's array holds: the geometry last staged,
+// the views handed to the kernels, and the host copy the transfer reads from
+// (kept until the next geometry replaces it).
+struct StagedTables {
+  bool valid = false;
+  int64_t key[7] = {0, 0, 0, 0, 0, 0, 0};
+  mellin::DeviceTable by_f, by_h;
+  std::vector<int32_t> host_f, host_h;
+};
+StagedTables g_staged[kMaxDevices];
+
 // The array's name is a host-side stand-in, not a device address: resolve it
 // once per device, with that device current, and hand the result to kernels.
-int resolve_scratch(unsigned char **out) {
+int resolve_scratch(unsigned char **out, int *device) {
   int dev = 0;
   cudaError_t err = cudaGetDevice(&dev);
   if (err != cudaSuccess) return mellin::fail(MELLIN_ERR_LAUNCH, std::string("cudaGetDevice: ") + cudaGetErrorString(err));
@@ -54,15 +72,21 @@ int resolve_scratch(unsigned char **out) {
     err = cudaGetSymbolAddress(&ptr, g_static_scratch);
     if (err != cudaSuccess || ptr == nullptr)
       return mellin::fail(MELLIN_ERR_LAUNCH, std::string("cudaGetSymbolAddress(static scratch): ") + cudaGetErrorString(err));
+    // the array comes into being when the library image is loaded on this device;
+    // let that finish before the first stream-ordered use
+    err = cudaDeviceSynchronize();
+    if (err != cudaSuccess)
+      return mellin::fail(MELLIN_ERR_LAUNCH, std::string("cudaDeviceSynchronize(static scratch): ") + cudaGetErrorString(err));
     g_device_ptr[dev] = static_cast<unsigned char *>(ptr);
   }
   *out = g_device_ptr[dev];
+  *device = dev;
   return MELLIN_OK;
 }
 
 // Copies one host-built index map into the array at `offset` and returns a view of it.
 int stage_table(const mellin::IndexMapKey &key, unsigned char *base, size_t *offset, mellin::DeviceTable *view,
-                cudaStream_t stream) {
+                std::vector<int32_t> &host, cudaStream_t stream) {
   mellin::IndexMap m;
   try {
     m = mellin::build_index_map(key);
@@ -77,14 +101,14 @@ int stage_table(const mellin::IndexMapKey &key, unsigned char *base, size_t *off
   if (begin + bytes > kScratchBytes + kTableBytes)
     return mellin::fail(MELLIN_ERR_WORKSPACE, "index tables of this geometry need more than the " +
                                                   std::to_string(kTableBytes) + " bytes reserved in the static scratch");
-  std::vector<int32_t> host(ints + 2 * n_ent, 0);
+  host.assign(ints + 2 * n_ent, 0);
   for (size_t i = 0; i < n_ptr; ++i) host[i] = m.row_ptr[i];
   for (size_t i = 0; i < n_ord; ++i) host[n_ptr + i] = m.order[i];
   for (size_t i = 0; i < n_ent; ++i) {
     host[ints + 2 * i] = m.entries[i].a;
     host[ints + 2 * i + 1] = m.entries[i].b;
   }
-  // pageable source: the runtime stages the bytes before returning, so `host` may go out of scope
+  // `host` lives in g_staged until another geometry replaces it
   cudaError_t err = cudaMemcpyAsync(base + begin, host.data(), bytes, cudaMemcpyHostToDevice, stream);
   if (err != cudaSuccess) return mellin::fail(MELLIN_ERR_LAUNCH, std::string("cudaMemcpyAsync(index table): ") + cudaGetErrorString(err));
   const int32_t *dev = reinterpret_cast<const int32_t *>(base + begin);
@@ -123,13 +147,29 @@ extern "C" int mellin_mcorrlcorr_grad_weight_noalloc_f32(const float *x, const f
                                           " bytes, above the " + std::to_string(kScratchBytes) +
                                           " bytes of the built-in scratch; use mellin_mcorrlcorr_grad_weight_f32 with your own workspace");
   unsigned char *base = nullptr;
-  int rc = resolve_scratch(&base);
+  int dev = 0;
+  int rc = resolve_scratch(&base, &dev);
   if (rc) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  size_t offset = kScratchBytes;  // tables sit behind the partial sums
-  rc = stage_table(IndexMapKey{Relation::Corr, SortBy::F, nfx, ngx, nhx, sx, dx, px, ux}, base, &offset, &p.table, s);
-  if (rc) return rc;
-  rc = stage_table(IndexMapKey{Relation::Corr, SortBy::H, nfx, ngx, nhx, sx, dx, px, ux}, base, &offset, &p.table_h, s);
-  if (rc) return rc;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    StagedTables &st = g_staged[dev];
+    const int64_t key[7] = {nfx, ngx, nhx, sx, dx, px, ux};
+    bool same = st.valid;
+    for (int i = 0; i < 7 && same; ++i) same = st.key[i] == key[i];
+    if (!same) {
+      st.valid = false;
+      size_t offset = kScratchBytes;  // tables sit behind the partial sums
+      rc = stage_table(IndexMapKey{Relation::Corr, SortBy::F, nfx, ngx, nhx, sx, dx, px, ux}, base, &offset, &st.by_f,
+                       st.host_f, s);
+      if (rc) return rc;
+      rc = stage_table(IndexMapKey{Relation::Corr, SortBy::H, nfx, ngx, nhx, sx, dx, px, ux}, base, &offset, &st.by_h,
+                       st.host_h, s);
+      if (rc) return rc;
+      for (int i = 0; i < 7; ++i) st.key[i] = key[i];
+      st.valid = true;
+    }
+    p.table = st.by_f, p.table_h = st.by_h;
+  }
   return launch_gradw<float>(p, base, kScratchBytes, s);
 }

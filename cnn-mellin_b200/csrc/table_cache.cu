@@ -81,6 +81,10 @@ int get_device_table(const IndexMapKey &key, DeviceTable *out) {
   err = cudaMalloc(&c.block, bytes > 0 ? bytes : 16);
   if (err != cudaSuccess) return fail(MELLIN_ERR_LAUNCH, std::string("cudaMalloc(index table): ") + cudaGetErrorString(err));
   err = cudaMemcpy(c.block, host.data(), bytes, cudaMemcpyHostToDevice);
+  // A copy from pageable memory returns once the bytes are staged; the transfer
+  // itself is ordered on the legacy default stream only.  The caller's kernels
+  // may run on a stream that does not synchronise with it, so wait here.
+  if (err == cudaSuccess) err = cudaStreamSynchronize(cudaStreamLegacy);
   if (err != cudaSuccess) {
     cudaFree(c.block);
     return fail(MELLIN_ERR_LAUNCH, std::string("cudaMemcpy(index table): ") + cudaGetErrorString(err));

@@ -935,7 +935,11 @@ int TC_FN(launch_direct_tc)(const DirectProblem<float> &p, void *workspace, size
   }
   plan.params.w_hi = w_hi;
   plan.params.w_lo = w_lo;
+#ifdef MELLIN_TUNING_HOOKS
   const char *prof = getenv("MELLIN_TC_PROFILE");
+#else
+  const char *prof = nullptr;
+#endif
   plan.params.profile = (prof != nullptr && prof[0] == '1') ? 1 : 0;
   void (*kernel)(TcParams, const CUtensorMap, const CUtensorMap) = nullptr;
   switch (plan.params.NP / 16) {

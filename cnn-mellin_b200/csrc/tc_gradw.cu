@@ -608,7 +608,11 @@ int launch_gradw_tc(const GradWProblem<float> &p, float *part_w, float *part_b, 
     for (int g0 = 0; g0 < p.nky; g0 += kMaxTaps)
       if (!plan_tc_gradw(p, g0, std::min(kMaxTaps, p.nky - g0), probe)) return MELLIN_ERR_UNSUPPORTED;
   }
+#ifdef MELLIN_TUNING_HOOKS
   const char *prof = getenv("MELLIN_TC_PROFILE");
+#else
+  const char *prof = nullptr;
+#endif
   for (int g0 = 0; g0 < p.nky; g0 += kMaxTaps) {
     const int nky = std::min(kMaxTaps, p.nky - g0);
     GwPlan plan;

@@ -233,23 +233,21 @@ int64_t mellin_launch_count(void);
  * returns the previous setting.  Disabled, every operator runs on CUDA cores. */
 int mellin_set_tensor_cores(int enable);
 
-/* The tensor-core kernels bound every wait on a barrier; if one ever gives up it
- * records a non-zero code on the device instead of hanging.  This call
- * synchronises the current device, stores the code (0 = healthy) in *code and
+/* Every kernel that waits on a barrier (the tensor-core kernels and the
+ * row-streaming first-layer kernels) bounds the wait; if one ever gives up it
+ * records a non-zero code on the device instead of hanging, and the results of
+ * that launch are incomplete.  This call synchronises the current device,
+ * stores the first code recorded since the last query in *code (0 = healthy;
+ * 1..99 tensor-core forward / grad-input, 100.. tensor-core weight gradient,
+ * 200.. row-streaming weight gradient, 300.. row-streaming grad-input) and
  * clears it. */
 int mellin_device_status(int *code);
 
-/* Per-role cycle counters of block 0 of the last tensor-core forward /
- * grad-input launch (mellin_tc_profile) or weight-gradient launch
- * (mellin_tc_gradw_profile) made while the environment variable
- * MELLIN_TC_PROFILE was "1": out[2 * r] = cycles role r spent waiting on
- * barriers, out[2 * r + 1] = cycles it spent working; r = 0 epilogue,
- * 1 converter, 2 MMA issuer, 3 copy issuer (the weight-gradient kernel adds
- * r = 4, its second converter group, out[12] = MMA cycles spent waiting for
- * the level-1 accumulators, out[13] = stages).  16 values.  Tuning aid with
- * no reference counterpart. */
-int mellin_tc_profile(long long *out);
-int mellin_tc_gradw_profile(long long *out);
+/* Self-test of the bounded waits: launches one thread that waits, with a limit
+ * of 1000 polls, on a barrier nothing ever arms.  The kernel must return by
+ * itself and leave mellin_device_status() reporting 202.  No reference
+ * counterpart (the reference's kernels never wait). */
+int mellin_selftest_unarmed_wait(void *stream);
 
 /* Drop every cached index table of the current device (frees device memory). */
 int mellin_clear_tables(void);

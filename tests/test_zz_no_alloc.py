@@ -1,11 +1,12 @@
 """The grad-weight entry point that brings its own scratch.
 
-Hosts that cannot allocate device memory where they need the gradient (inside a
-stream capture, in a backward pass whose framework forbids allocation, in a
-plugin with a fixed arena) call ``mellin_mcorrlcorr_grad_weight_noalloc_f32``:
-partial sums and index tables live in a fixed array inside the library.  This
-file is collected last on purpose, so that a run stopping at the first failure
-has already exercised everything else; the test also passes when run alone.
+Hosts that cannot allocate device memory where they need the gradient (a runtime
+plugin handed a fixed arena, a real-time loop whose memory is pinned down at
+start-up, a backward pass whose framework forbids allocation) call
+``mellin_mcorrlcorr_grad_weight_noalloc_f32``: partial sums and index tables
+live in a fixed array inside the library.  The file is collected last, so that
+a run stopping at the first failure has already exercised everything else; the
+test also passes when run alone in a fresh process.
 """
 import numpy as np
 import pytest
