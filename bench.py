@@ -1,29 +1,39 @@
-"""Benchmark of the Mellin x linear 2-D layer hot path (forward + backward).
+"""Benchmark of the Mellin-convolution hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--skip train,layers,sweep,latency]
 
-Workload (``config.workload``): one 2-D layer, Mellin correlation along the 41
-frequency bins and linear correlation along 800 frames, batch 32 per GPU,
-3 -> 64 channels, kernel 8 x 3, stride 1, dilation 1, time padding 1,
-same-size output (41 x 800), FP32; inputs ~ N(0, 1), Kaiming-normal weights,
-zero bias, upstream gradient ~ N(0, 1); everything synthetic and seeded.
+Headline workload (``config.workload``): one 2-D layer, Mellin correlation along
+the 41 frequency bins and linear correlation along 800 frames, batch 32 per GPU,
+3 -> 64 channels, kernel 8 x 3, stride 1, dilation 1, time padding 1, same-size
+output (41 x 800), FP32; inputs ~ N(0, 1), Kaiming-normal weights, zero bias,
+upstream gradient ~ N(0, 1); everything synthetic and seeded.
 
-One step = forward, grad-input and grad-weight(+bias) of that layer.  The
-metric is effective GB/s: the algorithmic bytes of the step (every operand and
-result counted once; the upstream gradient once for the whole backward)
-divided by the time.  ``value`` is measured with every tensor resident in
-HBM (CUDA events on the launching stream, per step, L2 flushed between
-steps); ``e2e`` is measured through ``mconv.MCorrLCorr`` with the step's input
-batch copied from pinned host memory inside the timed region and the weight
-and bias gradients copied back.
+One step = forward, weight(+bias) gradient and input gradient of that layer.
+The metric is effective GB/s: the algorithmic bytes of the step (every operand
+and result counted once; the upstream gradient once for the whole backward)
+divided by the time.  ``value`` is measured with every tensor resident in HBM
+(CUDA events on the launching stream around EXACTLY ``--steps`` steps, L2
+flushed between steps); the block of K steps is repeated until about two
+seconds of device time have passed and the median block is reported, with the
+value per sampled SM clock beside it.  ``e2e`` is measured through
+``mconv.MCorrLCorr`` with the step's input batch copied from pinned host memory
+inside the timed region and the weight and bias gradients copied back.
 
-With ``--impl reference`` the same step is run by the reference's own CPU
+Further blocks of the same JSON line (each skippable with ``--skip``):
+``train_step`` (the ten-layer CNN-CTC training step, utterances/s, data-parallel
+with bucketed gradient all-reduce overlapped with backward), ``layers`` (the
+wide layers of the three-layer stack against measured TF32 / FP32 peaks),
+``sweep`` (the 1-D Mellin and linear operators at batch 64 x 256 channels x
+16384 samples, batch-sharded over the ranks), ``latency_us`` (the small 1-D
+operator against an empty launch).
+
+With ``--impl reference`` the headline step is run by the reference's own CPU
 kernels (``oracle/_ref``, OpenMP over all host cores; the C restatement when
-that library is absent) on a bounded sample of the batch.
+that library is absent) on the full batch, for the steps asked for.
 
 Multi-GPU (torchrun, one rank per GPU): every rank runs its own batch-32 shard
-(weak scaling); the weight and bias gradients are summed with one NCCL
-all-reduce inside the step.
+(weak scaling); the weight and bias gradients land directly in a flat bucket
+whose NCCL all-reduce runs while the input gradient is computed.
 """
 import argparse
 import json
@@ -40,7 +50,7 @@ for _p in (ROOT, os.path.join(ROOT, "cnn-mellin_b200")):
         sys.path.insert(0, _p)
 
 WORKLOAD = dict(batch=32, c_in=3, c_out=64, ng=(41, 800), nf=(8, 3), s=(1, 1), d=(1, 1), p=(0, 1), u=(1, 1))
-# the other layers of the reference's three-layer stack (kernel 6x3, Mellin dilation 2), for --kernels-only captures
+# the other layers of the reference's three-layer stack (kernel 6x3, Mellin dilation 2)
 PROFILE_LAYERS = {
     "3to64": {},
     "64to128": dict(c_in=64, c_out=128, nf=(6, 3), d=(2, 1)),
@@ -50,8 +60,8 @@ METRIC = "mcorrlcorr_fwd_bwd_effective_bandwidth"
 UNIT = "GB/s"
 
 
-def geometry(batch):
-    w = WORKLOAD
+def geometry(batch, w=None):
+    w = w or WORKLOAD
     valid = (w["ng"][0] * (w["p"][0] + 1)) // (w["nf"][0] + w["d"][0] - 1) - w["s"][0] + 1
     r = (w["ng"][0] - valid, 1)
     x_shape = (batch, w["c_in"]) + w["ng"]
@@ -83,6 +93,25 @@ def workload_name():
             "kernel 8x3, s=1, d=1, time pad 1, same-size output, fp32")
 
 
+def mellin_pairs(nf, ng, nh, s, d, p=0, u=1):
+    """(output, tap) pairs of the Mellin axis that read inside the signal: (h + s)(f + d) = (p + 1)(g + u)."""
+    import numpy as np
+
+    num = (np.arange(nh, dtype=np.int64)[:, None] + s) * (np.arange(nf, dtype=np.int64)[None, :] + d)
+    g = num // (p + 1) - u
+    return int(((num % (p + 1) == 0) & (g >= 0) & (g < ng)).sum())
+
+
+def linear_pairs(nf, ng, nh, s, d, p=0):
+    """(output, tap) pairs of the linear axis that read inside the signal: g = s h + d f - p (no up-sampling)."""
+    count = 0
+    for f in range(nf):
+        h_lo = max(0, -((d * f - p) // s))               # ceil((p - d f) / s)
+        h_hi = min(nh - 1, (ng - 1 + p - d * f) // s)
+        count += max(0, h_hi - h_lo + 1)
+    return count
+
+
 # ---------------------------------------------------------------------------------
 class ClockSampler:
     """Samples nvidia-smi while the timed region runs."""
@@ -94,7 +123,7 @@ class ClockSampler:
     def __init__(self, index):
         self.index = index
         self.proc = None
-        self.lines = []
+        self.lines = []  # (host time, text)
 
     def start(self):
         try:
@@ -108,9 +137,22 @@ class ClockSampler:
 
     def _pump(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.perf_counter(), line.strip()))
 
-    def stop(self):
+    def samples(self):
+        out = []
+        for t, line in list(self.lines):
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                out.append((t, float(parts[0]), float(parts[1]), parts[3:7]))
+            except ValueError:
+                continue
+        return out
+
+    def stop(self, windows=None):
+        """Summary over the samples taken inside `windows` (list of (t0, t1) host times; None = all samples)."""
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         self.proc.terminate()
@@ -118,18 +160,14 @@ class ClockSampler:
             self.proc.wait(timeout=2)
         except Exception:
             pass
-        clocks, maxes, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 7:
+        clocks, maxes, reasons = [], [], set()
+        for t, clk, mx, flags in self.samples():
+            if windows is not None and not any(a <= t <= b for a, b in windows):
                 continue
-            try:
-                clocks.append(float(parts[0]))
-                maxes.append(float(parts[1]))
-            except ValueError:
-                continue
-            for name, val in zip(names, parts[3:7]):
+            clocks.append(clk)
+            maxes.append(mx)
+            for name, val in zip(names, flags):
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(clocks) if clocks else None,
@@ -150,14 +188,10 @@ def _use_all_cores():
     return cores
 
 
-def run_reference(args):
-    """The reference's CPU implementation of the same step on the host cores."""
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
-        return
+def _cpu_step_factory():
+    """The headline step (full batch) on the host cores: returns (step function, oracle kind, cores)."""
     import numpy as np
 
-    # torchrun exports OMP_NUM_THREADS=1 to its workers; this arm is meant to use every host core it may
     cores = len(os.sched_getaffinity(0))
     os.environ["OMP_NUM_THREADS"] = str(cores)
     from oracle.oracle import Oracle
@@ -165,8 +199,7 @@ def run_reference(args):
     kind = "reference" if Oracle.reference_available() else "port"
     oracle = Oracle(kind)
     _use_all_cores()
-    sample_batch = 2
-    xs, ws, ys, r = geometry(sample_batch)
+    xs, ws, ys, r = geometry(WORKLOAD["batch"])
     w_ = WORKLOAD
     rng = np.random.default_rng(0)
     x = rng.standard_normal(xs).astype(np.float32)
@@ -178,21 +211,37 @@ def run_reference(args):
         oracle.mcorrlcorr(x, w, b, w_["s"], w_["d"], w_["p"], w_["u"], r)
         oracle.mcorrlcorr_backward(x, w, go, w_["s"], w_["d"], w_["p"], w_["u"])
 
-    for _ in range(max(1, min(args.warmup, 2))):
+    return step, kind, cores
+
+
+def run_reference(args):
+    """The reference's CPU implementation of the same step, same batch, on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    step, kind, cores = _cpu_step_factory()
+    budget_s = 150.0  # the whole arm must end within a few minutes whatever K is
+    t_begin = time.perf_counter()
+    for _ in range(args.warmup):
         step()
-    steps = max(1, min(args.steps, 10))
+        if time.perf_counter() - t_begin > budget_s / 3:
+            break
+    steps = 0
     t0 = time.perf_counter()
-    for _ in range(steps):
+    while steps < args.steps:
         step()
+        steps += 1
+        if time.perf_counter() - t_begin > budget_s:
+            break
     dt = (time.perf_counter() - t0) / steps
-    value = algorithmic_bytes(sample_batch)["step"] / dt / 1e9
-    sample = "batch %d of the %d-utterance batch per step (the step's cost is linear in the batch), %d steps" % (
-        sample_batch, WORKLOAD["batch"], steps)
+    value = algorithmic_bytes(WORKLOAD["batch"])["step"] / dt / 1e9
+    sample = "the full %d-utterance batch per step, %d steps%s" % (
+        WORKLOAD["batch"], steps, "" if steps == args.steps else " (of %d asked: capped at %.0f s of wall time)" % (args.steps, budget_s))
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
-        "warmup": args.warmup, "ms_per_step": dt * 1e3 * WORKLOAD["batch"] / sample_batch,
+        "warmup": args.warmup, "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": workload_name(), "sample": sample},
+        "config": {"workload": workload_name(), "global_batch": WORKLOAD["batch"]},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -201,57 +250,141 @@ def run_reference(args):
 
 
 def cpu_baseline_leg():
-    import numpy as np
-    from oracle.oracle import Oracle
-
-    kind = "reference" if Oracle.reference_available() else "port"
-    oracle = Oracle(kind)
-    _use_all_cores()
-    sample_batch = 2
-    xs, ws, ys, r = geometry(sample_batch)
-    w_ = WORKLOAD
-    rng = np.random.default_rng(0)
-    x = rng.standard_normal(xs).astype(np.float32)
-    w = (rng.standard_normal(ws) * (2.0 / (ws[1] * ws[2] * ws[3])) ** 0.5).astype(np.float32)
-    b = np.zeros(ws[0], dtype=np.float32)
-    go = rng.standard_normal(ys).astype(np.float32)
-
-    def step():
-        oracle.mcorrlcorr(x, w, b, w_["s"], w_["d"], w_["p"], w_["u"], r)
-        oracle.mcorrlcorr_backward(x, w, go, w_["s"], w_["d"], w_["p"], w_["u"])
-
+    step, kind, cores = _cpu_step_factory()
     step()
     reps, t0 = 0, time.perf_counter()
-    while reps < 3 or (time.perf_counter() - t0 < 10.0 and reps < 50):
+    while reps < 3 or (time.perf_counter() - t0 < 12.0 and reps < 40):
         step()
         reps += 1
     dt = (time.perf_counter() - t0) / reps
-    return {"value": algorithmic_bytes(sample_batch)["step"] / dt / 1e9, "unit": UNIT,
-            "cores": len(os.sched_getaffinity(0)) if kind == "reference" else len(os.sched_getaffinity(0)),
-            "kind": kind,
-            "sample": "batch %d of %d per step, %d repetitions, OpenMP over all listed cores" % (
-                sample_batch, WORKLOAD["batch"], reps)}
+    return {"value": algorithmic_bytes(WORKLOAD["batch"])["step"] / dt / 1e9, "unit": UNIT, "cores": cores, "kind": kind,
+            "ms_per_step": dt * 1e3,
+            "sample": "the full %d-utterance batch per step, %d repetitions (about 12 s), OpenMP over all listed cores" % (
+                WORKLOAD["batch"], reps)}
 
 
 # ---------------------------------------------------------------------------------
-def run_ours(args):
-    import torch
-    import torch.distributed as dist
+class Ctx:
+    """What every block of the GPU arm needs."""
 
+    def __init__(self, args):
+        import torch
+        import torch.distributed as dist
+
+        self.torch, self.dist, self.args = torch, dist, args
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        if not torch.cuda.is_available():
+            raise RuntimeError("bench.py needs a CUDA device: the product has no CPU path")
+        torch.cuda.set_device(self.local_rank)
+        self.dev = torch.device("cuda", self.local_rank)
+        if self.world > 1:
+            dist.init_process_group("nccl", device_id=self.dev)
+        self.flush_buf = torch.empty(192 * 1024 * 1024, dtype=torch.uint8, device=self.dev)  # > 126 MB of L2
+
+    def ev(self):
+        return self.torch.cuda.Event(enable_timing=True)
+
+    def flush(self):
+        self.flush_buf.zero_()
+
+    def barrier(self):
+        self.torch.cuda.synchronize()
+        if self.world > 1:
+            self.dist.barrier()
+            self.torch.cuda.synchronize()
+
+    def max_over_ranks(self, values):
+        t = self.torch.tensor(values, device=self.dev, dtype=self.torch.float64)
+        if self.world > 1:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return [float(v) for v in t.tolist()]
+
+    def time_ms(self, fn, iters, warm=1, flush=False):
+        """Mean device time of fn over iters calls (events on the current stream), max over ranks."""
+        for _ in range(warm):
+            fn()
+        self.barrier()
+        total = 0.0
+        for _ in range(iters):
+            if flush:
+                self.flush()
+            a, b = self.ev(), self.ev()
+            a.record()
+            fn()
+            b.record()
+            self.torch.cuda.synchronize()
+            total += a.elapsed_time(b)
+        return self.max_over_ranks([total / iters])[0]
+
+
+def measure_peaks(ctx):
+    """Denominators the wide-layer and CUDA-core fractions use, measured here as MEASURED_PEAKS.json measures
+    its bf16 entry: a dense TF32 8192^3 product (cuBLAS through torch.matmul: burst = best of 10, sustained =
+    back to back for ~1.5 s) and the FMA-bound micro-kernel of this library."""
+    import capi
+
+    torch = ctx.torch
+    out = {}
+    # the FMA kernel first: the sustained TF32 loop below leaves the part power-capped for a while
+    sms = torch.cuda.get_device_properties(ctx.dev).multi_processor_count
+    buf = torch.empty(sms * 8 * 256, device=ctx.dev)
+    capi.fma_rate(buf, sms * 8, 64)
+    torch.cuda.synchronize()
+    best = None
+    for _ in range(5):
+        e0, e1 = ctx.ev(), ctx.ev()
+        e0.record()
+        fmas = capi.fma_rate(buf, sms * 8, 2048)
+        e1.record()
+        torch.cuda.synchronize()
+        rate = 2 * fmas / e0.elapsed_time(e1) / 1e9
+        best = rate if best is None else max(best, rate)
+    out["fp32_fma_tflops"] = best
+    n = 8192
+    a = torch.randn(n, n, device=ctx.dev)
+    b = torch.randn(n, n, device=ctx.dev)
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    try:
+        c = torch.matmul(a, b)
+        torch.cuda.synchronize()
+        best = None
+        for _ in range(10):
+            e0, e1 = ctx.ev(), ctx.ev()
+            e0.record()
+            c = torch.matmul(a, b)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1)
+            best = ms if best is None else min(best, ms)
+        out["tf32_tflops"] = 2 * n ** 3 / best / 1e9
+        e0, e1 = ctx.ev(), ctx.ev()
+        reps = max(10, int(1500.0 / best))
+        e0.record()
+        for _ in range(reps):
+            c = torch.matmul(a, b)
+        e1.record()
+        torch.cuda.synchronize()
+        out["tf32_tflops_sustained"] = 2 * n ** 3 * reps / e0.elapsed_time(e1) / 1e9
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    del a, b, c
+    out["how"] = ("tf32: torch.matmul 8192^3 with allow_tf32 (best of 10; back to back for ~1.5 s); "
+                  "fp32: FMA-bound micro-kernel, 8 blocks of 256 threads per SM, best of 5")
+    return out
+
+
+# ---------------------------------------------------------------------------------
+def bench_headline(ctx, sampler):
+    """The config-2 layer: value (resident tensors), per-kernel times, e2e through the public surface."""
     import capi
     import dp
     import mconv
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise RuntimeError("bench.py needs a CUDA device: the product has no CPU path")
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-
+    torch, dist, args = ctx.torch, ctx.dist, ctx.args
+    world, rank, dev = ctx.world, ctx.rank, ctx.dev
     w_ = WORKLOAD
     batch = w_["batch"]
     xs, ws, ys, r = geometry(batch)
@@ -268,18 +401,13 @@ def run_ours(args):
     del go_host
     y = torch.empty(ys, device=dev)
     gx = torch.empty_like(x)
-    gw = torch.empty_like(w)
-    gb = torch.empty_like(b)
+    # the gradient kernels write straight into the flat bucket that is all-reduced: nothing is packed
     bucket = dp.GradBucket([ws, (ws[0],)], device=dev)
-    grads_flat = bucket.flat
+    gw, gb = bucket.views()
     ws_bytes = capi.grad_weight_workspace_bytes(xs, ws, ys, s, d, p, u)
     workspace = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
     ws_fwd = torch.empty(max(capi.forward_workspace_bytes(xs, ws, ys, s, d, p, u), 256), dtype=torch.uint8, device=dev)
     ws_gin = torch.empty(max(capi.grad_input_workspace_bytes(xs, ws, ys, s, d, p, u), 256), dtype=torch.uint8, device=dev)
-    flush = torch.empty(192 * 1024 * 1024, dtype=torch.uint8, device=dev)  # > 126 MB of L2
-
-    def ev():
-        return torch.cuda.Event(enable_timing=True)
 
     def step(events=None):
         if events:
@@ -287,64 +415,75 @@ def run_ours(args):
         capi.forward(x, w, b, y, s, d, p, u, workspace=ws_fwd)
         if events:
             events[1].record()
-        capi.grad_input(w, go, gx, s, d, p, u, workspace=ws_gin)
-        if events:
-            events[2].record()
         capi.grad_weight(x, go, gw, gb, s, d, p, u, workspace=workspace)
         if events:
+            events[2].record()
+        # the reduction of grad_w / grad_b runs on the communication library's stream while grad-input computes
+        work = bucket.all_reduce(async_op=True) if world > 1 else None
+        capi.grad_input(w, go, gx, s, d, p, u, workspace=ws_gin)
+        if events:
             events[3].record()
-        if world > 1:
-            bucket.pack([gw, gb])
-            bucket.all_reduce()
+        if work is not None:
+            work.wait()  # orders the compute stream after the reduction
         if events:
             events[4].record()
 
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize()
-
     for _ in range(args.warmup):
-        flush.zero_()
+        ctx.flush()
         step()
-    barrier()
+    ctx.barrier()
 
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
+    # ---- value: blocks of exactly K steps, repeated until ~2 s of device time ----
     launches0 = capi.launch_count()
-    all_events = []
-    for _ in range(args.steps):
-        flush.zero_()
-        evs = [ev() for _ in range(5)]
-        step(evs)
-        all_events.append(evs)
-    barrier()
-    launches = capi.launch_count() - launches0
-    per = {"forward": 0.0, "grad_input": 0.0, "grad_weight": 0.0, "allreduce": 0.0}
-    total_ms = 0.0
-    for evs in all_events:
-        per["forward"] += evs[0].elapsed_time(evs[1])
-        per["grad_input"] += evs[1].elapsed_time(evs[2])
-        per["grad_weight"] += evs[2].elapsed_time(evs[3])
-        per["allreduce"] += evs[3].elapsed_time(evs[4])
-        total_ms += evs[0].elapsed_time(evs[4])
-
+    blocks = []  # (host t0, host t1, total ms, per-kernel ms)
+    device_ms, n_blocks = 0.0, 0
+    max_blocks = 1 if args.kernels_only else 400
+    while n_blocks < max_blocks and (n_blocks < 3 or device_ms < 2000.0):
+        evs_all = []
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            ctx.flush()
+            evs = [ctx.ev() for _ in range(5)]
+            step(evs)
+            evs_all.append(evs)
+        ctx.barrier()
+        t1 = time.perf_counter()
+        per = [0.0, 0.0, 0.0, 0.0]
+        total = 0.0
+        for evs in evs_all:
+            for k in range(4):
+                per[k] += evs[k].elapsed_time(evs[k + 1])
+            total += evs[0].elapsed_time(evs[4])
+        if n_blocks == 0:
+            launches = capi.launch_count() - launches0
+        vals = ctx.max_over_ranks([total / args.steps] + [v / args.steps for v in per])
+        blocks.append((t0, t1, vals))
+        device_ms += (t1 - t0) * 1e3
+        n_blocks += 1
+    order = sorted(range(len(blocks)), key=lambda i: blocks[i][2][0])
+    med = blocks[order[len(order) // 2]][2]
+    ms_step, ms_f, ms_w, ms_i, ms_exposed = med
     if args.kernels_only:
-        if rank == 0:
-            sampler.stop()
-            print(json.dumps({"kernels_only": True, "batch": batch, "ms": {k: v / args.steps for k, v in per.items()},
-                              "gpu_launches": launches}), flush=True)
-        if world > 1:
-            dist.destroy_process_group()
-        return
+        return {"kernels_only": True, "batch": batch, "ms": {"forward": ms_f, "grad_weight": ms_w, "grad_input": ms_i},
+                "gpu_launches": launches}
+
+    # value per sampled SM clock: each block takes the median clock of the samples inside its host window
+    nbytes = algorithmic_bytes(batch)
+    by_clock = {}
+    if rank == 0:
+        samples = sampler.samples()
+        for t0, t1, vals in blocks:
+            clk = [c for t, c, _, _ in samples if t0 <= t <= t1]
+            if clk:
+                by_clock.setdefault(int(statistics.median(clk)), []).append(world * nbytes["step"] / vals[0] / 1e6)
+    value_by_clock = [{"sm_mhz": k, "blocks": len(v), "value": statistics.median(v)} for k, v in sorted(by_clock.items())]
 
     # ---- end to end through the public PyTorch surface, host buffers -------------
     layer = mconv.MCorrLCorr(w_["c_in"], w_["c_out"], w_["nf"], s, d, p, r).to(dev)
     with torch.no_grad():
         layer.weight.copy_(w)
         layer.bias.zero_()
+    layer.weight.grad, layer.bias.grad = gw, gb  # autograd accumulates into the bucket's views
     gw_hosts = [torch.empty(ws, pin_memory=True) for _ in range(2)]
     gb_hosts = [torch.empty(ws[0], pin_memory=True) for _ in range(2)]
     downloaded = [torch.cuda.Event() for _ in range(2)]
@@ -361,34 +500,36 @@ def run_ours(args):
     copy_stream = torch.cuda.Stream(device=dev)
     main_stream = torch.cuda.current_stream()
     counter = {"next_upload": 0, "next_step": 0}
+    h2d_events = []
 
-    def upload():
+    def upload(timed=False):
         k = counter["next_upload"] % 2
         with torch.cuda.stream(copy_stream):
             copy_stream.wait_event(consumed[k])
+            if timed:
+                a, b_ = ctx.ev(), ctx.ev()
+                a.record(copy_stream)
             x_bufs[k].copy_(x_host, non_blocking=True)
+            if timed:
+                b_.record(copy_stream)
+                h2d_events.append((a, b_))
             uploaded[k].record(copy_stream)
         counter["next_upload"] += 1
 
-    def e2e_step():
+    def e2e_step(timed=False):
         k = counter["next_step"] % 2
         counter["next_step"] += 1
-        upload()  # the next step's batch
+        upload(timed)  # the next step's batch
         main_stream.wait_event(uploaded[k])
         xin = x_bufs[k].detach().requires_grad_(True)
+        bucket.flat.zero_()
         out = layer(xin)
-        layer.weight.grad = None
-        layer.bias.grad = None
         out.backward(go)
         consumed[k].record(main_stream)
         if world > 1:
-            bucket.pack([layer.weight.grad, layer.bias.grad])
             bucket.all_reduce()
-            gw_hosts[k].copy_(grads_flat[: gw.numel()].view(ws), non_blocking=True)
-            gb_hosts[k].copy_(grads_flat[gw.numel():], non_blocking=True)
-        else:
-            gw_hosts[k].copy_(layer.weight.grad, non_blocking=True)
-            gb_hosts[k].copy_(layer.bias.grad, non_blocking=True)
+        gw_hosts[k].copy_(gw, non_blocking=True)
+        gb_hosts[k].copy_(gb, non_blocking=True)
         downloaded[k].record(main_stream)
         read_back(1 - k)
 
@@ -401,81 +542,309 @@ def run_ours(args):
     upload()
     for _ in range(max(3, args.warmup // 2)):
         e2e_step()
-    barrier()
-    e2e_steps = max(5, args.steps // 4)
-    e_start, e_end = ev(), ev()
-    e_start.record()
-    for _ in range(e2e_steps):
-        e2e_step()
-    e_end.record()
-    read_back((counter["next_step"] - 1) % 2)  # the last step's gradients
-    barrier()
-    e2e_ms = e_start.elapsed_time(e_end) / e2e_steps
-    clocks = sampler.stop() if rank == 0 else None
+    ctx.barrier()
+    e2e_blocks = []
+    e2e_device_ms = 0.0
+    while len(e2e_blocks) < 3 or (e2e_device_ms < 1000.0 and len(e2e_blocks) < 200):
+        e_start, e_end = ctx.ev(), ctx.ev()
+        t0 = time.perf_counter()
+        e_start.record()
+        for _ in range(args.steps):
+            e2e_step(timed=True)
+        e_end.record()
+        read_back((counter["next_step"] - 1) % 2)  # the last step's gradients
+        ctx.barrier()
+        e2e_device_ms += (time.perf_counter() - t0) * 1e3
+        e2e_blocks.append(ctx.max_over_ranks([e_start.elapsed_time(e_end) / args.steps])[0])
+    ms_e2e = statistics.median(e2e_blocks)
+    h2d_ms = ctx.max_over_ranks([statistics.median([a.elapsed_time(b_) for a, b_ in h2d_events])])[0]
 
-    times = torch.tensor([total_ms / args.steps, e2e_ms, per["forward"] / args.steps, per["grad_input"] / args.steps,
-                          per["grad_weight"] / args.steps, per["allreduce"] / args.steps], device=dev,
-                         dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    ms_step, ms_e2e, ms_f, ms_i, ms_w, ms_ar = [float(v) for v in times.tolist()]
-
-    if rank == 0:
-        nbytes = algorithmic_bytes(batch)
-        peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-        if os.path.isfile(peaks_path):
-            peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
-        else:
-            peak, peak_src = 6650.0, "fallback"
-        kernels = {
-            "forward": {"ms": ms_f, "GBps": nbytes["forward"] / ms_f / 1e6},
-            "grad_input": {"ms": ms_i, "GBps": nbytes["grad_input"] / ms_i / 1e6},
-            "grad_weight": {"ms": ms_w, "GBps": nbytes["grad_weight"] / ms_w / 1e6},
-        }
-        dominant = max(kernels, key=lambda k: kernels[k]["ms"])
-        achieved = kernels[dominant]["GBps"]
-        traffic_path = os.path.join(ROOT, "profiles", "traffic.json")
-        traffic = None
-        if os.path.isfile(traffic_path):
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(peaks_path):
+        peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    else:
+        peak, peak_src = 6650.0, "fallback"
+    kernels = {
+        "forward": {"ms": ms_f, "GBps": nbytes["forward"] / ms_f / 1e6},
+        "grad_input": {"ms": ms_i, "GBps": nbytes["grad_input"] / ms_i / 1e6},
+        "grad_weight": {"ms": ms_w, "GBps": nbytes["grad_weight"] / ms_w / 1e6},
+    }
+    for k in kernels.values():
+        k["frac_of_hbm_peak"] = k["GBps"] / peak
+    dominant = max(kernels, key=lambda k: kernels[k]["ms"])
+    achieved = kernels[dominant]["GBps"]
+    traffic_path = os.path.join(ROOT, "profiles", "traffic.json")
+    traffic = None
+    if os.path.isfile(traffic_path):
+        try:
             traffic = json.load(open(traffic_path)).get(dominant)
-        line = {
-            "metric": METRIC, "value": world * nbytes["step"] / ms_step / 1e6, "unit": UNIT, "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": workload_name(), "global_batch": batch * world,
-                       "l2": "working set 562 MB per step exceeds the 126 MB L2 and a 192 MB buffer is written between timed steps",
-                       "parallelism": "dp%d (batch-sharded, NCCL all-reduce of grad_w and grad_b)" % world},
-            "roofline": {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak,
-                         "peak_source": peak_src, "unit": "GB/s", "frac": achieved / peak, "traffic": traffic},
-            "kernels": kernels,
-            "allreduce_ms": ms_ar,
-            "e2e": {"value": world * nbytes["step"] / ms_e2e / 1e6, "unit": UNIT, "ms_per_step": ms_e2e,
-                    "h2d_bytes_per_step": 4 * numel(xs), "d2h_bytes_per_step": 4 * (numel(ws) + ws[0]),
-                    "api": "mconv.MCorrLCorr forward + autograd backward; input batch from pinned host memory "
-                           "(double-buffered: the upload of step k+1 runs on a copy stream during step k), "
-                           "weight and bias gradients of every step copied to pinned host memory and read by the host one step later; upstream gradient resident on the device"},
-            "gpu_launches": launches,
-            "clocks": clocks,
-        }
+        except ValueError:
+            traffic = None
+    windows = [(t0, t1) for t0, t1, _ in blocks]
+    return {
+        "metric": METRIC, "value": world * nbytes["step"] / ms_step / 1e6, "unit": UNIT, "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_name(), "global_batch": batch * world,
+                   "l2": "working set 562 MB per step exceeds the 126 MB L2 and a 192 MB buffer is written between timed steps",
+                   "timing": "median of %d timed blocks of %d steps each (about 2 s of device time)" % (n_blocks, args.steps),
+                   "parallelism": "dp%d (batch-sharded; grad_w and grad_b are written into one flat bucket whose NCCL "
+                                  "all-reduce overlaps grad-input)" % world},
+        "roofline": {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak,
+                     "peak_source": peak_src, "unit": "GB/s", "frac": achieved / peak, "traffic": traffic},
+        "kernels": kernels,
+        "allreduce_exposed_ms": ms_exposed,
+        "timed_blocks": n_blocks,
+        "value_by_clock": value_by_clock,
+        "e2e": {"value": world * nbytes["step"] / ms_e2e / 1e6, "unit": UNIT, "ms_per_step": ms_e2e, "h2d_ms": h2d_ms,
+                "h2d_bytes_per_step": 4 * numel(xs), "d2h_bytes_per_step": 4 * (numel(ws) + ws[0]),
+                "api": "mconv.MCorrLCorr forward + autograd backward; input batch from pinned host memory "
+                       "(double-buffered: the upload of step k+1 runs on a copy stream during step k; h2d_ms is that copy's "
+                       "own duration), weight and bias gradients of every step copied to pinned host memory and read by the "
+                       "host one step later; upstream gradient resident on the device"},
+        "gpu_launches": launches,
+        "_windows": windows,
+    }
+
+
+def bench_train_step(ctx):
+    """Config 4: the ten-layer CNN-CTC training step, batch 32 per GPU, data-parallel."""
+    import ctc_model
+    import dp
+
+    torch, world, rank, dev = ctx.torch, ctx.world, ctx.rank, ctx.dev
+    per_gpu = 32
+    torch.manual_seed(4321)  # identical initial weights on every rank
+    model = ctc_model.MellinCTCNet().to(dev)
+    reducer = dp.BucketedReducer(model.parameters())
+    step = ctc_model.TrainStep(model, lr=1e-4, reducer=reducer)
+    n_params = sum(p.numel() for p in model.parameters())
+
+    def make_batch(k):
+        # the global batch of 32 * world ragged utterances is dealt so that every rank gets 32 of them and the
+        # frame counts are even (each rank computes the same deal from the same seed); features and labels per rank
+        lengths = ctc_model.synthetic_lengths(per_gpu * world, seed=1000 + k)
+        mine = dp.snake_shards(lengths, world)[rank]
+        return ctc_model.synthetic_batch([lengths[i] for i in mine], seed=100000 * (rank + 1) + k, device=dev)
+
+    warm, timed = 3, 6
+    batches = [make_batch(k) for k in range(warm + timed)]
+    frames = sum(int(b[1].sum()) for b in batches[warm:])
+    padded = sum(int(b[0].shape[0] * b[0].shape[3]) for b in batches[warm:])
+    losses = []
+    for k in range(warm):
+        losses.append(step(*batches[k]))
+    ctx.barrier()
+    e0, e1 = ctx.ev(), ctx.ev()
+    e0.record()
+    for k in range(warm, warm + timed):
+        losses.append(step(*batches[k]))
+    e1.record()
+    ctx.barrier()
+    ms = ctx.max_over_ranks([e0.elapsed_time(e1) / timed])[0]
+    loss_vals = [float(v) for v in losses]
+    import capi
+
+    status = capi.device_status()
+    reducer.remove()
+    del model, step, batches
+    torch.cuda.empty_cache()
+    return {
+        "workload": "config[3]: 10 Mellin x linear layers 3->128->(x4)128->256->(x4)256, kernel 6x3, same-size, ReLU, dropout 0.05, "
+                    "length-masked; FC 10496->1024->1024->62 per frame; log_softmax; CTC(blank=61, zero_infinity); Adam 1e-4; fp32; "
+                    "batch 32 per GPU of (3, 41, T), T ~ U{200..800}, labels U{20..80} over 61 phones; synthetic",
+        "utts_per_s": per_gpu * world / ms * 1e3, "ms_per_step": ms, "steps": timed, "warmup": warm,
+        "global_batch": per_gpu * world, "parameters": n_params, "gradient_bytes_reduced": reducer.reduced_bytes,
+        "buckets": len(reducer.buckets),
+        "frames_per_step_this_rank": frames / timed, "padded_frames_per_step_this_rank": padded / timed,
+        "balance": "global batch dealt longest-first in boustrophedon order: 32 utterances per rank, near-equal frames",
+        "loss_first": loss_vals[0], "loss_last": loss_vals[-1], "device_status": status,
+    }
+
+
+def bench_layers(ctx, peaks):
+    """Wide layers of the three-layer stack (kernel 6x3, Mellin dilation 2, 41 x 800): ms, FP32-equivalent TFLOP/s
+    and the fraction of measured TF32 / 3 (the kernels run 3xTF32)."""
+    import capi
+
+    torch, dev = ctx.torch, ctx.dev
+    out = {}
+    tf32_third = peaks["tf32_tflops"] / 3.0
+    for name, batch in (("64to128", 8), ("128to256", 4)):
+        cfg = dict(WORKLOAD)
+        cfg.update(PROFILE_LAYERS[name])
+        xs, ws, ys, r = geometry(batch, cfg)
+        s, d, p, u = cfg["s"], cfg["d"], cfg["p"], cfg["u"]
+        x = torch.randn(xs, device=dev)
+        w = torch.randn(ws, device=dev) * (2.0 / (ws[1] * ws[2] * ws[3])) ** 0.5
+        b = torch.zeros(ws[0], device=dev)
+        go = torch.randn(ys, device=dev)
+        y, gx, gw, gb = torch.empty(ys, device=dev), torch.empty_like(x), torch.empty_like(w), torch.empty_like(b)
+        px = mellin_pairs(ws[2], xs[2], ys[2], s[0], d[0])
+        py = linear_pairs(ws[3], xs[3], ys[3], s[1], d[1], p[1])
+        flop = 2.0 * batch * ws[0] * ws[1] * px * py
+        cell = {"batch": batch, "gflop": flop / 1e9}
+        for key, fn in (("forward", lambda: capi.forward(x, w, b, y, s, d, p, u)),
+                        ("grad_input", lambda: capi.grad_input(w, go, gx, s, d, p, u)),
+                        ("grad_weight", lambda: capi.grad_weight(x, go, gw, gb, s, d, p, u))):
+            ms = ctx.time_ms(fn, iters=10, warm=2, flush=True)
+            tf = flop / ms / 1e9
+            cell[key] = {"ms": ms, "tflops_fp32_equiv": tf, "frac_of_tf32_third": tf / tf32_third}
+        out[name] = cell
+        del x, w, go, y, gx, gw
+    out["denominator"] = "measured TF32 dense burst (peaks.tf32_tflops) / 3: every product is three TF32 MMAs"
+    return out
+
+
+def bench_sweep(ctx, peaks):
+    """Config 5: 1-D Mellin and 1-D linear correlation, batch 64 (sharded over the ranks), 256 -> 256 channels,
+    16384 samples, kernel 64, stride and dilation in {1, 2}; forward + grad-input + grad-weight, one all-reduce
+    of grad_w (16.8 MB) when sharded."""
+    import capi
+
+    torch, dist, world, dev = ctx.torch, ctx.dist, ctx.world, ctx.dev
+    total_batch, C, L, K = 64, 256, 16384, 64
+    if total_batch % world:
+        return {"skipped": "batch 64 does not split over %d ranks" % world}
+    N = total_batch // world
+    cells = {}
+    tf32_third = peaks["tf32_tflops"] / 3.0
+    I = __import__("ctypes").c_int64
+    for kind in ("mcorr1d", "lcorr1d"):
+        for s in (1, 2):
+            for d in (1, 2):
+                name = "%s_s%d_d%d" % (kind, s, d)
+                if kind == "mcorr1d":
+                    nh = L  # same-size output (the variant that keeps every tap of every position)
+                    xs, ws_, ys = (N, C, L, 1), (C, C, K, 1), (N, C, nh, 1)
+                    S, D, P, U = (s, 1), (d, 1), (0, 0), (1, 1)
+                    pairs = mellin_pairs(K, L, nh, s, d)
+                else:
+                    nh = int(capi.lib().mellin_lcorr_valid_size(I(K), I(L), I(s), I(d), I(0), I(1)))
+                    xs, ws_, ys = (N, C, 1, L), (C, C, 1, K), (N, C, 1, nh)
+                    S, D, P, U = (1, s), (1, d), (0, 0), (1, 1)
+                    pairs = linear_pairs(K, L, nh, s, d)
+                flop = 2.0 * total_batch * C * C * pairs
+                x = torch.randn(xs, device=dev)
+                w = torch.randn(ws_, device=dev)
+                b = torch.zeros(C, device=dev)
+                go = torch.randn(ys, device=dev)
+                y, gx, gw, gb = torch.empty(ys, device=dev), torch.empty_like(x), torch.empty_like(w), torch.empty_like(b)
+                cell = {"out_len": nh, "pairs": pairs, "gflop_per_kernel": flop / 1e9, "batch_per_gpu": N}
+                try:
+                    # a cell the fast kernels do not cover falls to the per-output kernels: seconds per call at this
+                    # size.  Time one forward first and skip the cell when it is out of proportion.
+                    t_probe = ctx.time_ms(lambda: capi.forward(x, w, b, y, S, D, P, U), iters=1, warm=0)
+                    if t_probe > 400.0:
+                        cell["skipped"] = "forward took %.0f ms: not covered by the tensor-core kernels" % t_probe
+                    else:
+                        def fwd_bwd():
+                            capi.forward(x, w, b, y, S, D, P, U)
+                            capi.grad_weight(x, go, gw, gb, S, D, P, U)
+                            work = dist.all_reduce(gw, async_op=True) if world > 1 else None
+                            capi.grad_input(w, go, gx, S, D, P, U)
+                            if work is not None:
+                                work.wait()
+                        for key, fn in (("forward", lambda: capi.forward(x, w, b, y, S, D, P, U)),
+                                        ("grad_input", lambda: capi.grad_input(w, go, gx, S, D, P, U)),
+                                        ("grad_weight", lambda: capi.grad_weight(x, go, gw, gb, S, D, P, U))):
+                            ms = ctx.time_ms(fn, iters=2, warm=1)
+                            cell[key] = {"ms": ms, "tflops_fp32_equiv": flop / ms / 1e9}
+                        ms = ctx.time_ms(fwd_bwd, iters=2, warm=1)
+                        cell["fwd_bwd_ms"] = ms
+                        cell["tflops_fp32_equiv"] = 3 * flop / ms / 1e9
+                        cell["frac_of_tf32_third"] = cell["tflops_fp32_equiv"] / tf32_third
+                except capi.MellinError as e:
+                    cell["error"] = str(e)
+                cells[name] = cell
+                del x, w, go, y, gx, gw
+                torch.cuda.empty_cache()
+    cells["scaling"] = "strong: batch 64 split over %d rank(s), grad_w summed with one all-reduce" % world
+    return cells
+
+
+def bench_latency(ctx):
+    """Config 1: the small 1-D Mellin correlation (batch 8, 4 -> 8 channels, length 256, kernel 16) is
+    launch-latency-bound: microseconds per call against an empty-stream event pair and a trivial torch kernel."""
+    import capi
+
+    torch, dev = ctx.torch, ctx.dev
+    x = torch.randn((8, 4, 256, 1), device=dev)
+    w = torch.randn((8, 4, 16, 1), device=dev) / 8.0
+    go = torch.randn((8, 8, 16, 1), device=dev)
+    y, gx, gw = torch.empty_like(go), torch.empty_like(x), torch.empty_like(w)
+    S, D, P, U = (1, 1), (1, 1), (0, 0), (1, 1)
+    tiny = torch.zeros(32, device=dev)
+
+    def us(fn, n=200):
+        for _ in range(20):
+            fn()
+        torch.cuda.synchronize()
+        a, b = ctx.ev(), ctx.ev()
+        a.record()
+        for _ in range(n):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / n * 1e3
+
+    return {"forward": us(lambda: capi.forward(x, w, None, y, S, D, P, U)),
+            "grad_input": us(lambda: capi.grad_input(w, go, gx, S, D, P, U)),
+            "grad_weight": us(lambda: capi.grad_weight(x, go, gw, None, S, D, P, U)),
+            "trivial_kernel": us(lambda: tiny.add_(1.0)),
+            "note": "microseconds per call, 200 back-to-back calls on one stream (host launch cost included); "
+                    "config[0] shapes, r = 0 (16 outputs per row)"}
+
+
+def run_ours(args):
+    ctx = Ctx(args)
+    rank, world = ctx.rank, ctx.world
+    skip = set(args.skip.split(",")) if args.skip else set()
+    sampler = ClockSampler(ctx.local_rank)
+    if rank == 0:
+        sampler.start()
+    line = bench_headline(ctx, sampler)
+    if args.kernels_only:
+        if rank == 0:
+            sampler.stop()
+            print(json.dumps(line), flush=True)
+        if world > 1:
+            ctx.dist.destroy_process_group()
+        return
+    windows = line.pop("_windows")
+    clocks = sampler.stop(windows) if rank == 0 else None
+    line["clocks"] = clocks
+    peaks = measure_peaks(ctx)
+    line["peaks"] = peaks
+    if "latency" not in skip:
+        line["latency_us"] = bench_latency(ctx)
+    if "layers" not in skip:
+        line["layers"] = bench_layers(ctx, peaks)
+    if "sweep" not in skip:
+        line["sweep"] = bench_sweep(ctx, peaks)
+    if "train" not in skip:
+        line["train_step"] = bench_train_step(ctx)
+    if rank == 0:
         if world == 1:
             line["cpu_baseline"] = cpu_baseline_leg()  # timed on rank 0 of the single-GPU run only
         print(json.dumps(line), flush=True)
     if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+        ctx.dist.barrier()
+        ctx.dist.destroy_process_group()
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=WORKLOAD["batch"],
                     help="utterances per GPU; values other than 32 are for profiler captures of a smaller case, "
                          "not for bench lines")
     ap.add_argument("--kernels-only", action="store_true",
-                    help="skip the end-to-end and CPU-baseline legs (profiler captures)")
+                    help="one timed block of the headline kernels only (profiler captures)")
+    ap.add_argument("--skip", default="", help="comma-separated blocks to leave out: train, layers, sweep, latency")
     ap.add_argument("--layer", default="3to64", choices=sorted(PROFILE_LAYERS),
                     help="with --kernels-only: time another layer of the reference's stacks (profiler captures of the "
                          "wide-layer kernels); bench lines are always the 3to64 layer")

@@ -31,7 +31,7 @@ MISC = ["mellin_abi_version", "mellin_last_error", "mellin_launch_count", "melli
         "mellin_set_tensor_cores", "mellin_device_status", "mellin_mcorrlcorr_forward_workspace_bytes",
         "mellin_mcorrlcorr_grad_input_workspace_bytes", "mellin_mcorrlcorr_grad_weight_noalloc_f32",
         "mellin_mcorrlcorr_grad_weight_workspace_bytes", "mellin_index_map_build",
-        "mellin_selftest_unarmed_wait"]
+        "mellin_selftest_unarmed_wait", "mellin_selftest_fma_rate"]
 
 
 def exported_symbols():
@@ -176,6 +176,16 @@ def set_tensor_cores(enable):
 def selftest_unarmed_wait():
     """Launch the bounded-wait self-test: device_status() must report 202 afterwards."""
     _check(lib().mellin_selftest_unarmed_wait(_stream()))
+
+
+def fma_rate(out, blocks, iters):
+    """Launch the FMA-bound micro-kernel; returns the multiply-adds it performs (time it with events)."""
+    fn = lib().mellin_selftest_fma_rate
+    fn.restype = _I64
+    n = fn(_p(out), _I64(blocks), _I64(iters), _stream())
+    if n < 0:
+        raise MellinError(1, lib().mellin_last_error().decode())
+    return int(n)
 
 
 def device_status():

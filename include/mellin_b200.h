@@ -249,6 +249,13 @@ int mellin_device_status(int *code);
  * counterpart (the reference's kernels never wait). */
 int mellin_selftest_unarmed_wait(void *stream);
 
+/* Measurement aid: runs `blocks` blocks of 256 threads, each thread `iters`
+ * iterations of 128 packed FP32 multiply-adds on registers, and returns the
+ * number of multiply-adds performed (-1 on bad arguments); `out` receives
+ * blocks * 256 floats.  Timed by the caller, it gives the FP32 CUDA-core
+ * ceiling of the device.  No reference counterpart. */
+int64_t mellin_selftest_fma_rate(float *out, int64_t blocks, int64_t iters, void *stream);
+
 /* Drop every cached index table of the current device (frees device memory). */
 int mellin_clear_tables(void);
 

@@ -79,3 +79,58 @@ def test_shard_helpers():
     assert max(loads) - min(loads) <= 200
     with pytest.raises(ValueError):
         dp.shard_range(4, 2, 2)
+
+
+def _reducer_worker(rank, world, port, out_dir):
+    for p in (ROOT, os.path.join(ROOT, "cnn-mellin_b200")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    import dp
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.manual_seed(0)  # identical model and data on every rank; each takes its slice of the batch
+        model = torch.nn.Sequential(torch.nn.Linear(6, 16), torch.nn.ReLU(), torch.nn.Linear(16, 16), torch.nn.ReLU(),
+                                    torch.nn.Linear(16, 3)).double()
+        x, t = torch.randn(8, 6, dtype=torch.float64), torch.randn(8, 3, dtype=torch.float64)
+        full = [g.clone() for g in torch.autograd.grad(((model(x) - t) ** 2).mean(), list(model.parameters()))]
+        # small buckets: the six parameters spread over several of them
+        reducer = dp.BucketedReducer(model.parameters(), bucket_bytes=1024)
+        lo, hi = dp.shard_range(8, world, rank)
+        ok = len(reducer.buckets) >= 2
+        for step in range(2):  # the second step checks that the buckets are re-armed and re-zeroed
+            reducer.begin_step()
+            ((model(x[lo:hi]) - t[lo:hi]) ** 2).mean().backward()
+            reducer.finish_step()
+            for p_, g in zip(model.parameters(), full):
+                ok = ok and torch.allclose(p_.grad, g, rtol=1e-12, atol=1e-14)
+                ok = ok and p_.grad.data_ptr() >= reducer.buckets[reducer._bucket_of[p_]].data_ptr()
+        with open(os.path.join(out_dir, "rank%d" % rank), "w") as fp:
+            fp.write("ok" if ok else "mismatch")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_bucketed_reducer_averages_gradients_during_backward(tmp_path):
+    world = 2
+    mp.spawn(_reducer_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        assert (tmp_path / ("rank%d" % r)).read_text() == "ok"
+
+
+def test_snake_shards_are_equal_count_and_balanced():
+    sys.path.insert(0, os.path.join(ROOT, "cnn-mellin_b200"))
+    import dp
+
+    rng = np.random.default_rng(3)
+    for world in (1, 2, 4, 8):
+        lengths = rng.integers(200, 801, size=32 * world).tolist()
+        shards = dp.snake_shards(lengths, world)
+        assert sorted(i for sh in shards for i in sh) == list(range(32 * world))
+        assert all(len(sh) == 32 for sh in shards)
+        loads = [sum(lengths[i] for i in sh) for sh in shards]
+        assert max(loads) - min(loads) <= 600  # under one utterance, against ~1000 (one sigma) for a random deal
+    with pytest.raises(ValueError):
+        dp.snake_shards([1, 2, 3], 2)
