@@ -483,7 +483,11 @@ def bench_headline(ctx, sampler):
     with torch.no_grad():
         layer.weight.copy_(w)
         layer.bias.zero_()
-    layer.weight.grad, layer.bias.grad = gw, gb  # autograd accumulates into the bucket's views
+    # Two flat buckets alternate: the gradients of step k accumulate into bucket k % 2 (the layer's .grad tensors
+    # are views of it), its all-reduce is launched asynchronously after backward and is waited for -- and the result
+    # copied to the host -- only after step k + 1 has been queued, so the reduction never stalls the compute stream.
+    e2e_buckets = [bucket, dp.GradBucket([ws, (ws[0],)], device=dev)]
+    works = [None, None]
     gw_hosts = [torch.empty(ws, pin_memory=True) for _ in range(2)]
     gb_hosts = [torch.empty(ws[0], pin_memory=True) for _ in range(2)]
     downloaded = [torch.cuda.Event() for _ in range(2)]
@@ -492,7 +496,7 @@ def bench_headline(ctx, sampler):
     # pinned host memory while step k computes.  Every timed step still owns one
     # upload and one download; the upload before the first timed step is paid by
     # the upload the last timed step issues for a step that never runs.  The host
-    # reads the gradients of step k - 1 (pinned buffers, double-buffered too) after
+    # reads the gradients of step k - 2 (pinned buffers, double-buffered too) after
     # it has queued step k, so that the device never waits for the host.
     x_bufs = [torch.empty(xs, device=dev) for _ in range(2)]
     uploaded = [torch.cuda.Event() for _ in range(2)]
@@ -516,22 +520,31 @@ def bench_headline(ctx, sampler):
             uploaded[k].record(copy_stream)
         counter["next_upload"] += 1
 
+    def download(k):
+        """Gradients of the step that used bucket k: wait for their reduction, copy them to the host."""
+        if works[k] is not None:
+            works[k].wait()
+            works[k] = None
+        gwk, gbk = e2e_buckets[k].views()
+        gw_hosts[k].copy_(gwk, non_blocking=True)
+        gb_hosts[k].copy_(gbk, non_blocking=True)
+        downloaded[k].record(main_stream)
+
     def e2e_step(timed=False):
         k = counter["next_step"] % 2
         counter["next_step"] += 1
         upload(timed)  # the next step's batch
         main_stream.wait_event(uploaded[k])
+        read_back(k)  # the host is done with this bucket's previous download before the bucket is reused
         xin = x_bufs[k].detach().requires_grad_(True)
-        bucket.flat.zero_()
+        e2e_buckets[k].flat.zero_()
+        layer.weight.grad, layer.bias.grad = e2e_buckets[k].views()  # autograd accumulates into the bucket
         out = layer(xin)
         out.backward(go)
         consumed[k].record(main_stream)
         if world > 1:
-            bucket.all_reduce()
-        gw_hosts[k].copy_(gw, non_blocking=True)
-        gb_hosts[k].copy_(gb, non_blocking=True)
-        downloaded[k].record(main_stream)
-        read_back(1 - k)
+            works[k] = e2e_buckets[k].all_reduce(async_op=True)
+        download(1 - k)  # the previous step's gradients, reduced while this step ran
 
     def read_back(k):
         downloaded[k].synchronize()
@@ -552,7 +565,8 @@ def bench_headline(ctx, sampler):
         for _ in range(args.steps):
             e2e_step(timed=True)
         e_end.record()
-        read_back((counter["next_step"] - 1) % 2)  # the last step's gradients
+        download((counter["next_step"] - 1) % 2)  # the last step's gradients
+        read_back((counter["next_step"] - 1) % 2)
         ctx.barrier()
         e2e_device_ms += (time.perf_counter() - t0) * 1e3
         e2e_blocks.append(ctx.max_over_ranks([e_start.elapsed_time(e_end) / args.steps])[0])
@@ -627,20 +641,26 @@ def bench_train_step(ctx):
         mine = dp.snake_shards(lengths, world)[rank]
         return ctc_model.synthetic_batch([lengths[i] for i in mine], seed=100000 * (rank + 1) + k, device=dev)
 
-    warm, timed = 3, 6
-    batches = [make_batch(k) for k in range(warm + timed)]
+    warm, timed = 3, 20  # about 4 s: long enough for the clocks to settle under the power cap
+    distinct = [make_batch(k) for k in range(6)]
+    batches = [distinct[k % 6] for k in range(warm + timed)]
     frames = sum(int(b[1].sum()) for b in batches[warm:])
     padded = sum(int(b[0].shape[0] * b[0].shape[3]) for b in batches[warm:])
     losses = []
     for k in range(warm):
         losses.append(step(*batches[k]))
     ctx.barrier()
+    sampler = ClockSampler(ctx.local_rank)
+    if rank == 0:
+        sampler.start()
     e0, e1 = ctx.ev(), ctx.ev()
+    t_begin = time.perf_counter()
     e0.record()
     for k in range(warm, warm + timed):
         losses.append(step(*batches[k]))
     e1.record()
     ctx.barrier()
+    clocks = sampler.stop([(t_begin, time.perf_counter())]) if rank == 0 else None
     ms = ctx.max_over_ranks([e0.elapsed_time(e1) / timed])[0]
     loss_vals = [float(v) for v in losses]
     import capi
@@ -658,7 +678,7 @@ def bench_train_step(ctx):
         "buckets": len(reducer.buckets),
         "frames_per_step_this_rank": frames / timed, "padded_frames_per_step_this_rank": padded / timed,
         "balance": "global batch dealt longest-first in boustrophedon order: 32 utterances per rank, near-equal frames",
-        "loss_first": loss_vals[0], "loss_last": loss_vals[-1], "device_status": status,
+        "loss_first": loss_vals[0], "loss_last": loss_vals[-1], "device_status": status, "clocks": clocks,
     }
 
 
@@ -735,7 +755,7 @@ def bench_sweep(ctx, peaks):
                     # a cell the fast kernels do not cover falls to the per-output kernels: seconds per call at this
                     # size.  Time one forward first and skip the cell when it is out of proportion.
                     t_probe = ctx.time_ms(lambda: capi.forward(x, w, b, y, S, D, P, U), iters=1, warm=0)
-                    if t_probe > 400.0:
+                    if t_probe > max(60.0, flop / world / 10e9):  # slower than 10 TFLOP/s: the per-output fallback
                         cell["skipped"] = "forward took %.0f ms: not covered by the tensor-core kernels" % t_probe
                     else:
                         def fwd_bwd():

@@ -118,6 +118,12 @@ int dispatch_direct(const DirectProblem<float> &p, void *workspace, size_t works
       if (rc != MELLIN_ERR_UNSUPPORTED) return rc;
     }
   }
+  if (p.B <= 4 && p.A >= 8) {
+    // a handful of reduced channels (a first layer's forward) without the tensor cores: the row kernel
+    // (152 us at the benchmark layer against 121 us for the tcgen05 kernel and 220 us for the tile kernel)
+    const int rc = launch_few_in_rows(p, stream);
+    if (rc != MELLIN_ERR_UNSUPPORTED) return rc;
+  }
   return launch_direct<float>(p, stream);
 }
 int dispatch_direct(const DirectProblem<double> &p, void *, size_t, cudaStream_t stream) {

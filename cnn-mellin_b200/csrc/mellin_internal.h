@@ -96,6 +96,9 @@ template <typename T> int launch_direct(const DirectProblem<T> &p, cudaStream_t 
 // tensor-core path (tc_direct.cu): scratch for the packed hi/lo weights, launch
 // (MELLIN_ERR_UNSUPPORTED when the problem is outside its coverage), and the
 // device-side timeout flag
+// few-input-channel forward kernel (few_in_rows.cu), carries the fused mask / ReLU epilogue;
+// MELLIN_ERR_UNSUPPORTED when not covered
+int launch_few_in_rows(const DirectProblem<float> &p, cudaStream_t stream);
 // few-output-channel kernel (direct_rows.cu); MELLIN_ERR_UNSUPPORTED when not covered
 size_t direct_rows_workspace_bytes(const DirectProblem<float> &p);
 int launch_direct_rows(const DirectProblem<float> &p, void *workspace, size_t workspace_bytes, cudaStream_t stream);
