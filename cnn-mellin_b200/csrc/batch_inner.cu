@@ -25,9 +25,9 @@ namespace {
 
 constexpr int kTile = 32;
 
-// dst[(c * L + x) * N + n] = src[n * sn + c * sc + x]
-__global__ void to_batch_inner_kernel(const float *__restrict__ src, long long sn, long long sc, int N, int C, int L,
-                                      float *__restrict__ dst) {
+// dst[(c * L + x) * Np + n] = n < N ? src[n * sn + c * sc + x] : 0   (Np >= N: the padded batch)
+__global__ void to_batch_inner_kernel(const float *__restrict__ src, long long sn, long long sc, int N, int Np, int C,
+                                      int L, float *__restrict__ dst) {
   __shared__ float tile[kTile][kTile + 1];
   const int c = blockIdx.z;
   const int x0 = blockIdx.x * kTile, n0 = blockIdx.y * kTile;
@@ -38,19 +38,19 @@ __global__ void to_batch_inner_kernel(const float *__restrict__ src, long long s
   __syncthreads();
   for (int j = threadIdx.y; j < kTile; j += blockDim.y) {
     const int x = x0 + j, n = n0 + threadIdx.x;
-    if (x < L && n < N) dst[((long long)c * L + x) * N + n] = tile[threadIdx.x][j];
+    if (x < L && n < Np) dst[((long long)c * L + x) * Np + n] = tile[threadIdx.x][j];
   }
 }
 
-// dst[n * dn + c * dc + x] = src[(c * L + x) * N + n]
-__global__ void from_batch_inner_kernel(const float *__restrict__ src, int N, int C, int L, float *__restrict__ dst,
-                                        long long dn, long long dc) {
+// dst[n * dn + c * dc + x] = src[(c * L + x) * Np + n]
+__global__ void from_batch_inner_kernel(const float *__restrict__ src, int N, int Np, int C, int L,
+                                        float *__restrict__ dst, long long dn, long long dc) {
   __shared__ float tile[kTile][kTile + 1];
   const int c = blockIdx.z;
   const int x0 = blockIdx.x * kTile, n0 = blockIdx.y * kTile;
   for (int j = threadIdx.y; j < kTile; j += blockDim.y) {
     const int x = x0 + j, n = n0 + threadIdx.x;
-    tile[j][threadIdx.x] = (x < L && n < N) ? src[((long long)c * L + x) * N + n] : 0.f;
+    tile[j][threadIdx.x] = (x < L && n < N) ? src[((long long)c * L + x) * Np + n] : 0.f;
   }
   __syncthreads();
   for (int j = threadIdx.y; j < kTile; j += blockDim.y) {
@@ -78,17 +78,21 @@ int check(const char *what) {
   return MELLIN_OK;
 }
 
+// the batch padded to what the tensor-core kernels need of a linear axis: at least 16 positions, a multiple of 4
+int padded_batch(int N) { return std::max(16, (N + 3) / 4 * 4); }
+
 int to_batch_inner(const float *src, long long sn, long long sc, int N, int C, int L, float *dst, cudaStream_t s) {
   if (C > 65535) return MELLIN_ERR_UNSUPPORTED;
-  const dim3 grid((L + kTile - 1) / kTile, (N + kTile - 1) / kTile, C);
-  to_batch_inner_kernel<<<grid, dim3(kTile, 8), 0, s>>>(src, sn, sc, N, C, L, dst);
+  const int Np = padded_batch(N);
+  const dim3 grid((L + kTile - 1) / kTile, (Np + kTile - 1) / kTile, C);
+  to_batch_inner_kernel<<<grid, dim3(kTile, 8), 0, s>>>(src, sn, sc, N, Np, C, L, dst);
   return check("to_batch_inner_kernel");
 }
 
 int from_batch_inner(const float *src, int N, int C, int L, float *dst, long long dn, long long dc, cudaStream_t s) {
   if (C > 65535) return MELLIN_ERR_UNSUPPORTED;
   const dim3 grid((L + kTile - 1) / kTile, (N + kTile - 1) / kTile, C);
-  from_batch_inner_kernel<<<grid, dim3(kTile, 8), 0, s>>>(src, N, C, L, dst, dn, dc);
+  from_batch_inner_kernel<<<grid, dim3(kTile, 8), 0, s>>>(src, N, padded_batch(N), C, L, dst, dn, dc);
   return check("from_batch_inner_kernel");
 }
 
@@ -110,16 +114,17 @@ GradWProblem<float> padded_gradw(const GradWProblem<float> &p) {
 
 // wide 1-D Mellin operators with a batch that can stand in for the linear axis
 bool eligible(int N, int A, int B, int nky, int niy, int noy, int Ay, int Cy, int Dy) {
-  return tensor_cores_enabled() && niy == 1 && noy == 1 && nky == 1 && Ay == 1 && Cy == 0 && Dy == 1 && N >= 16 &&
-         N % 4 == 0 && A >= 32 && B >= 16 && A <= 65535 && B <= 65535;
+  return tensor_cores_enabled() && niy == 1 && noy == 1 && nky == 1 && Ay == 1 && Cy == 0 && Dy == 1 && N >= 2 &&
+         A >= 32 && B >= 16 && A <= 65535 && B <= 65535;
 }
 
 DirectProblem<float> inner_direct(const DirectProblem<float> &p, const float *xt, float *yt) {
   DirectProblem<float> q = p;
   q.in = xt, q.out = yt;
-  q.N = 1, q.niy = p.N, q.noy = p.N;
-  q.in_sn = (long long)p.B * p.nix * p.N, q.in_sb = (long long)p.nix * p.N;
-  q.out_sn = (long long)p.A * p.nox * p.N, q.out_sa = (long long)p.nox * p.N;
+  const int Np = padded_batch(p.N);
+  q.N = 1, q.niy = Np, q.noy = Np;
+  q.in_sn = (long long)p.B * p.nix * Np, q.in_sb = (long long)p.nix * Np;
+  q.out_sn = (long long)p.A * p.nox * Np, q.out_sa = (long long)p.nox * Np;
   q.Ay = 1, q.By = 1, q.Cy = 0, q.Dy = 1;
   return q;
 }
@@ -128,7 +133,7 @@ GradWProblem<float> inner_gradw(const GradWProblem<float> &p, const float *xt, c
   GradWProblem<float> q = p;
   q.in = xt, q.go = got;
   q.lens = nullptr;  // the linear axis is the batch here
-  q.N = 1, q.niy = p.N, q.noy = p.N;
+  q.N = 1, q.niy = padded_batch(p.N), q.noy = padded_batch(p.N);
   q.Ay = 1, q.By = 1, q.Cy = 0, q.Dy = 1;
   return q;
 }
@@ -137,8 +142,8 @@ GradWProblem<float> inner_gradw(const GradWProblem<float> &p, const float *xt, c
 
 size_t direct_batch_inner_workspace_bytes(const DirectProblem<float> &p) {
   if (p.accumulate || !eligible(p.N, p.A, p.B, p.nky, p.niy, p.noy, p.Ay, p.Cy, p.Dy)) return 0;
-  const size_t xt = round256((size_t)p.B * p.nix * p.N * sizeof(float));
-  const size_t yt = round256((size_t)p.A * p.nox * p.N * sizeof(float));
+  const size_t xt = round256((size_t)p.B * p.nix * padded_batch(p.N) * sizeof(float));
+  const size_t yt = round256((size_t)p.A * p.nox * padded_batch(p.N) * sizeof(float));
   const size_t tc = direct_tc_workspace_bytes(inner_direct(p, nullptr, nullptr));
   return tc ? xt + yt + tc : 0;
 }
@@ -150,8 +155,8 @@ int launch_direct_batch_inner(const DirectProblem<float> &p, void *workspace, si
       reinterpret_cast<uintptr_t>(workspace) % 256 != 0)
     return MELLIN_ERR_UNSUPPORTED;
   unsigned char *base = static_cast<unsigned char *>(workspace);
-  const size_t xt_bytes = round256((size_t)p.B * p.nix * p.N * sizeof(float));
-  const size_t yt_bytes = round256((size_t)p.A * p.nox * p.N * sizeof(float));
+  const size_t xt_bytes = round256((size_t)p.B * p.nix * padded_batch(p.N) * sizeof(float));
+  const size_t yt_bytes = round256((size_t)p.A * p.nox * padded_batch(p.N) * sizeof(float));
   float *xt = reinterpret_cast<float *>(base);
   float *yt = reinterpret_cast<float *>(base + xt_bytes);
   int rc = to_batch_inner(p.in, p.in_sn, p.in_sb, p.N, p.B, p.nix, xt, stream);
@@ -164,8 +169,8 @@ int launch_direct_batch_inner(const DirectProblem<float> &p, void *workspace, si
 
 size_t gradw_batch_inner_workspace_bytes(const GradWProblem<float> &p) {
   if (!eligible(p.N, p.A, p.B, p.nky, p.niy, p.noy, p.Ay, p.Cy, p.Dy)) return 0;
-  const size_t xt = round256((size_t)p.B * p.nix * p.N * sizeof(float));
-  const size_t got = round256((size_t)p.A * p.nox * p.N * sizeof(float));
+  const size_t xt = round256((size_t)p.B * p.nix * padded_batch(p.N) * sizeof(float));
+  const size_t got = round256((size_t)p.A * p.nox * padded_batch(p.N) * sizeof(float));
   const size_t tc = gradw_tc_workspace_floats(inner_gradw(p, nullptr, nullptr), nullptr) * sizeof(float);
   return tc ? xt + got + round256(tc) : 0;
 }
@@ -177,8 +182,8 @@ int launch_gradw_batch_inner(const GradWProblem<float> &p, void *workspace, size
       reinterpret_cast<uintptr_t>(workspace) % 256 != 0)
     return MELLIN_ERR_UNSUPPORTED;
   unsigned char *base = static_cast<unsigned char *>(workspace);
-  const size_t xt_bytes = round256((size_t)p.B * p.nix * p.N * sizeof(float));
-  const size_t got_bytes = round256((size_t)p.A * p.nox * p.N * sizeof(float));
+  const size_t xt_bytes = round256((size_t)p.B * p.nix * padded_batch(p.N) * sizeof(float));
+  const size_t got_bytes = round256((size_t)p.A * p.nox * padded_batch(p.N) * sizeof(float));
   float *xt = reinterpret_cast<float *>(base);
   float *got = reinterpret_cast<float *>(base + xt_bytes);
   int rc = to_batch_inner(p.in, (long long)p.B * p.nix, p.nix, p.N, p.B, p.nix, xt, stream);

@@ -5,6 +5,7 @@
 #include <cstdint>
 #include <stdexcept>
 #include <string>
+#include <type_traits>
 
 #include "../../include/mellin_b200.h"
 #include "mellin_internal.h"
@@ -131,6 +132,116 @@ int dispatch_direct(const DirectProblem<double> &p, void *, size_t, cudaStream_t
   return (rc || (p.lens == nullptr && !p.relu)) ? rc : launch_mask_relu(p, stream);
 }
 
+// ---- polyphase forms of linear stride / dilation 2 -------------------------------------
+// The tensor-core kernels take linear stride 1 and dilation 1.  A layer-level operator
+// whose linear axis has (stride, dilation) = (1, 2), (2, 1) or (2, 2) and no padding is
+// rewritten, exactly, as a stride-1 dilation-1 operator on de-interleaved tensors:
+//   (1, 2)  y[2m + q] = sum_k W[k] x[2(m + k) + q]: the two phases of x are two utterances
+//           whose outputs interleave into y (batch 2N, half the length);
+//   (2, 2)  y[h] = sum_k W[k] x[2(h + k)]: only the even phase of x is read;
+//   (2, 1)  y[h] = sum_j W[2j] x[2(h + j)] + sum_j W[2j + 1] x[2(h + j) + 1]: the phases of
+//           x become extra input channels and the kernel splits into its even and odd taps.
+// The copies are two passes over tensors the operator reads once; the products and the
+// set of terms of every sum are those of the definition.
+struct Polyphase {
+  int mode = 0;  // 1: (1, 2), 2: (2, 1), 3: (2, 2)
+  Geometry2D inner;
+  int64_t Lp = 0, Hp = 0, Kp = 0;  // half lengths of input rows, output rows, kernel taps
+};
+
+size_t round256(size_t b) { return (b + 255) / 256 * 256; }
+
+bool plan_polyphase(const Geometry2D &q, Polyphase &P) {
+  if (!tensor_cores_enabled() || q.uy != 1 || q.py != 0) return false;
+  if (q.sy == 1 && q.dy == 2) P.mode = 1;
+  else if (q.sy == 2 && q.dy == 1) P.mode = 2;
+  else if (q.sy == 2 && q.dy == 2) P.mode = 3;
+  else return false;
+  // only where the stride-1 form then runs on the tensor cores
+  if (q.c_in < 16 || q.c_out < 32 || q.ngy < 64 || q.nhy < 16 || q.nfy < 2 || q.batch < 1) return false;
+  P.Lp = (q.ngy + 1) / 2, P.Hp = (q.nhy + 1) / 2, P.Kp = (q.nfy + 1) / 2;
+  P.inner = q;
+  P.inner.sy = 1, P.inner.dy = 1, P.inner.ngy = P.Lp;
+  if (P.mode == 1) P.inner.batch = 2 * q.batch, P.inner.nhy = P.Hp;
+  if (P.mode == 2) P.inner.c_in = 2 * q.c_in, P.inner.nfy = P.Kp;
+  return true;
+}
+
+// dst[((o * phases + t) * inner + r) * Lp + m] = src[(o * inner + r) * L + 2 m + t]  (0 past the row's end)
+__global__ void deinterleave_kernel(const float *__restrict__ src, long long outer, long long inner, int L, int Lp,
+                                    int phases, float *__restrict__ dst) {
+  const long long total = outer * phases * inner * Lp;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int m = (int)(i % Lp);
+    long long r = i / Lp;
+    const long long ri = r % inner;
+    r /= inner;
+    const int t = (int)(r % phases);
+    const long long o = r / phases;
+    const int x = 2 * m + t;
+    dst[i] = x < L ? src[(o * inner + ri) * L + x] : 0.f;
+  }
+}
+// dst[(o * inner + r) * L + x] = x odd and phases == 1 ? 0 : src[((o * phases + x % 2) * inner + r) * Lp + x / 2]
+__global__ void interleave_kernel(const float *__restrict__ src, long long outer, long long inner, int L, int Lp,
+                                  int phases, float *__restrict__ dst) {
+  const long long total = outer * inner * L;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int x = (int)(i % L);
+    const long long r = i / L;
+    const long long ri = r % inner, o = r / inner;
+    const int t = x & 1;
+    dst[i] = t < phases ? src[((o * phases + t) * inner + ri) * Lp + (x >> 1)] : 0.f;
+  }
+}
+int copy_launch(bool split, const float *src, int64_t outer, int64_t inner, int64_t L, int64_t Lp, int phases, float *dst,
+                cudaStream_t stream) {
+  const long long total = split ? outer * phases * inner * Lp : outer * inner * L;
+  if (total <= 0) return MELLIN_OK;
+  const int blocks = (int)std::min<long long>((total + 255) / 256, (long long)sm_count() * 32);
+  if (split) deinterleave_kernel<<<blocks, 256, 0, stream>>>(src, outer, inner, (int)L, (int)Lp, phases, dst);
+  else interleave_kernel<<<blocks, 256, 0, stream>>>(src, outer, inner, (int)L, (int)Lp, phases, dst);
+  const cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return fail(MELLIN_ERR_LAUNCH, std::string("polyphase copy: ") + cudaGetErrorString(err));
+  count_launch();
+  return MELLIN_OK;
+}
+
+size_t direct_workspace_query(const Geometry2D &q, bool input_gradient);
+size_t gradw_workspace_query(const Geometry2D &q);
+
+// scratch of the polyphase forms: copies first, then the inner operator's own scratch
+struct PolyBuffers {
+  size_t in_copy = 0, out_copy = 0, w_copy = 0, inner = 0;
+  size_t total() const { return in_copy + out_copy + w_copy + inner; }
+};
+PolyBuffers polyphase_buffers(const Geometry2D &q, const Polyphase &P, int op /*0 fwd, 1 grad-input, 2 grad-weight*/) {
+  PolyBuffers b;
+  const Geometry2D &i = P.inner;
+  const size_t x_inner = round256((size_t)i.batch * i.c_in * i.ngx * i.ngy * sizeof(float));
+  const size_t y_inner = round256((size_t)i.batch * i.c_out * i.nhx * i.nhy * sizeof(float));
+  const size_t w_inner = round256((size_t)i.c_out * i.c_in * i.nfx * i.nfy * sizeof(float));
+  if (op == 0) {
+    b.in_copy = x_inner;
+    b.out_copy = P.mode == 1 ? y_inner : 0;
+    b.w_copy = P.mode == 2 ? w_inner : 0;
+    b.inner = direct_workspace_query(i, false);
+  } else if (op == 1) {
+    b.in_copy = P.mode == 1 ? y_inner : 0;  // de-interleaved grad_y
+    b.out_copy = x_inner;                   // grad_x of the inner problem
+    b.w_copy = P.mode == 2 ? w_inner : 0;
+    b.inner = direct_workspace_query(i, true);
+  } else {
+    b.in_copy = x_inner + (P.mode == 1 ? y_inner : 0);
+    b.out_copy = P.mode == 2 ? w_inner : 0;  // grad_w of the inner problem
+    b.inner = gradw_workspace_query(i);
+  }
+  b.inner = round256(b.inner);
+  return b;
+}
+
 template <typename T>
 int op2d(const char *who, Relation rel, const T *f, const T *g, const Geometry2D &q, int tf, int tg, int th,
          T *h, const T *bias, bool accumulate, void *workspace, size_t workspace_bytes, void *stream,
@@ -143,6 +254,35 @@ int op2d(const char *who, Relation rel, const T *f, const T *g, const Geometry2D
   const bool has_terms = q.c_in > 0 && q.nfx > 0 && q.nfy > 0 && q.ngx > 0 && q.ngy > 0;
   if (has_terms && (f == nullptr || g == nullptr))
     return fail(MELLIN_ERR_BAD_ARGUMENT, std::string(who) + ": null operand");
+  if constexpr (std::is_same<T, float>::value) {
+    Polyphase P;
+    if (rel == Relation::Corr && !accumulate && !tf && !tg && !th && has_terms && lens == nullptr && !relu &&
+        workspace != nullptr && reinterpret_cast<uintptr_t>(workspace) % 256 == 0 && plan_polyphase(q, P)) {
+      const PolyBuffers b = polyphase_buffers(q, P, 0);
+      if (workspace_bytes >= b.total()) {
+        cudaStream_t st = static_cast<cudaStream_t>(stream);
+        unsigned char *base = static_cast<unsigned char *>(workspace);
+        float *xc = reinterpret_cast<float *>(base), *yc = reinterpret_cast<float *>(base + b.in_copy);
+        float *wc = reinterpret_cast<float *>(base + b.in_copy + b.out_copy);
+        void *inner_ws = base + b.in_copy + b.out_copy + b.w_copy;
+        const int64_t rows_x = q.c_in * q.ngx;
+        if (P.mode == 1) rc = copy_launch(true, g, 1, q.batch * rows_x, q.ngy, P.Lp, 2, xc, st);
+        else if (P.mode == 2) rc = copy_launch(true, g, q.batch, rows_x, q.ngy, P.Lp, 2, xc, st);
+        else rc = copy_launch(true, g, 1, q.batch * rows_x, q.ngy, P.Lp, 1, xc, st);
+        if (rc) return rc;
+        const float *w_in = f;
+        if (P.mode == 2) {
+          rc = copy_launch(true, f, q.c_out, q.c_in * q.nfx, q.nfy, P.Kp, 2, wc, st);
+          if (rc) return rc;
+          w_in = wc;
+        }
+        float *y_out = P.mode == 1 ? yc : h;
+        rc = op2d<float>(who, rel, w_in, xc, P.inner, 0, 0, 0, y_out, bias, false, inner_ws, b.inner, stream);
+        if (rc || P.mode != 1) return rc;
+        return copy_launch(false, yc, 1, q.batch * q.c_out * q.nhx, q.nhy, P.Hp, 2, h, st);
+      }
+    }
+  }
   DirectProblem<T> p;
   rc = get_device_table(IndexMapKey{rel, SortBy::H, has_terms ? q.nfx : 0, q.ngx, q.nhx, q.sx, q.dx, q.px, q.ux},
                         &p.table);
@@ -177,6 +317,36 @@ int grad_input(const char *who, const T *w, const T *go, const Geometry2D &q, T 
   const bool has_terms = q.c_out > 0 && q.nfx > 0 && q.nfy > 0 && q.nhx > 0 && q.nhy > 0;
   if (has_terms && (w == nullptr || go == nullptr))
     return fail(MELLIN_ERR_BAD_ARGUMENT, std::string(who) + ": null operand");
+  if constexpr (std::is_same<T, float>::value) {
+    Polyphase P;
+    if (has_terms && lens == nullptr && workspace != nullptr && reinterpret_cast<uintptr_t>(workspace) % 256 == 0 &&
+        plan_polyphase(q, P)) {
+      const PolyBuffers b = polyphase_buffers(q, P, 1);
+      if (workspace_bytes >= b.total()) {
+        cudaStream_t st = static_cast<cudaStream_t>(stream);
+        unsigned char *base = static_cast<unsigned char *>(workspace);
+        float *goc = reinterpret_cast<float *>(base), *gxc = reinterpret_cast<float *>(base + b.in_copy);
+        float *wc = reinterpret_cast<float *>(base + b.in_copy + b.out_copy);
+        void *inner_ws = base + b.in_copy + b.out_copy + b.w_copy;
+        const float *go_in = go, *w_in = w;
+        if (P.mode == 1) {
+          rc = copy_launch(true, go, 1, q.batch * q.c_out * q.nhx, q.nhy, P.Hp, 2, goc, st);
+          if (rc) return rc;
+          go_in = goc;
+        }
+        if (P.mode == 2) {
+          rc = copy_launch(true, w, q.c_out, q.c_in * q.nfx, q.nfy, P.Kp, 2, wc, st);
+          if (rc) return rc;
+          w_in = wc;
+        }
+        rc = grad_input<float>(who, w_in, go_in, P.inner, gxc, inner_ws, b.inner, stream);
+        if (rc) return rc;
+        const int64_t rows_x = q.c_in * q.ngx;
+        if (P.mode == 2) return copy_launch(false, gxc, q.batch, rows_x, q.ngy, P.Lp, 2, gx, st);
+        return copy_launch(false, gxc, 1, q.batch * rows_x, q.ngy, P.Lp, P.mode == 1 ? 2 : 1, gx, st);
+      }
+    }
+  }
   DirectProblem<T> p;
   rc = get_device_table(
       IndexMapKey{Relation::Corr, SortBy::G, has_terms ? q.nfx : 0, q.ngx, q.nhx, q.sx, q.dx, q.px, q.ux}, &p.table);
@@ -232,6 +402,35 @@ int grad_weight(const char *who, const T *x, const T *go, const Geometry2D &q, T
     return fail(MELLIN_ERR_BAD_ARGUMENT, std::string(who) + ": null operand");
   if (gb != nullptr && has_terms && go == nullptr)
     return fail(MELLIN_ERR_BAD_ARGUMENT, std::string(who) + ": null grad_y");
+  if constexpr (std::is_same<T, float>::value) {
+    Polyphase P;
+    if (has_terms && gw_elems > 0 && lens == nullptr && workspace != nullptr &&
+        reinterpret_cast<uintptr_t>(workspace) % 256 == 0 && plan_polyphase(q, P)) {
+      const PolyBuffers b = polyphase_buffers(q, P, 2);
+      if (workspace_bytes >= b.total()) {
+        cudaStream_t st = static_cast<cudaStream_t>(stream);
+        unsigned char *base = static_cast<unsigned char *>(workspace);
+        const Geometry2D &i = P.inner;
+        const size_t x_inner = round256((size_t)i.batch * i.c_in * i.ngx * i.ngy * sizeof(float));
+        float *xc = reinterpret_cast<float *>(base), *goc = reinterpret_cast<float *>(base + x_inner);
+        float *gwc = reinterpret_cast<float *>(base + b.in_copy);
+        void *inner_ws = base + b.in_copy + b.out_copy;
+        const int64_t rows_x = q.c_in * q.ngx;
+        if (P.mode == 2) rc = copy_launch(true, x, q.batch, rows_x, q.ngy, P.Lp, 2, xc, st);
+        else rc = copy_launch(true, x, 1, q.batch * rows_x, q.ngy, P.Lp, P.mode == 1 ? 2 : 1, xc, st);
+        if (rc) return rc;
+        const float *go_in = go;
+        if (P.mode == 1) {
+          rc = copy_launch(true, go, 1, q.batch * q.c_out * q.nhx, q.nhy, P.Hp, 2, goc, st);
+          if (rc) return rc;
+          go_in = goc;
+        }
+        rc = grad_weight<float>(who, xc, go_in, P.inner, P.mode == 2 ? gwc : gw, gb, inner_ws, b.inner, stream);
+        if (rc || P.mode != 2) return rc;
+        return copy_launch(false, gwc, q.c_out, q.c_in * q.nfx, q.nfy, P.Kp, 2, gw, st);
+      }
+    }
+  }
   p.in = x, p.go = go, p.gw = gw, p.gb = gb;
   p.lens = q.nhy > 1 ? lens : nullptr;
   if (gw_elems == 0 && (gb == nullptr || q.c_out == 0)) return MELLIN_OK;
@@ -401,8 +600,14 @@ int mellin_selftest_unarmed_wait(void *stream) { return launch_unarmed_wait(stat
 
 // Workspace queries plan with the extents only (tables are not needed: the
 // longest table row is bounded by the kernel extent along the Mellin axis).
-static size_t direct_workspace_query(const Geometry2D &q, bool input_gradient) {
+}  // extern "C"
+namespace {
+size_t direct_workspace_query(const Geometry2D &q, bool input_gradient) {
   if (check_geometry("workspace_bytes", q, input_gradient ? q.sy : q.uy)) return 0;
+  {
+    Polyphase P;
+    if (plan_polyphase(q, P)) return polyphase_buffers(q, P, input_gradient ? 1 : 0).total();
+  }
   DirectProblem<float> p;
   p.N = (int)q.batch;
   p.A = input_gradient ? (int)q.c_in : (int)q.c_out;
@@ -421,6 +626,21 @@ static size_t direct_workspace_query(const Geometry2D &q, bool input_gradient) {
   return std::max(std::max(rows, direct_tc_workspace_bytes(p)),
                   std::max(direct_batch_inner_workspace_bytes(p), direct_repitch_workspace_bytes(p)));
 }
+size_t gradw_workspace_query(const Geometry2D &q) {
+  {
+    Polyphase P;
+    if (check_geometry("grad_weight_workspace_bytes", q, q.uy) == MELLIN_OK && plan_polyphase(q, P))
+      return polyphase_buffers(q, P, 2).total();
+  }
+  GradWProblem<float> p;
+  if (make_gradw_problem<float>("grad_weight_workspace_bytes", q, &p, false)) return 0;
+  // planning only looks at extents, parameters and pointer alignment; probe
+  // with an aligned dummy so that the answer is an upper bound for any buffer
+  p.go = reinterpret_cast<const float *>(uintptr_t(256));
+  return gradw_workspace_bytes<float>(p);
+}
+}  // namespace
+extern "C" {
 size_t mellin_mcorrlcorr_forward_workspace_bytes(MELLIN_LAYER_GEOMETRY) {
   return direct_workspace_query(GEOM_FROM_LAYER, false);
 }
@@ -453,12 +673,7 @@ int64_t mellin_index_map_build(int relation, int order, int64_t nf, int64_t ng, 
 }
 
 size_t mellin_mcorrlcorr_grad_weight_workspace_bytes(MELLIN_LAYER_GEOMETRY) {
-  GradWProblem<float> p;
-  if (make_gradw_problem<float>("grad_weight_workspace_bytes", GEOM_FROM_LAYER, &p, false)) return 0;
-  // planning only looks at extents, parameters and pointer alignment; probe
-  // with an aligned dummy so that the answer is an upper bound for any buffer
-  p.go = reinterpret_cast<const float *>(uintptr_t(256));
-  return gradw_workspace_bytes<float>(p);
+  return gradw_workspace_query(GEOM_FROM_LAYER);
 }
 
 }  // extern "C"
