@@ -770,6 +770,13 @@ def bench_sweep(ctx, peaks):
                                         ("grad_weight", lambda: capi.grad_weight(x, go, gw, gb, S, D, P, U))):
                             ms = ctx.time_ms(fn, iters=2, warm=1)
                             cell[key] = {"ms": ms, "tflops_fp32_equiv": flop / ms / 1e9}
+                        if s == 1 and d == 1:
+                            # the reference-shaped operator (accumulates into y, no workspace argument) on the same data
+                            if kind == "mcorr1d":
+                                op = lambda: capi.op1d("mcorr1d", w[..., 0], x[..., 0], y[..., 0], C, C, N, s, d, 0, 1)
+                            else:
+                                op = lambda: capi.op2d("mcorrlcorr", w, x, y, C, C, N, S, D, P, U)
+                            cell["operator_level_forward_ms"] = ctx.time_ms(op, iters=2, warm=1)
                         ms = ctx.time_ms(fwd_bwd, iters=2, warm=1)
                         cell["fwd_bwd_ms"] = ms
                         cell["tflops_fp32_equiv"] = 3 * flop / ms / 1e9
@@ -816,6 +823,45 @@ def bench_latency(ctx):
                     "config[0] shapes, r = 0 (16 outputs per row)"}
 
 
+def bench_incumbent():
+    """The reference's own CUDA kernels (its stock thread-per-output kernels, unmodified, compiled for sm_100a by
+    oracle/build_oracle.py into oracle/_ref/mconv_cuda_profiling) at the headline layer, timed by the reference's
+    own harness (CUDA events around back-to-back launches on uninitialised buffers).  Roles as the reference's
+    backward assigns them (ext/torch.cpp:261-308): grad-input is its convolution kernel over grad_out with the
+    channel roles swapped, grad-weight its correlation kernel with batch and channels transposed."""
+    import re
+
+    exe = os.path.join(ROOT, "oracle", "_ref", "mconv_cuda_profiling")
+    if not os.path.isfile(exe):
+        return {"unavailable": "oracle/_ref/mconv_cuda_profiling was not built (no reference checkout at build time)"}
+    w = WORKLOAD
+    common = ["-t", "float", "--px", "0", "--py", "1"]
+    runs = {
+        "forward": ["-k", "MCorrLCorr", "--c-out", str(w["c_out"]), "--c-in", str(w["c_in"]), "--batch", str(w["batch"]),
+                    "--nfx", str(w["nf"][0]), "--nfy", str(w["nf"][1]), "--ngx", str(w["ng"][0]), "--ngy", str(w["ng"][1]),
+                    "-n", "5", "--burn-in", "2"],
+        "grad_input": ["-k", "MConvLConv", "--c-out", str(w["c_in"]), "--c-in", str(w["c_out"]), "--batch", str(w["batch"]),
+                       "--nfx", str(w["nf"][0]), "--nfy", str(w["nf"][1]), "--ngx", str(w["ng"][0]), "--ngy", str(w["ng"][1]),
+                       "-n", "5", "--burn-in", "2"],
+        # "kernel" = grad_out^T (c_out, batch, 41, 800), "input" = x^T (c_in, batch, 41, 800), output (c_in, c_out, 8, 3)
+        "grad_weight": ["-k", "MCorrLCorr", "--c-out", str(w["c_out"]), "--c-in", str(w["batch"]), "--batch", str(w["c_in"]),
+                        "--nfx", str(w["ng"][0]), "--nfy", str(w["ng"][1]), "--ngx", str(w["ng"][0]), "--ngy", str(w["ng"][1]),
+                        "--rx", str(w["nf"][0] - 1), "--ry", "1", "--transpose-f", "--transpose-g", "--transpose-h",
+                        "-n", "2", "--burn-in", "1"],
+    }
+    out = {}
+    for name, extra in runs.items():
+        try:
+            proc = subprocess.run([exe] + extra + common, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
+                                  timeout=120)
+            m = re.search(r"average ([0-9.eE+-]+)ms", proc.stdout)
+            out[name] = {"ms": float(m.group(1))} if (m and proc.returncode == 0) else {"error": proc.stdout[-300:]}
+        except subprocess.TimeoutExpired:
+            out[name] = {"error": "no result within 120 s"}
+    out["what"] = "reference's stock CUDA kernels (mconv_cuda.cuh, 32-thread blocks, one thread per output) on this GPU"
+    return out
+
+
 def run_ours(args):
     ctx = Ctx(args)
     rank, world = ctx.rank, ctx.world
@@ -846,6 +892,9 @@ def run_ours(args):
         line["train_step"] = bench_train_step(ctx)
     if rank == 0:
         if world == 1:
+            if "incumbent" not in skip:
+                ctx.torch.cuda.synchronize()
+                line["gpu_incumbent"] = bench_incumbent()
             line["cpu_baseline"] = cpu_baseline_leg()  # timed on rank 0 of the single-GPU run only
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -864,7 +913,7 @@ def main():
                          "not for bench lines")
     ap.add_argument("--kernels-only", action="store_true",
                     help="one timed block of the headline kernels only (profiler captures)")
-    ap.add_argument("--skip", default="", help="comma-separated blocks to leave out: train, layers, sweep, latency")
+    ap.add_argument("--skip", default="", help="comma-separated blocks to leave out: train, layers, sweep, latency, incumbent")
     ap.add_argument("--layer", default="3to64", choices=sorted(PROFILE_LAYERS),
                     help="with --kernels-only: time another layer of the reference's stacks (profiler captures of the "
                          "wide-layer kernels); bench lines are always the 3to64 layer")

@@ -127,6 +127,52 @@ int dispatch_direct(const DirectProblem<float> &p, void *workspace, size_t works
   }
   return launch_direct<float>(p, stream);
 }
+// out[n, a, :] += tmp[n, a, :] for a dense tmp and an `out` with arbitrary (n, a) strides
+__global__ void add_into_kernel(const float *__restrict__ tmp, float *__restrict__ out, long long plane, int A,
+                                long long out_sn, long long out_sa, long long total) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long na = i / plane, r = i - na * plane;
+    const long long n = na / A, a = na - n * A;
+    out[n * out_sn + a * out_sa + r] += tmp[i];
+  }
+}
+
+int add_into(const float *tmp, float *out, long long plane, int A, long long n_count, long long out_sn, long long out_sa,
+             cudaStream_t stream) {
+  const long long total = n_count * A * plane;
+  if (total <= 0) return MELLIN_OK;
+  const int blocks = (int)std::min<long long>((total + 255) / 256, (long long)sm_count() * 32);
+  add_into_kernel<<<blocks, 256, 0, stream>>>(tmp, out, plane, A, out_sn, out_sa, total);
+  const cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return fail(MELLIN_ERR_LAUNCH, std::string("add_into_kernel: ") + cudaGetErrorString(err));
+  count_launch();
+  return MELLIN_OK;
+}
+
+// Operator-level calls accumulate into their output and bring no workspace (the reference's
+// signatures have none).  Where a tensor-core kernel covers the problem it is run into
+// library-owned scratch and the result added to the output: two more passes over the
+// output, against per-output kernels that are orders of magnitude slower at wide channels.
+int dispatch_accumulating(const DirectProblem<float> &p, cudaStream_t stream) {
+  if (!p.accumulate || !tensor_cores_enabled() || p.A <= 4 || p.B < 16) return MELLIN_ERR_UNSUPPORTED;
+  DirectProblem<float> q = p;
+  q.accumulate = false, q.bias = nullptr, q.lens = nullptr, q.relu = 0;
+  const long long plane = (long long)p.nox * p.noy;
+  q.out_sa = plane, q.out_sn = plane * p.A;
+  const size_t ws = std::max(std::max(direct_tc_workspace_bytes(q), direct_batch_inner_workspace_bytes(q)),
+                             direct_repitch_workspace_bytes(q));
+  if (ws == 0) return MELLIN_ERR_UNSUPPORTED;
+  const size_t out_bytes = ((size_t)p.N * p.A * plane * sizeof(float) + 255) / 256 * 256;
+  unsigned char *arena = static_cast<unsigned char *>(scratch_arena(out_bytes + ws + 256, stream));
+  if (arena == nullptr) return MELLIN_ERR_UNSUPPORTED;  // no memory for the scratch: the slow kernels need none
+  q.out = reinterpret_cast<float *>(arena);
+  int rc = dispatch_direct(q, arena + out_bytes, ws + 256, stream);
+  if (rc) return rc;
+  return add_into(q.out, p.out, plane, p.A, p.N, p.out_sn, p.out_sa, stream);
+}
+int dispatch_accumulating(const DirectProblem<double> &, cudaStream_t) { return MELLIN_ERR_UNSUPPORTED; }
+
 int dispatch_direct(const DirectProblem<double> &p, void *, size_t, cudaStream_t stream) {
   const int rc = launch_direct<double>(p, stream);
   return (rc || (p.lens == nullptr && !p.relu)) ? rc : launch_mask_relu(p, stream);
@@ -211,6 +257,8 @@ int copy_launch(bool split, const float *src, int64_t outer, int64_t inner, int6
 
 size_t direct_workspace_query(const Geometry2D &q, bool input_gradient);
 size_t gradw_workspace_query(const Geometry2D &q);
+int add_into(const float *tmp, float *out, long long plane, int A, long long n_count, long long out_sn, long long out_sa,
+             cudaStream_t stream);
 
 // scratch of the polyphase forms: copies first, then the inner operator's own scratch
 struct PolyBuffers {
@@ -256,6 +304,20 @@ int op2d(const char *who, Relation rel, const T *f, const T *g, const Geometry2D
     return fail(MELLIN_ERR_BAD_ARGUMENT, std::string(who) + ": null operand");
   if constexpr (std::is_same<T, float>::value) {
     Polyphase P;
+    if (rel == Relation::Corr && accumulate && workspace == nullptr && !tf && !tg && has_terms && plan_polyphase(q, P)) {
+      // operator-level call of a strided / dilated linear operator: the polyphase form into library scratch, then h += it
+      const size_t out_bytes = round256((size_t)out_elems * sizeof(float));
+      const size_t ws = polyphase_buffers(q, P, 0).total();
+      unsigned char *arena = static_cast<unsigned char *>(scratch_arena(out_bytes + ws + 256, static_cast<cudaStream_t>(stream)));
+      if (arena != nullptr) {
+        float *tmp = reinterpret_cast<float *>(arena);
+        rc = op2d<float>(who, rel, f, g, q, 0, 0, 0, tmp, nullptr, false, arena + out_bytes, ws + 256, stream);
+        if (rc) return rc;
+        const int64_t hp = q.nhx * q.nhy;
+        return add_into(tmp, h, hp, (int)q.c_out, q.batch, th ? hp : q.c_out * hp, th ? q.batch * hp : hp,
+                        static_cast<cudaStream_t>(stream));
+      }
+    }
     if (rel == Relation::Corr && !accumulate && !tf && !tg && !th && has_terms && lens == nullptr && !relu &&
         workspace != nullptr && reinterpret_cast<uintptr_t>(workspace) % 256 == 0 && plan_polyphase(q, P)) {
       const PolyBuffers b = polyphase_buffers(q, P, 0);
@@ -304,6 +366,10 @@ int op2d(const char *who, Relation rel, const T *f, const T *g, const Geometry2D
   p.Dy = (int)q.uy;
   p.accumulate = accumulate;
   p.lens = lens, p.relu = relu;
+  if (accumulate && workspace == nullptr) {
+    rc = dispatch_accumulating(p, static_cast<cudaStream_t>(stream));
+    if (rc != MELLIN_ERR_UNSUPPORTED) return rc;
+  }
   return dispatch_direct(p, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 

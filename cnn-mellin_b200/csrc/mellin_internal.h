@@ -30,6 +30,8 @@ struct DeviceTable {
 // once per geometry per device).  Returns a status code.
 int get_device_table(const IndexMapKey &key, DeviceTable *out);
 int clear_device_tables();
+// library-owned scratch of the operator-level entry points (table_cache.cu); nullptr when it cannot be had
+void *scratch_arena(size_t bytes, cudaStream_t stream);
 int sm_count();  // of the current device (cached)
 
 // ---- problem descriptions ------------------------------------------------------

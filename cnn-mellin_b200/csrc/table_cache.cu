@@ -23,7 +23,38 @@ struct CachedTable {
 std::mutex g_mutex;
 std::map<std::pair<int, IndexMapKey>, CachedTable> g_tables;
 std::map<int, int> g_sm_count;
+struct Arena {
+  void *ptr = nullptr;
+  size_t bytes = 0;
+};
+std::map<std::pair<int, cudaStream_t>, Arena> g_arenas;
 }  // namespace
+
+// Scratch owned by the library for the operator-level entry points, whose
+// reference signatures have no workspace argument: one arena per (device,
+// stream), grown on demand (growing synchronises the stream and reallocates --
+// a set-up cost of the first call of a larger geometry) and kept until
+// mellin_clear_tables().  Returns nullptr when the allocation fails.
+void *scratch_arena(size_t bytes, cudaStream_t stream) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  Arena &a = g_arenas[std::make_pair(dev, stream)];
+  if (a.bytes >= bytes) return a.ptr;
+  if (a.ptr != nullptr) {
+    if (cudaStreamSynchronize(stream) != cudaSuccess) return nullptr;  // earlier calls may still be using it
+    cudaFree(a.ptr);
+    a.ptr = nullptr, a.bytes = 0;
+  }
+  const size_t want = bytes + bytes / 8;  // a little head-room: geometries of one model differ slightly
+  if (cudaMalloc(&a.ptr, want) != cudaSuccess) {
+    cudaGetLastError();
+    a.ptr = nullptr;
+    return nullptr;
+  }
+  a.bytes = want;
+  return a.ptr;
+}
 
 void set_error(const std::string &msg) { g_last_error = msg; }
 int fail(int code, const std::string &msg) {
@@ -105,7 +136,16 @@ int get_device_table(const IndexMapKey &key, DeviceTable *out) {
 int clear_device_tables() {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return MELLIN_ERR_LAUNCH;
+  cudaDeviceSynchronize();  // nothing in flight may still read what is freed below
   std::lock_guard<std::mutex> lock(g_mutex);
+  for (auto it = g_arenas.begin(); it != g_arenas.end();) {
+    if (it->first.first == dev) {
+      cudaFree(it->second.ptr);
+      it = g_arenas.erase(it);
+    } else {
+      ++it;
+    }
+  }
   for (auto it = g_tables.begin(); it != g_tables.end();) {
     if (it->first.first == dev) {
       cudaFree(it->second.block);

@@ -9,6 +9,9 @@ TEST INFRASTRUCTURE (see oracle.py).  Two shared libraries:
   the reference is present (its sources are compiled where they lie and are
   never copied).  ``-O3 -fopenmp`` so that its OpenMP loops use every host core.
 
+* ``oracle/_ref/mconv_cuda_profiling`` -- the reference's own CUDA timing harness,
+  compiled for sm_100a where a checkout is present: the GPU incumbent of the benchmark.
+
 Run ``python oracle/build_oracle.py`` or call :func:`build`.
 """
 import os
@@ -74,11 +77,38 @@ def build_reference(force=False):
     return REF_SO
 
 
+REF_GPU_PROFILER = os.path.join(HERE, "_ref", "mconv_cuda_profiling")
+
+
+def build_reference_gpu_profiler(force=False):
+    """The reference's own CUDA timing harness (c/performance/mconv_cuda_profiling.cu: its stock
+    thread-per-output kernels behind a command line), compiled for sm_100a from the sources where
+    they lie.  It is the GPU incumbent the benchmark quotes beside this library's kernels.  Returns
+    the binary's path, or None when neither a checkout nor a prebuilt binary is there."""
+    inc = reference_include_dir()
+    if inc is None:
+        return REF_GPU_PROFILER if os.path.isfile(REF_GPU_PROFILER) else None
+    root = os.path.dirname(os.path.dirname(inc))  # .../ext/include -> checkout root
+    perf = os.path.join(root, "c", "performance")
+    srcs = [os.path.join(perf, "mconv_cuda_profiling.cu"), os.path.join(perf, "OptionParser.cpp")]
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not all(os.path.isfile(s) for s in srcs) or not os.path.isfile(nvcc):
+        return REF_GPU_PROFILER if os.path.isfile(REF_GPU_PROFILER) else None
+    if not force and _newer(REF_GPU_PROFILER, srcs):
+        return REF_GPU_PROFILER
+    os.makedirs(os.path.dirname(REF_GPU_PROFILER), exist_ok=True)
+    _run([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++14",
+          "-I", os.path.join(root, "c", "cuda", "include"), "-I", os.path.join(root, "c", "cpu", "include"), "-I", inc,
+          "-o", REF_GPU_PROFILER] + srcs + ["-lcublas"])
+    return REF_GPU_PROFILER
+
+
 def build(force=False):
-    return build_port(force), build_reference(force)
+    return build_port(force), build_reference(force), build_reference_gpu_profiler(force)
 
 
 if __name__ == "__main__":
-    port, ref = build(force="--force" in sys.argv)
+    port, ref, gpu = build(force="--force" in sys.argv)
     print("port:", port)
     print("reference:", ref)
+    print("reference GPU profiler:", gpu)

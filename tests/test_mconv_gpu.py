@@ -290,6 +290,48 @@ def test_half_tensors_and_column_operators(mconv):
     assert torch.equal(y, mconv.mcorrlcorr(x.float(), w.float(), _impl="direct").half())
 
 
+def test_half_operators_match_the_oracle_on_the_rounded_inputs(mconv):
+    """The reference computes float16 tensors with a float32 accumulator (mconv_cuda.cuh:135-139) and rounds the
+    result.  Oracle: its float32 CPU kernels on the float16-rounded operands; tolerance one float16 unit
+    (2^-10 relative to the tensor's largest value) for outputs and gradients."""
+    import numpy as np
+
+    import helpers
+    from oracle.oracle import Oracle
+
+    oracle = Oracle("reference") if Oracle.reference_available() else Oracle("port")
+    half_ulp = 2.0 ** -10
+    torch.manual_seed(11)
+    for n, ci, co, ng, nf, d in ((3, 3, 16, (12, 40), (4, 3), (1, 1)), (2, 24, 40, (12, 64), (4, 3), (2, 1))):
+        s, p = (1, 1), (0, 1)
+        r = (ng[0] - mconv.mcorr_valid_size(nf[0], ng[0], 1, d[0]), 1)
+        x = torch.randn((n, ci) + ng, device="cuda").half().requires_grad_(True)
+        w = (torch.randn((co, ci) + nf, device="cuda") / (ci * nf[0] * nf[1]) ** 0.5).half().requires_grad_(True)
+        b = torch.randn(co, device="cuda").half().requires_grad_(True)
+        y = mconv.mcorrlcorr(x, w, b, s, d, p, r, _impl="direct")
+        assert y.dtype == torch.half
+        go = torch.randn_like(y)
+        y.backward(go)
+        x_h, w_h, b_h, go_h = (t.detach().float().cpu().numpy() for t in (x, w, b, go))
+        y_exp = oracle.mcorrlcorr(x_h, w_h, b_h, s, d, p, (1, 1), r)
+        gx_exp, gw_exp, gb_exp = oracle.mcorrlcorr_backward(x_h, w_h, go_h, s, d, p, (1, 1))
+        assert helpers.rel_err(y.detach().float().cpu().numpy(), y_exp) <= half_ulp
+        assert x.grad.dtype == torch.half and w.grad.dtype == torch.half
+        assert helpers.rel_err(x.grad.float().cpu().numpy(), gx_exp) <= half_ulp
+        assert helpers.rel_err(w.grad.float().cpu().numpy(), gw_exp) <= half_ulp
+        assert helpers.rel_err(b.grad.float().cpu().numpy(), gb_exp) <= half_ulp
+    # autocast: float32 parameters and inputs, float16 arithmetic inputs and result
+    x = torch.randn(4, 24, 12, 64, device="cuda")
+    w = torch.randn(40, 24, 4, 3, device="cuda") / 17.0
+    b = torch.randn(40, device="cuda")
+    with torch.autocast("cuda"):
+        got = mconv.mcorrlcorr(x, w, b, _impl="direct")
+    assert got.dtype == torch.half
+    exp = oracle.mcorrlcorr(x.half().float().cpu().numpy(), w.half().float().cpu().numpy(),
+                            b.half().float().cpu().numpy(), 1, 1, 0, 1, 0)
+    assert helpers.rel_err(got.float().cpu().numpy(), exp) <= half_ulp
+
+
 # ---- three stacked layers with ReLU and length masks against the reference extension ----
 def test_three_layer_stack_matches_the_reference_extension(mconv):
     """The reference's three-layer stack at reduced width (tests/golden/make_golden.py,

@@ -145,3 +145,84 @@ def test_full_size_sweep_cells_match_the_definition(kind, sd):
     assert abs(float((gx.double() * x.double()).sum()) - form) <= F32_TOL * scale
     assert abs(float((gw.double() * w.double()).sum()) - form) <= F32_TOL * scale
     assert capi.device_status() == 0
+
+
+# ---- operator-level entry points (accumulate into h, transposition flags, no workspace) on wide layers ----
+@pytest.mark.parametrize("flags", [(0, 0, 0), (1, 0, 0), (0, 1, 0), (0, 0, 1), (1, 1, 1)], ids=lambda f: "t%d%d%d" % f)
+@pytest.mark.parametrize("kind", ["corr", "conv"])
+def test_operator_level_calls_on_wide_layers_match_the_oracle(oracle, kind, flags):
+    """These reach the tensor-core kernels through library-owned scratch; the oracle is the reference's own
+    operator with the same flags, accumulating into the same pre-filled output."""
+    tf, tg, th = flags
+    n, ci, co, ng, nf = 3, 24, 40, (12, 96), (4, 3)
+    s, d, p, u = (1, 1), (2, 1), (0, 1), (1, 1)
+    rng = np.random.default_rng(41)
+    f_h = (rng.standard_normal(((ci, co) if tf else (co, ci)) + nf) / np.sqrt(ci * 12)).astype(np.float32)
+    g_h = rng.standard_normal(((ci, n) if tg else (n, ci)) + ng).astype(np.float32)
+    if kind == "corr":
+        nh = (ng[0], oracle.lcorr_valid_size(nf[1], ng[1], s[1], d[1], p[1], u[1]) + 1)
+    else:
+        nh = (oracle.mconv_support_size(nf[0], ng[0], s[0], d[0], p[0], u[0]),
+              oracle.lconv_valid_size(nf[1], ng[1], s[1], d[1], p[1], u[1]) + 2)
+    h0 = rng.standard_normal(((co, n) if th else (n, co)) + nh).astype(np.float32)
+    h_exp = oracle.op2d(kind, f_h, g_h, h0.copy(), co, ci, n, s, d, p, u, bool(tf), bool(tg), bool(th))
+    f, g, h = (torch.from_numpy(a).cuda() for a in (f_h, g_h, h0))
+    capi.op2d("mcorrlcorr" if kind == "corr" else "mconvlconv", f, g, h, co, ci, n, s, d, p, u, bool(tf), bool(tg), bool(th))
+    torch.cuda.synchronize()
+    assert helpers.rel_err(h.cpu().numpy(), h_exp) <= F32_TOL
+    assert capi.device_status() == 0
+
+
+@pytest.mark.parametrize("sd", [(1, 1), (2, 1), (1, 2), (2, 2)], ids=lambda v: "s%d_d%d" % v)
+def test_operator_level_linear_1d_variants_match_the_oracle(oracle, sd):
+    n, ci, co, length, taps = 2, 16, 32, 200, 8
+    s, d = (1, sd[0]), (1, sd[1])
+    rng = np.random.default_rng(43)
+    f_h = (rng.standard_normal((co, ci, 1, taps)) / np.sqrt(ci * taps)).astype(np.float32)
+    g_h = rng.standard_normal((n, ci, 1, length)).astype(np.float32)
+    nh = (1, oracle.lcorr_valid_size(taps, length, sd[0], sd[1], 0, 1))
+    h0 = rng.standard_normal((n, co) + nh).astype(np.float32)
+    h_exp = oracle.op2d("corr", f_h, g_h, h0.copy(), co, ci, n, s, d, (0, 0), (1, 1))
+    f, g, h = (torch.from_numpy(a).cuda() for a in (f_h, g_h, h0))
+    capi.op2d("mcorrlcorr", f, g, h, co, ci, n, s, d, (0, 0), (1, 1))
+    torch.cuda.synchronize()
+    assert helpers.rel_err(h.cpu().numpy(), h_exp) <= F32_TOL
+
+
+def test_operator_level_1d_mellin_reaches_the_fast_kernels(oracle):
+    """mellin_mcorr1d_f32 / mellin_mconv1d_f32 at the sweep's channel counts (reduced length and batch): parity with
+    the oracle, and a time that is the tensor-core path's, not the per-output kernel's."""
+    n, c, length, taps = 8, 256, 2048, 64
+    rng = np.random.default_rng(47)
+    f_h = (rng.standard_normal((c, c, taps)) / np.sqrt(c * taps)).astype(np.float32)
+    g_h = rng.standard_normal((n, c, length)).astype(np.float32)
+    f, g = torch.from_numpy(f_h).cuda(), torch.from_numpy(g_h).cuda()
+    for kind, name in (("corr", "mcorr1d"), ("conv", "mconv1d")):
+        nh = length if kind == "corr" else oracle.mconv_support_size(taps, length, 1, 1, 0, 1) // 4
+        h = torch.zeros((n, c, nh), device="cuda")
+        capi.op1d(name, f, g, h, c, c, n, 1, 1, 0, 1)  # warm-up: tables, scratch
+        h.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        capi.op1d(name, f, g, h, c, c, n, 1, 1, 0, 1)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        # sampled outputs in float64 from the definition
+        worst, scale = 0.0, float(h.abs().max())
+        fd, gd = f.double(), g.double()
+        ks = torch.arange(taps, device="cuda")
+        for _ in range(10):
+            b, a, t = int(rng.integers(n)), int(rng.integers(c)), int(rng.integers(nh))
+            if kind == "corr":
+                idx = (t + 1) * (ks + 1) - 1
+                ok = idx < length
+            else:
+                ok = ((t + 1) % (ks + 1)) == 0
+                idx = torch.div(t + 1, ks + 1, rounding_mode="floor") - 1
+                ok = ok & (idx >= 0) & (idx < length)
+            total = float((fd[a][:, ks[ok]] * gd[b][:, idx[ok]]).sum())
+            worst = max(worst, abs(float(h[b, a, t]) - total) / scale)
+        assert worst <= F32_TOL, (name, worst)
+        flop = 2.0 * n * c * c * (77701 / 16384.0 * nh if kind == "corr" else nh * 4)  # rough: pairs per output
+        assert ms < 20.0, "%s took %.1f ms: the per-output kernel, not the tensor-core path" % (name, ms)
