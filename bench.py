@@ -535,7 +535,6 @@ def bench_headline(ctx, sampler):
         counter["next_step"] += 1
         upload(timed)  # the next step's batch
         main_stream.wait_event(uploaded[k])
-        read_back(k)  # the host is done with this bucket's previous download before the bucket is reused
         xin = x_bufs[k].detach().requires_grad_(True)
         e2e_buckets[k].flat.zero_()
         layer.weight.grad, layer.bias.grad = e2e_buckets[k].views()  # autograd accumulates into the bucket
@@ -545,6 +544,7 @@ def bench_headline(ctx, sampler):
         if world > 1:
             works[k] = e2e_buckets[k].all_reduce(async_op=True)
         download(1 - k)  # the previous step's gradients, reduced while this step ran
+        read_back(k)     # the download queued one step ago (long finished): the host never stalls the device
 
     def read_back(k):
         downloaded[k].synchronize()
