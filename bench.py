@@ -914,6 +914,9 @@ def main():
     ap.add_argument("--kernels-only", action="store_true",
                     help="one timed block of the headline kernels only (profiler captures)")
     ap.add_argument("--skip", default="", help="comma-separated blocks to leave out: train, layers, sweep, latency, incumbent")
+    ap.add_argument("--engine", default="tensor_cores", choices=["tensor_cores", "cuda_cores"],
+                    help="with --kernels-only: cuda_cores switches the tcgen05 kernels off (profiler captures of the "
+                         "CUDA-core kernels); bench lines always run the default engine")
     ap.add_argument("--layer", default="3to64", choices=sorted(PROFILE_LAYERS),
                     help="with --kernels-only: time another layer of the reference's stacks (profiler captures of the "
                          "wide-layer kernels); bench lines are always the 3to64 layer")
@@ -923,6 +926,12 @@ def main():
         if not args.kernels_only:
             ap.error("--layer needs --kernels-only")
         WORKLOAD.update(PROFILE_LAYERS[args.layer])
+    if args.engine != "tensor_cores":
+        if not args.kernels_only:
+            ap.error("--engine needs --kernels-only")
+        import capi
+
+        capi.set_tensor_cores(False)
     if not args.kernels_only:
         args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
