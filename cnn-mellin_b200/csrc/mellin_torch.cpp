@@ -515,7 +515,7 @@ class MCorrLCorrMaskedFunction : public torch::autograd::Function<MCorrLCorrMask
     const Tensor &lens = saved[2], &y = saved[3];
     Tensor go;
     if (ctx->saved_data["relu"].toBool()) {
-      go = grads[0] * (y > 0);
+      go = at::threshold_backward(grads[0], y, 0);  // grad where y > 0, else 0: one pass
     } else {
       Tensor mask = at::arange(y.size(3), lens.options()).unsqueeze(0) < lens.unsqueeze(1);  // (N, positions)
       go = grads[0] * mask.unsqueeze(1).unsqueeze(1);

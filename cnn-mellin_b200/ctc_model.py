@@ -27,6 +27,42 @@ CHANNELS = (3, 128, 128, 128, 128, 128, 256, 256, 256, 256, 256)
 KERNEL = (6, 3)
 
 
+class _PackFrames(torch.autograd.Function):
+    """(N, K, T) padded features -> (K, sum of lengths): the frames inside each utterance, utterance by utterance."""
+
+    @staticmethod
+    def forward(ctx, x, lengths):
+        ctx.lengths, ctx.shape = lengths, x.shape
+        return torch.cat([x[i, :, :n] for i, n in enumerate(lengths)], dim=1)
+
+    @staticmethod
+    def backward(ctx, grad):
+        gx = grad.new_zeros(ctx.shape)
+        o = 0
+        for i, n in enumerate(ctx.lengths):
+            gx[i, :, :n] = grad[:, o:o + n]
+            o += n
+        return gx, None
+
+
+class _UnpackFrames(torch.autograd.Function):
+    """(C, sum of lengths) -> (T, N, C) padded with zeros: the layout the CTC loss reads."""
+
+    @staticmethod
+    def forward(ctx, packed, lengths, t):
+        ctx.lengths = lengths
+        out = packed.new_zeros((t, len(lengths), packed.shape[0]))
+        o = 0
+        for i, n in enumerate(lengths):
+            out[:n, i] = packed[:, o:o + n].t()
+            o += n
+        return out
+
+    @staticmethod
+    def backward(ctx, grad):
+        return torch.cat([grad[:n, i].t() for i, n in enumerate(ctx.lengths)], dim=1), None, None
+
+
 class MellinCTCNet(torch.nn.Module):
     def __init__(self, channels: Sequence[int] = CHANNELS, kernel: Tuple[int, int] = KERNEL, bins: int = BINS,
                  hidden: int = 1024, classes: int = CLASSES, dropout: float = 0.05):
@@ -51,12 +87,16 @@ class MellinCTCNet(torch.nn.Module):
             x = mconv.mcorrlcorr_masked(x, conv.weight, conv.bias, lens, True, conv.s, conv.d, conv.p, conv.r)
             x = F.dropout(x, self.dropout, self.training)
         n, c, b, t = x.shape
-        # per-frame features (c * bins) stay in the layers' (N, features, T) layout: W @ x[n] needs no transposition
-        h = x.reshape(n, c * b, t)
-        h = F.relu(torch.matmul(self.fc1.weight, h) + self.fc1.bias[:, None])
-        h = F.relu(torch.matmul(self.fc2.weight, h) + self.fc2.bias[:, None])
-        logits = torch.matmul(self.out.weight, h) + self.out.bias[:, None]  # (N, classes, T)
-        return F.log_softmax(logits, dim=1).permute(2, 0, 1)
+        # Only the frames inside the utterances go through the per-frame layers (the reference packs its frames the
+        # same way before its recurrent layers, models.py:407-411): features (c * bins, frames) gathered utterance by
+        # utterance, so that W @ h needs no transposition and the ~37 % of padding costs nothing.
+        lengths = [min(int(v), t) for v in lens.tolist()]
+        h = _PackFrames.apply(x.reshape(n, c * b, t), lengths)                        # (features, valid frames)
+        h = F.relu(torch.addmm(self.fc1.bias[:, None], self.fc1.weight, h))
+        h = F.relu(torch.addmm(self.fc2.bias[:, None], self.fc2.weight, h))
+        logits = torch.addmm(self.out.bias[:, None], self.out.weight, h)              # (classes, valid frames)
+        # back to the padded (T, N, classes) layout the loss expects; frames past an utterance's end are never read
+        return _UnpackFrames.apply(F.log_softmax(logits, dim=0), lengths, t)
 
 
 def synthetic_lengths(count: int, seed: int, lo: int = 200, hi: int = 800) -> List[int]:
