@@ -24,7 +24,8 @@ OP1D = ["mellin_mconv1d", "mellin_mcorr1d"]
 OP2D = ["mellin_mconvlconv", "mellin_mcorrlcorr"]
 COL1D = ["mellin_snd2col", "mellin_col2snd"]
 COL2D = ["mellin_spec2col", "mellin_col2spec"]
-LAYER = ["mellin_mcorrlcorr_forward", "mellin_mcorrlcorr_forward_masked", "mellin_mcorrlcorr_grad_input",
+LAYER = ["mellin_mcorrlcorr_forward", "mellin_mcorrlcorr_forward_masked", "mellin_mcorrlcorr_forward_fused",
+         "mellin_relu_dropout_backward", "mellin_mcorrlcorr_grad_input",
          "mellin_mcorrlcorr_grad_input_masked",
          "mellin_mcorrlcorr_grad_weight", "mellin_mcorrlcorr_grad_weight_masked"]
 MISC = ["mellin_abi_version", "mellin_last_error", "mellin_launch_count", "mellin_clear_tables",
@@ -235,6 +236,26 @@ def forward_masked(x, w, bias, lens, relu, y, s, d, p, u, workspace=None):
     _check(fn(_p(x), _p(w), _p(bias), _p(lens), _INT(1 if relu else 0), *geom, _p(y), _p(workspace),
               ctypes.c_size_t(nbytes), _stream()))
     return y
+
+
+def forward_fused(x, w, bias, lens, relu, dropout_p, seed, y, s, d, p, u, workspace=None):
+    """y = dropout(mask * act(bias + mcorrlcorr(x, w))) with the mask a function of (seed, position)."""
+    import torch
+
+    geom = _geometry(x.shape, w.shape, y.shape, s, d, p, u)
+    need = int(lib().mellin_mcorrlcorr_forward_workspace_bytes(*geom)) if y.dtype == torch.float32 else 0
+    workspace, nbytes = _scratch(need, y, workspace)
+    fn = getattr(lib(), "mellin_mcorrlcorr_forward_fused" + _sfx(y))
+    _check(fn(_p(x), _p(w), _p(bias), _p(lens), _INT(1 if relu else 0), ctypes.c_double(dropout_p),
+              ctypes.c_uint32(seed & 0xFFFFFFFF), *geom, _p(y), _p(workspace), ctypes.c_size_t(nbytes), _stream()))
+    return y
+
+
+def relu_dropout_backward(grad_y, y, scale, grad_pre):
+    """grad_pre = y > 0 ? grad_y * scale : 0 (one pass)."""
+    fn = getattr(lib(), "mellin_relu_dropout_backward" + _sfx(y))
+    _check(fn(_p(grad_y), _p(y), ctypes.c_double(scale), _p(grad_pre), _I64(y.numel()), _stream()))
+    return grad_pre
 
 
 def grad_input(w, grad_y, grad_x, s, d, p, u, workspace=None):

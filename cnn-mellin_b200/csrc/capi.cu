@@ -57,15 +57,39 @@ int check_geometry(const char *who, const Geometry2D &q, int64_t linear_divisor)
 // epilogue as a separate pass, for the paths that do not carry it themselves
 template <typename T>
 __global__ void mask_relu_kernel(T *__restrict__ out, const int *__restrict__ lens, int len_scale, int len_offset,
-                                 int relu, long long total, long long per_utterance, int noy) {
+                                 int relu, unsigned drop_threshold, unsigned drop_seed, float drop_scale,
+                                 long long total, long long per_utterance, int noy) {
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
     const int n = (int)(i / per_utterance), oy = (int)(i % noy);
     T v = out[i];
     if (relu && v < T(0)) v = T(0);
     if (lens != nullptr && oy >= lens[n] * len_scale + len_offset) v = T(0);
+    if (drop_threshold != 0u)
+      v = dropout_hash(drop_seed, (unsigned long long)i) < drop_threshold ? T(0) : v * T(drop_scale);
     out[i] = v;
   }
+}
+
+// grad_pre[i] = y[i] > 0 ? grad[i] * scale : 0: the backward of relu + mask + dropout in one pass, read off the
+// layer's own output (an element is positive exactly where it passed all three)
+template <typename T>
+__global__ void relu_dropout_backward_kernel(const T *__restrict__ grad, const T *__restrict__ y, T scale,
+                                             T *__restrict__ out, long long total) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x)
+    out[i] = y[i] > T(0) ? grad[i] * scale : T(0);
+}
+template <typename T>
+int launch_relu_dropout_backward(const T *grad, const T *y, double scale, T *out, int64_t total, void *stream) {
+  if (total <= 0) return MELLIN_OK;
+  if (grad == nullptr || y == nullptr || out == nullptr) return fail(MELLIN_ERR_BAD_ARGUMENT, "relu_dropout_backward: null pointer");
+  const int blocks = (int)std::min<long long>((total + 255) / 256, (long long)sm_count() * 32);
+  relu_dropout_backward_kernel<T><<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(grad, y, (T)scale, out, total);
+  const cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return fail(MELLIN_ERR_LAUNCH, std::string("relu_dropout_backward_kernel: ") + cudaGetErrorString(err));
+  count_launch();
+  return MELLIN_OK;
 }
 
 template <typename T>
@@ -73,8 +97,8 @@ int launch_mask_relu(const DirectProblem<T> &p, cudaStream_t stream) {
   const long long per_utterance = (long long)p.A * p.nox * p.noy, total = per_utterance * p.N;
   if (total == 0) return MELLIN_OK;
   const int blocks = (int)std::min<long long>((total + 255) / 256, (long long)sm_count() * 16);
-  mask_relu_kernel<T><<<blocks, 256, 0, stream>>>(p.out, p.lens, p.len_scale, p.len_offset, p.relu, total,
-                                                  per_utterance, p.noy);
+  mask_relu_kernel<T><<<blocks, 256, 0, stream>>>(p.out, p.lens, p.len_scale, p.len_offset, p.relu, p.drop_threshold,
+                                                  p.drop_seed, p.drop_scale, total, per_utterance, p.noy);
   const cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return fail(MELLIN_ERR_LAUNCH, std::string("mask_relu_kernel: ") + cudaGetErrorString(err));
   count_launch();
@@ -83,8 +107,8 @@ int launch_mask_relu(const DirectProblem<T> &p, cudaStream_t stream) {
 
 // tensor cores when enabled, covered and given scratch; CUDA cores otherwise
 int dispatch_direct(const DirectProblem<float> &p, void *workspace, size_t workspace_bytes, cudaStream_t stream) {
-  if (p.lens != nullptr || p.relu) {
-    // fused length mask / ReLU: the tensor-core kernel that carries it, else the plain operator and one more pass
+  if (p.lens != nullptr || p.relu || p.drop_threshold) {
+    // fused length mask / ReLU / dropout: the tensor-core kernel that carries it, else the plain operator and one more pass
     if (p.lens != nullptr && !p.accumulate && tensor_cores_enabled() && workspace != nullptr && p.A > 4) {
       const size_t need = direct_tc_workspace_bytes_masked(p);
       if (need > 0 && workspace_bytes >= need) {
@@ -92,8 +116,13 @@ int dispatch_direct(const DirectProblem<float> &p, void *workspace, size_t works
         if (rc != MELLIN_ERR_UNSUPPORTED) return rc;
       }
     }
+    if (p.B <= 4 && p.A >= 8 && !p.accumulate) {
+      // first layers without the tensor cores: the row kernel carries the epilogue too
+      const int rc = launch_few_in_rows(p, stream);
+      if (rc != MELLIN_ERR_UNSUPPORTED) return rc;
+    }
     DirectProblem<float> plain = p;
-    plain.lens = nullptr, plain.relu = 0;
+    plain.lens = nullptr, plain.relu = 0, plain.drop_threshold = 0;
     const int rc = dispatch_direct(plain, workspace, workspace_bytes, stream);
     return rc ? rc : launch_mask_relu(p, stream);
   }
@@ -174,8 +203,10 @@ int dispatch_accumulating(const DirectProblem<float> &p, cudaStream_t stream) {
 int dispatch_accumulating(const DirectProblem<double> &, cudaStream_t) { return MELLIN_ERR_UNSUPPORTED; }
 
 int dispatch_direct(const DirectProblem<double> &p, void *, size_t, cudaStream_t stream) {
-  const int rc = launch_direct<double>(p, stream);
-  return (rc || (p.lens == nullptr && !p.relu)) ? rc : launch_mask_relu(p, stream);
+  DirectProblem<double> plain = p;
+  plain.drop_threshold = 0;
+  const int rc = launch_direct<double>(plain, stream);
+  return (rc || (p.lens == nullptr && !p.relu && !p.drop_threshold)) ? rc : launch_mask_relu(p, stream);
 }
 
 // ---- polyphase forms of linear stride / dilation 2 -------------------------------------
@@ -293,7 +324,9 @@ PolyBuffers polyphase_buffers(const Geometry2D &q, const Polyphase &P, int op /*
 template <typename T>
 int op2d(const char *who, Relation rel, const T *f, const T *g, const Geometry2D &q, int tf, int tg, int th,
          T *h, const T *bias, bool accumulate, void *workspace, size_t workspace_bytes, void *stream,
-         const int *lens = nullptr, int relu = 0) {
+         const int *lens = nullptr, int relu = 0, double dropout_p = 0.0, unsigned dropout_seed = 0) {
+  if (!(dropout_p >= 0.0 && dropout_p < 1.0))
+    return fail(MELLIN_ERR_BAD_ARGUMENT, std::string(who) + ": dropout probability must be in [0, 1)");
   int rc = check_geometry(who, q, q.uy);
   if (rc) return rc;
   const int64_t out_elems = q.batch * q.c_out * q.nhx * q.nhy;
@@ -366,6 +399,11 @@ int op2d(const char *who, Relation rel, const T *f, const T *g, const Geometry2D
   p.Dy = (int)q.uy;
   p.accumulate = accumulate;
   p.lens = lens, p.relu = relu;
+  if (dropout_p > 0.0) {
+    p.drop_threshold = (unsigned)std::min<double>(dropout_p * 4294967296.0, 4294967295.0);
+    p.drop_seed = dropout_seed;
+    p.drop_scale = (float)(1.0 / (1.0 - dropout_p));
+  }
   if (accumulate && workspace == nullptr) {
     rc = dispatch_accumulating(p, static_cast<cudaStream_t>(stream));
     if (rc != MELLIN_ERR_UNSUPPORTED) return rc;
@@ -610,6 +648,18 @@ int64_t mellin_lcorr_support_size(int64_t ng, int64_t s, int64_t p, int64_t u) {
                                              size_t workspace_bytes, void *stream) {                  \
     return op2d<T>("mcorrlcorr_forward_masked", Relation::Corr, w, x, GEOM_FROM_LAYER, 0, 0, 0, y,    \
                    bias, false, workspace, workspace_bytes, stream, lens, relu ? 1 : 0);              \
+  }                                                                                                   \
+  int mellin_mcorrlcorr_forward_fused_##sfx(const T *x, const T *w, const T *bias, const int *lens,    \
+                                            int relu, double dropout_p, uint32_t dropout_seed,        \
+                                            MELLIN_LAYER_GEOMETRY, T *y, void *workspace,             \
+                                            size_t workspace_bytes, void *stream) {                   \
+    return op2d<T>("mcorrlcorr_forward_fused", Relation::Corr, w, x, GEOM_FROM_LAYER, 0, 0, 0, y,     \
+                   bias, false, workspace, workspace_bytes, stream, lens, relu ? 1 : 0, dropout_p,    \
+                   dropout_seed);                                                                     \
+  }                                                                                                   \
+  int mellin_relu_dropout_backward_##sfx(const T *grad_y, const T *y, double scale, T *grad_pre,      \
+                                         int64_t count, void *stream) {                               \
+    return launch_relu_dropout_backward<T>(grad_y, y, scale, grad_pre, count, stream);                \
   }                                                                                                   \
   int mellin_mcorrlcorr_grad_input_##sfx(const T *w, const T *grad_y, MELLIN_LAYER_GEOMETRY,          \
                                          T *grad_x, void *workspace, size_t workspace_bytes,          \

@@ -210,6 +210,11 @@ few_in_rows_kernel(const DirectProblem<float> p, const FewInPlan t) {
           v[j] = val;
         }
         float *out = p.out + c.n * p.out_sn + a * p.out_sa + (long long)c.ox * p.noy + y;
+        if (p.drop_threshold != 0u) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            v[j] = dropout_hash(p.drop_seed, (unsigned long long)(out + j - p.out)) < p.drop_threshold ? 0.f : v[j] * p.drop_scale;
+        }
         if (p.accumulate) {
           const float4 old = *reinterpret_cast<const float4 *>(out);
           v[0] += old.x, v[1] += old.y, v[2] += old.z, v[3] += old.w;

@@ -62,7 +62,23 @@ struct DirectProblem {
   const int *lens = nullptr;  // device array of N lengths along the linear axis, or null
   int len_scale = 1, len_offset = 0;  // the bound used is lens[n] * len_scale + len_offset
   int relu = 0;
+  // fused dropout (training): an output element is zeroed when dropout_hash(seed, its offset in `out`) falls below
+  // drop_threshold (= p * 2^32; 0 switches dropout off) and scaled by drop_scale = 1 / (1 - p) otherwise
+  unsigned drop_threshold = 0, drop_seed = 0;
+  float drop_scale = 1.f;
 };
+
+// Stateless per-element random number of the fused dropout: a 32-bit avalanche hash of (seed, element offset).
+// Every kernel that can write a layer's output uses this one function, so the mask does not depend on the kernel.
+__host__ __device__ __forceinline__ unsigned dropout_hash(unsigned seed, unsigned long long offset) {
+  unsigned h = (unsigned)offset * 0x9E3779B1u ^ seed ^ ((unsigned)(offset >> 32) * 0x85EBCA77u);
+  h ^= h >> 16;
+  h *= 0x85EBCA6Bu;
+  h ^= h >> 13;
+  h *= 0xC2B2AE35u;
+  h ^= h >> 16;
+  return h;
+}
 
 // Weight gradient of a correlation layer:
 //   gw[a, b, kx, ky] = sum_n sum_{(ox, ix) in row kx} sum_oy

@@ -141,12 +141,14 @@ struct LayerGeometry {
 enum class Op { Corr, Conv };
 
 Tensor conv_like(const char *c, Op op, int64_t dim, const Tensor &input, const Tensor &weight, const OptTensor &bias,
-                 Pair s, Pair d, Pair p, Pair u, Pair r, const Tensor *lens = nullptr, bool relu = false) {
+                 Pair s, Pair d, Pair p, Pair u, Pair r, const Tensor *lens = nullptr, bool relu = false,
+                 double dropout_p = 0.0, int64_t seed = 0) {
   c10::cuda::CUDAGuard guard(weight.device());
   if (weight.scalar_type() == at::kHalf && input.scalar_type() == at::kHalf &&
       (!bias || bias->scalar_type() == at::kHalf)) {
     const OptTensor wide_bias = bias ? OptTensor(bias->to(at::kFloat)) : OptTensor();
-    return conv_like(c, op, dim, input.to(at::kFloat), weight.to(at::kFloat), wide_bias, s, d, p, u, r, lens, relu)
+    return conv_like(c, op, dim, input.to(at::kFloat), weight.to(at::kFloat), wide_bias, s, d, p, u, r, lens, relu,
+                     dropout_p, seed)
         .to(at::kHalf);
   }
   ConvArgs a = check_conv(c, dim, input, weight, bias);
@@ -177,13 +179,15 @@ Tensor conv_like(const char *c, Op op, int64_t dim, const Tensor &input, const T
                   c, ": 'lens' must be a contiguous int32 CUDA tensor with one length per utterance");
       const size_t bytes = f64 ? 0 : mellin_mcorrlcorr_forward_workspace_bytes(LAYER_ARGS(q));
       Tensor ws = at::empty({static_cast<int64_t>(bytes ? bytes : 16)}, weight.options().dtype(at::kByte));
-      rc = f64 ? mellin_mcorrlcorr_forward_masked_f64(a.g.dense.data_ptr<double>(), a.f.dense.data_ptr<double>(),
-                                                      bias ? b.data_ptr<double>() : nullptr, lens->data_ptr<int>(),
-                                                      relu, LAYER_ARGS(q), out.data_ptr<double>(), nullptr, 0, stream)
-               : mellin_mcorrlcorr_forward_masked_f32(a.g.dense.data_ptr<float>(), a.f.dense.data_ptr<float>(),
-                                                      bias ? b.data_ptr<float>() : nullptr, lens->data_ptr<int>(),
-                                                      relu, LAYER_ARGS(q), out.data_ptr<float>(), ws.data_ptr(), bytes,
-                                                      stream);
+      const uint32_t seed32 = static_cast<uint32_t>(static_cast<uint64_t>(seed) ^ (static_cast<uint64_t>(seed) >> 32));
+      rc = f64 ? mellin_mcorrlcorr_forward_fused_f64(a.g.dense.data_ptr<double>(), a.f.dense.data_ptr<double>(),
+                                                     bias ? b.data_ptr<double>() : nullptr, lens->data_ptr<int>(),
+                                                     relu, dropout_p, seed32, LAYER_ARGS(q), out.data_ptr<double>(),
+                                                     nullptr, 0, stream)
+               : mellin_mcorrlcorr_forward_fused_f32(a.g.dense.data_ptr<float>(), a.f.dense.data_ptr<float>(),
+                                                     bias ? b.data_ptr<float>() : nullptr, lens->data_ptr<int>(),
+                                                     relu, dropout_p, seed32, LAYER_ARGS(q), out.data_ptr<float>(),
+                                                     ws.data_ptr(), bytes, stream);
     } else if (f64) {
       rc = mellin_mcorrlcorr_forward_f64(a.g.dense.data_ptr<double>(), a.f.dense.data_ptr<double>(),
                                          bias ? b.data_ptr<double>() : nullptr, LAYER_ARGS(q), out.data_ptr<double>(),
@@ -231,10 +235,13 @@ Tensor mcorrlcorr_cuda(const Tensor &input, const Tensor &weight, const OptTenso
 }
 Tensor mcorrlcorr_masked_cuda(const Tensor &input, const Tensor &weight, const OptTensor &bias, const Tensor &lens,
                              bool relu, at::IntArrayRef s, at::IntArrayRef d, at::IntArrayRef p, at::IntArrayRef u,
-                             at::IntArrayRef r) {
+                             at::IntArrayRef r, double dropout_p, int64_t seed) {
   const char *c = "mcorrlcorr_masked_cuda";
+  TORCH_CHECK(dropout_p >= 0.0 && dropout_p < 1.0, c, ": dropout_p must be in [0, 1)");
+  TORCH_CHECK(dropout_p == 0.0 || relu, c, ": the fused dropout needs relu=True (its backward reads the mask off the output)");
   return conv_like(c, Op::Corr, 4, input.contiguous(), weight.contiguous(), bias, pair_of(s, c, "s"),
-                   pair_of(d, c, "d"), pair_of(p, c, "p"), pair_of(u, c, "u"), pair_of(r, c, "r"), &lens, relu);
+                   pair_of(d, c, "d"), pair_of(p, c, "p"), pair_of(u, c, "u"), pair_of(r, c, "r"), &lens, relu,
+                   dropout_p, seed);
 }
 
 Tensor mconvlconv_cuda(const Tensor &input, const Tensor &weight, const OptTensor &bias, at::IntArrayRef s,
@@ -482,11 +489,11 @@ class MCorrLCorrFunction : public torch::autograd::Function<MCorrLCorrFunction> 
 
 Tensor call_mcorrlcorr_masked(const Tensor &i, const Tensor &w, const OptTensor &b, const Tensor &lens, bool relu,
                               at::IntArrayRef s, at::IntArrayRef d, at::IntArrayRef p, at::IntArrayRef u,
-                              at::IntArrayRef r) {
+                              at::IntArrayRef r, double dropout_p, int64_t seed) {
   return typed_op<Tensor(const Tensor &, const Tensor &, const OptTensor &, const Tensor &, bool, at::IntArrayRef,
-                         at::IntArrayRef, at::IntArrayRef, at::IntArrayRef, at::IntArrayRef)>(
+                         at::IntArrayRef, at::IntArrayRef, at::IntArrayRef, at::IntArrayRef, double, int64_t)>(
              "mellin::mcorrlcorr_masked")
-      .call(i, w, b, lens, relu, s, d, p, u, r);
+      .call(i, w, b, lens, relu, s, d, p, u, r, dropout_p, seed);
 }
 
 // y = mask * act(layer(x)): dy/dz = mask * act'(z); for ReLU both factors are (y > 0)
@@ -494,15 +501,16 @@ class MCorrLCorrMaskedFunction : public torch::autograd::Function<MCorrLCorrMask
  public:
   static Tensor forward(torch::autograd::AutogradContext *ctx, const Tensor &input, const Tensor &weight,
                         const OptTensor &bias, const Tensor &lens, bool relu, at::IntArrayRef s, at::IntArrayRef d,
-                        at::IntArrayRef p, at::IntArrayRef u, at::IntArrayRef r) {
+                        at::IntArrayRef p, at::IntArrayRef u, at::IntArrayRef r, double dropout_p, int64_t seed) {
     ctx->saved_data["has_bias"] = bias.has_value();
     ctx->saved_data["relu"] = relu;
+    ctx->saved_data["dropout_p"] = dropout_p;
     ctx->saved_data["s"] = s.vec(), ctx->saved_data["d"] = d.vec();
     ctx->saved_data["p"] = p.vec(), ctx->saved_data["u"] = u.vec();
     Tensor y;
     {
       at::AutoDispatchBelowADInplaceOrView guard;
-      y = call_mcorrlcorr_masked(input, weight, bias, lens, relu, s, d, p, u, r);
+      y = call_mcorrlcorr_masked(input, weight, bias, lens, relu, s, d, p, u, r, dropout_p, seed);
     }
     ctx->save_for_backward({input, weight, lens, y});
     return y;
@@ -514,8 +522,21 @@ class MCorrLCorrMaskedFunction : public torch::autograd::Function<MCorrLCorrMask
     const bool has_bias = ctx->saved_data["has_bias"].toBool();
     const Tensor &lens = saved[2], &y = saved[3];
     Tensor go;
-    if (ctx->saved_data["relu"].toBool()) {
+    const double dropout_p = ctx->saved_data["dropout_p"].toDouble();
+    if (ctx->saved_data["relu"].toBool() && dropout_p > 0.0 && y.scalar_type() != at::kHalf) {
+      // relu, mask and dropout in one pass over y: an element is positive exactly where it passed all three
+      Tensor g = grads[0].contiguous();
+      go = at::empty_like(y);
+      c10::cuda::CUDAGuard guard(y.device());
+      const int rc = y.scalar_type() == at::kDouble
+                         ? mellin_relu_dropout_backward_f64(g.data_ptr<double>(), y.data_ptr<double>(), 1.0 / (1.0 - dropout_p),
+                                                            go.data_ptr<double>(), y.numel(), current_stream(y))
+                         : mellin_relu_dropout_backward_f32(g.data_ptr<float>(), y.data_ptr<float>(), 1.0 / (1.0 - dropout_p),
+                                                            go.data_ptr<float>(), y.numel(), current_stream(y));
+      check_status(rc, c);
+    } else if (ctx->saved_data["relu"].toBool()) {
       go = at::threshold_backward(grads[0], y, 0);  // grad where y > 0, else 0: one pass
+      if (dropout_p > 0.0) go.mul_(1.0 / (1.0 - dropout_p));
     } else {
       Tensor mask = at::arange(y.size(3), lens.options()).unsqueeze(0) < lens.unsqueeze(1);  // (N, positions)
       go = grads[0] * mask.unsqueeze(1).unsqueeze(1);
@@ -525,7 +546,7 @@ class MCorrLCorrMaskedFunction : public torch::autograd::Function<MCorrLCorrMask
                               pair_of(ctx->saved_data["p"].toIntVector(), c, "p"),
                               pair_of(ctx->saved_data["u"].toIntVector(), c, "u"), ctx->needs_input_grad(0),
                               ctx->needs_input_grad(1), has_bias && ctx->needs_input_grad(2), &lens);
-    return {out[0], out[1], out[2], Tensor(), Tensor(), Tensor(), Tensor(), Tensor(), Tensor(), Tensor()};
+    return {out[0], out[1], out[2], Tensor(), Tensor(), Tensor(), Tensor(), Tensor(), Tensor(), Tensor(), Tensor(), Tensor()};
   }
 };
 
@@ -575,8 +596,8 @@ Tensor mcorrlcorr_autograd(const Tensor &input, const Tensor &weight, const OptT
 }
 Tensor mcorrlcorr_masked_autograd(const Tensor &input, const Tensor &weight, const OptTensor &bias, const Tensor &lens,
                                  bool relu, at::IntArrayRef s, at::IntArrayRef d, at::IntArrayRef p, at::IntArrayRef u,
-                                 at::IntArrayRef r) {
-  return MCorrLCorrMaskedFunction::apply(input, weight, bias, lens, relu, s, d, p, u, r);
+                                 at::IntArrayRef r, double dropout_p, int64_t seed) {
+  return MCorrLCorrMaskedFunction::apply(input, weight, bias, lens, relu, s, d, p, u, r, dropout_p, seed);
 }
 Tensor snd2col_autograd(const Tensor &input, int64_t kernel_width, int64_t s, int64_t d, int64_t p, int64_t u,
                         int64_t r) {
@@ -602,7 +623,7 @@ TORCH_LIBRARY(mellin, m) {
   m.def("spec2col(Tensor input, int[2] kernel_size, int[2] s=1, int[2] d=1, int[2] p=0, int[2] u=1, int[2] r=0) -> Tensor");
   m.def("col2spec(Tensor input, int[2] spec_size, int[2] s=1, int[2] d=1, int[2] p=0, int[2] u=1) -> Tensor");
   // not in the reference: mcorrlcorr with the length mask and ReLU its models apply around a layer fused in
-  m.def("mcorrlcorr_masked(Tensor input, Tensor weight, Tensor? bias, Tensor lens, bool relu=True, int[2] s=1, int[2] d=1, int[2] p=0, int[2] u=1, int[2] r=0) -> Tensor");
+  m.def("mcorrlcorr_masked(Tensor input, Tensor weight, Tensor? bias, Tensor lens, bool relu=True, int[2] s=1, int[2] d=1, int[2] p=0, int[2] u=1, int[2] r=0, float dropout_p=0.0, int seed=0) -> Tensor");
 }
 
 TORCH_LIBRARY_IMPL(mellin, CUDA, m) {

@@ -100,6 +100,8 @@ struct TcParams {
   const int *lens;  // per utterance: outputs at positions >= lens[n] * len_scale + len_offset are zero
   int len_scale, len_offset;
   int relu;
+  unsigned drop_threshold, drop_seed;  // fused dropout (masked build): see DirectProblem
+  float drop_scale;
 #endif
   int table_in_smem;  // 1: row offsets, entries and row order are cached in shared memory
   int wide_box;  // 1: one TMA box brings all KB rows of a stage (they belong to one table entry)
@@ -305,7 +307,11 @@ struct TileWalker {
 #define EPILOGUE_LEN                                          \
   const float keep = oy < lens_s[tc_.n] ? 1.f : 0.f;          \
   const float floor_ = p.relu ? 0.f : -3.0e38f;
-#define STORE_VALUE(v) (fmaxf((v), floor_) * keep)
+#define STORE_VALUE(v)                                                                                           \
+  (fmaxf((v), floor_) * keep *                                                                                   \
+   ((p.drop_threshold != 0u && dropout_hash(p.drop_seed, (unsigned long long)(o - p.out)) < p.drop_threshold)    \
+        ? 0.f                                                                                                    \
+        : p.drop_scale))
 #else
 #define TILE_ROWS(rows) (rows)
 #define EPILOGUE_LEN
@@ -748,6 +754,7 @@ bool plan_tc_direct(const DirectProblem<float> &p, TcPlan &plan) {
 #ifdef MELLIN_MASKED
   if (p.lens == nullptr || p.N > kMaxLens) return false;
   q.lens = p.lens, q.relu = p.relu, q.len_scale = p.len_scale, q.len_offset = p.len_offset;
+  q.drop_threshold = p.drop_threshold, q.drop_seed = p.drop_seed, q.drop_scale = p.drop_threshold ? p.drop_scale : 1.f;
 #endif
   q.bias = p.accumulate ? nullptr : p.bias, q.out = p.out;
   q.table_in_smem = (p.nox <= kMaxTableRows && p.table.num_entries <= kMaxTableEntries) ? 1 : 0;

@@ -65,7 +65,7 @@ class _UnpackFrames(torch.autograd.Function):
 
 class MellinCTCNet(torch.nn.Module):
     def __init__(self, channels: Sequence[int] = CHANNELS, kernel: Tuple[int, int] = KERNEL, bins: int = BINS,
-                 hidden: int = 1024, classes: int = CLASSES, dropout: float = 0.05):
+                 hidden: int = 1024, classes: int = CLASSES, dropout: float = 0.05, fused_dropout: bool = True):
         super().__init__()
         valid = mconv.mcorr_valid_size(kernel[0], bins)
         same = (bins - valid, 1)  # same-size output on both axes (time padding 1)
@@ -76,6 +76,7 @@ class MellinCTCNet(torch.nn.Module):
             torch.nn.init.kaiming_normal_(conv.weight)
             torch.nn.init.zeros_(conv.bias)
         self.dropout = dropout
+        self.fused_dropout = fused_dropout  # False: torch's dropout as a separate pass (for comparison)
         self.fc1 = torch.nn.Linear(channels[-1] * bins, hidden)
         self.fc2 = torch.nn.Linear(hidden, hidden)
         self.out = torch.nn.Linear(hidden, classes)
@@ -83,9 +84,13 @@ class MellinCTCNet(torch.nn.Module):
     def forward(self, x: torch.Tensor, lens: torch.Tensor) -> torch.Tensor:
         """x: (N, 3, bins, T) zero beyond lens[n] frames; lens: int32 (N,).  Returns (T, N, classes) log-probabilities."""
         for conv in self.convs:
-            # relu(conv(x)) * mask fused in the layer's kernel; dropout as the reference applies it
-            x = mconv.mcorrlcorr_masked(x, conv.weight, conv.bias, lens, True, conv.s, conv.d, conv.p, conv.r)
-            x = F.dropout(x, self.dropout, self.training)
+            # dropout(relu(conv(x)) * mask): the reference's conv -> nonlinearity -> dropout block in one kernel
+            if self.fused_dropout:
+                x = mconv.mcorrlcorr_masked(x, conv.weight, conv.bias, lens, True, conv.s, conv.d, conv.p, conv.r,
+                                            dropout_p=self.dropout, training=self.training)
+            else:
+                x = mconv.mcorrlcorr_masked(x, conv.weight, conv.bias, lens, True, conv.s, conv.d, conv.p, conv.r)
+                x = F.dropout(x, self.dropout, self.training)
         n, c, b, t = x.shape
         # Only the frames inside the utterances go through the per-frame layers (the reference packs its frames the
         # same way before its recurrent layers, models.py:407-411): features (c * bins, frames) gathered utterance by

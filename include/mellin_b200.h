@@ -168,6 +168,26 @@ int mellin_mcorrlcorr_forward_masked_f64(const double *x, const double *w, const
                                          int relu, MELLIN_LAYER_GEOMETRY, double *y, void *workspace,
                                          size_t workspace_bytes, void *stream);
 
+/* The same with the models' dropout fused in as well (models.py:424-434 apply conv -> nonlinearity -> dropout):
+ * y = dropout(mask * act(bias + mcorrlcorr(x, w))) for a training step.  An element is dropped when a hash of
+ * (dropout_seed, its offset in y) falls below dropout_p * 2^32 and is scaled by 1 / (1 - dropout_p) otherwise;
+ * every kernel that can write y uses the same hash, so the mask depends on the seed only.  dropout_p = 0 is
+ * mellin_mcorrlcorr_forward_masked_*; lens may be NULL.  No reference counterpart (three operators there). */
+int mellin_mcorrlcorr_forward_fused_f32(const float *x, const float *w, const float *bias, const int *lens, int relu,
+                                        double dropout_p, uint32_t dropout_seed, MELLIN_LAYER_GEOMETRY, float *y,
+                                        void *workspace, size_t workspace_bytes, void *stream);
+int mellin_mcorrlcorr_forward_fused_f64(const double *x, const double *w, const double *bias, const int *lens,
+                                        int relu, double dropout_p, uint32_t dropout_seed, MELLIN_LAYER_GEOMETRY,
+                                        double *y, void *workspace, size_t workspace_bytes, void *stream);
+
+/* Backward of that epilogue in one pass over the layer's OUTPUT: grad_pre[i] = y[i] > 0 ? grad_y[i] * scale : 0
+ * (with ReLU an element of y is positive exactly where it passed the activation, the mask and the dropout);
+ * scale = 1 / (1 - dropout_p).  grad_pre is what the masked grad-input / grad-weight entry points take. */
+int mellin_relu_dropout_backward_f32(const float *grad_y, const float *y, double scale, float *grad_pre, int64_t count,
+                                     void *stream);
+int mellin_relu_dropout_backward_f64(const double *grad_y, const double *y, double scale, double *grad_pre,
+                                     int64_t count, void *stream);
+
 /* grad_input for a grad_y that is zero from position lens[n] on (the gradient of
  * a masked layer): the same result as mellin_mcorrlcorr_grad_input_*, but the
  * tensor-core path does not compute the tiles that can only hold zeros. */
