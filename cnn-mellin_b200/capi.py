@@ -32,7 +32,10 @@ MISC = ["mellin_abi_version", "mellin_last_error", "mellin_launch_count", "melli
         "mellin_set_tensor_cores", "mellin_device_status", "mellin_mcorrlcorr_forward_workspace_bytes",
         "mellin_mcorrlcorr_grad_input_workspace_bytes", "mellin_mcorrlcorr_grad_weight_noalloc_f32",
         "mellin_mcorrlcorr_grad_weight_workspace_bytes", "mellin_index_map_build",
-        "mellin_selftest_unarmed_wait", "mellin_selftest_fma_rate"]
+        "mellin_selftest_unarmed_wait", "mellin_selftest_fma_rate",
+        "mellin_mcorrlcorr_forward_f16", "mellin_mcorrlcorr_grad_input_f16", "mellin_mcorrlcorr_grad_weight_f16",
+        "mellin_mcorrlcorr_forward_workspace_bytes_f16", "mellin_mcorrlcorr_grad_input_workspace_bytes_f16",
+        "mellin_mcorrlcorr_grad_weight_workspace_bytes_f16"]
 
 
 def exported_symbols():
@@ -66,8 +69,9 @@ def lib():
         _lib.mellin_last_error.restype = ctypes.c_char_p
         _lib.mellin_launch_count.restype = _I64
         for name in ("grad_weight", "forward", "grad_input"):
-            fn = getattr(_lib, "mellin_mcorrlcorr_%s_workspace_bytes" % name)
-            fn.restype, fn.argtypes = ctypes.c_size_t, [_I64] * 17
+            for sfx in ("", "_f16"):
+                fn = getattr(_lib, "mellin_mcorrlcorr_%s_workspace_bytes%s" % (name, sfx))
+                fn.restype, fn.argtypes = ctypes.c_size_t, [_I64] * 17
     return _lib
 
 
@@ -279,6 +283,36 @@ def grad_input_masked(w, grad_y, lens, grad_x, s, d, p, u, workspace=None):
     fn = getattr(lib(), "mellin_mcorrlcorr_grad_input_masked" + _sfx(grad_x))
     _check(fn(_p(w), _p(grad_y), _p(lens), *geom, _p(grad_x), _p(workspace), ctypes.c_size_t(nbytes), _stream()))
     return grad_x
+
+
+def _half_workspace(name, geom, like):
+    import torch
+
+    need = int(getattr(lib(), "mellin_mcorrlcorr_%s_workspace_bytes_f16" % name)(*geom))
+    return torch.empty(need + 256, dtype=torch.uint8, device=like.device), need
+
+
+def forward_f16(x, w, bias, y, s, d, p, u):
+    """float16 tensors in and out, float32 accumulation; the tensor cores run one MMA per product."""
+    geom = _geometry(x.shape, w.shape, y.shape, s, d, p, u)
+    ws, need = _half_workspace("forward", geom, y)
+    _check(lib().mellin_mcorrlcorr_forward_f16(_p(x), _p(w), _p(bias), *geom, _p(y), _p(ws), ctypes.c_size_t(need), _stream()))
+    return y
+
+
+def grad_input_f16(w, grad_y, grad_x, s, d, p, u):
+    geom = _geometry(grad_x.shape, w.shape, grad_y.shape, s, d, p, u)
+    ws, need = _half_workspace("grad_input", geom, grad_x)
+    _check(lib().mellin_mcorrlcorr_grad_input_f16(_p(w), _p(grad_y), *geom, _p(grad_x), _p(ws), ctypes.c_size_t(need), _stream()))
+    return grad_x
+
+
+def grad_weight_f16(x, grad_y, grad_w, grad_b, s, d, p, u):
+    geom = _geometry(x.shape, grad_w.shape, grad_y.shape, s, d, p, u)
+    ws, need = _half_workspace("grad_weight", geom, x)
+    _check(lib().mellin_mcorrlcorr_grad_weight_f16(_p(x), _p(grad_y), *geom, _p(grad_w), _p(grad_b), _p(ws),
+                                                   ctypes.c_size_t(need), _stream()))
+    return grad_w, grad_b
 
 
 def grad_weight_noalloc(x, grad_y, grad_w, grad_b, s, d, p, u):

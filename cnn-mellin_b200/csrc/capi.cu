@@ -8,6 +8,8 @@
 #include <type_traits>
 
 #include "../../include/mellin_b200.h"
+#include <cuda_fp16.h>
+
 #include "mellin_internal.h"
 #include "tuning_hooks.h"
 
@@ -324,7 +326,7 @@ PolyBuffers polyphase_buffers(const Geometry2D &q, const Polyphase &P, int op /*
 template <typename T>
 int op2d(const char *who, Relation rel, const T *f, const T *g, const Geometry2D &q, int tf, int tg, int th,
          T *h, const T *bias, bool accumulate, void *workspace, size_t workspace_bytes, void *stream,
-         const int *lens = nullptr, int relu = 0, double dropout_p = 0.0, unsigned dropout_seed = 0) {
+         const int *lens = nullptr, int relu = 0, double dropout_p = 0.0, unsigned dropout_seed = 0, int exact = 0) {
   if (!(dropout_p >= 0.0 && dropout_p < 1.0))
     return fail(MELLIN_ERR_BAD_ARGUMENT, std::string(who) + ": dropout probability must be in [0, 1)");
   int rc = check_geometry(who, q, q.uy);
@@ -399,6 +401,7 @@ int op2d(const char *who, Relation rel, const T *f, const T *g, const Geometry2D
   p.Dy = (int)q.uy;
   p.accumulate = accumulate;
   p.lens = lens, p.relu = relu;
+  p.exact_tf32 = exact;
   if (dropout_p > 0.0) {
     p.drop_threshold = (unsigned)std::min<double>(dropout_p * 4294967296.0, 4294967295.0);
     p.drop_seed = dropout_seed;
@@ -413,7 +416,7 @@ int op2d(const char *who, Relation rel, const T *f, const T *g, const Geometry2D
 
 template <typename T>
 int grad_input(const char *who, const T *w, const T *go, const Geometry2D &q, T *gx, void *workspace,
-               size_t workspace_bytes, void *stream, const int *lens = nullptr) {
+               size_t workspace_bytes, void *stream, const int *lens = nullptr, int exact = 0) {
   int rc = check_geometry(who, q, q.sy);
   if (rc) return rc;
   if (q.batch * q.c_in * q.ngx * q.ngy == 0) return MELLIN_OK;
@@ -466,6 +469,7 @@ int grad_input(const char *who, const T *w, const T *go, const Geometry2D &q, T 
   // s hy + d fy - p = u gy   =>   hy = (u gy - d fy + p) / s
   p.Ay = (int)q.uy, p.By = -(int)q.dy, p.Cy = (int)q.py, p.Dy = (int)q.sy;
   p.accumulate = false;
+  p.exact_tf32 = exact;
   if (lens != nullptr && q.uy == 1 && p.A > 4) {
     // grad_y is zero from position lens[n] on, so grad_x is zero from this position on: the last
     // input position any output below lens[n] reads is s (len - 1) - p + d (nfy - 1)
@@ -495,7 +499,7 @@ int make_gradw_problem(const char *who, const Geometry2D &q, GradWProblem<T> *p,
 
 template <typename T>
 int grad_weight(const char *who, const T *x, const T *go, const Geometry2D &q, T *gw, T *gb, void *workspace,
-                size_t workspace_bytes, void *stream, const int *lens = nullptr) {
+                size_t workspace_bytes, void *stream, const int *lens = nullptr, int exact = 0) {
   GradWProblem<T> p;
   int rc = make_gradw_problem(who, q, &p, true);
   if (rc) return rc;
@@ -536,6 +540,7 @@ int grad_weight(const char *who, const T *x, const T *go, const Geometry2D &q, T
     }
   }
   p.in = x, p.go = go, p.gw = gw, p.gb = gb;
+  p.exact_tf32 = exact;
   p.lens = q.nhy > 1 ? lens : nullptr;
   if (gw_elems == 0 && (gb == nullptr || q.c_out == 0)) return MELLIN_OK;
   return launch_gradw<T>(p, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
@@ -562,6 +567,52 @@ int col_op(const char *who, bool gather, const T *src, T *dst, int64_t c_in, int
   p.transposed_g = tg != 0, p.transposed_gg = tgg != 0;
   return gather ? launch_spec2col<T>(p, static_cast<cudaStream_t>(stream))
                 : launch_col2spec<T>(p, static_cast<cudaStream_t>(stream));
+}
+
+// ---- float16 entry points -------------------------------------------------------------
+// The reference's kernels take Half tensors and accumulate them in float32 (mconv_cuda.cuh:135-139).
+// Here float16 operands are widened into scratch, the float32 kernels run on them, and the result
+// is rounded back.  Every float16 value is exact in TF32, so the tensor-core kernels skip the two
+// compensation products of their hi/lo split: one MMA per product instead of three.
+__global__ void widen_kernel(const __half *__restrict__ src, float *__restrict__ dst, long long n) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    dst[i] = __half2float(src[i]);
+}
+__global__ void narrow_kernel(const float *__restrict__ src, __half *__restrict__ dst, long long n) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    dst[i] = __float2half_rn(src[i]);
+}
+int convert_launch(bool widen, const void *src, void *dst, long long n, cudaStream_t stream) {
+  if (n <= 0 || src == nullptr) return MELLIN_OK;
+  const int blocks = (int)std::min<long long>((n + 255) / 256, (long long)sm_count() * 32);
+  if (widen) widen_kernel<<<blocks, 256, 0, stream>>>(static_cast<const __half *>(src), static_cast<float *>(dst), n);
+  else narrow_kernel<<<blocks, 256, 0, stream>>>(static_cast<const float *>(src), static_cast<__half *>(dst), n);
+  const cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return fail(MELLIN_ERR_LAUNCH, std::string("float16 conversion: ") + cudaGetErrorString(err));
+  count_launch();
+  return MELLIN_OK;
+}
+
+struct HalfBuffers {
+  size_t x = 0, w = 0, b = 0, y = 0, inner = 0;  // float32 copies of the four tensors, then the operator's own scratch
+  size_t total() const { return x + w + b + y + inner; }
+};
+HalfBuffers half_buffers(const Geometry2D &q, int op /*0 fwd, 1 grad-input, 2 grad-weight*/) {
+  HalfBuffers h;
+  h.x = round256((size_t)q.batch * q.c_in * q.ngx * q.ngy * sizeof(float));
+  h.w = round256((size_t)q.c_out * q.c_in * q.nfx * q.nfy * sizeof(float));
+  h.b = round256((size_t)q.c_out * sizeof(float));
+  h.y = round256((size_t)q.batch * q.c_out * q.nhx * q.nhy * sizeof(float));
+  h.inner = round256(op == 2 ? gradw_workspace_query(q) : direct_workspace_query(q, op == 1));
+  return h;
+}
+int half_check(const char *who, const Geometry2D &q, const HalfBuffers &h, void *workspace, size_t workspace_bytes) {
+  const int rc = check_geometry(who, q, q.uy);
+  if (rc) return rc;
+  if (workspace == nullptr || workspace_bytes < h.total() || reinterpret_cast<uintptr_t>(workspace) % 256 != 0)
+    return fail(MELLIN_ERR_WORKSPACE, std::string(who) + ": needs " + std::to_string(h.total()) +
+                                          " bytes of 256-byte aligned workspace, got " + std::to_string(workspace_bytes));
+  return MELLIN_OK;
 }
 
 }  // namespace
@@ -790,6 +841,66 @@ int64_t mellin_index_map_build(int relation, int order, int64_t nf, int64_t ng, 
 
 size_t mellin_mcorrlcorr_grad_weight_workspace_bytes(MELLIN_LAYER_GEOMETRY) {
   return gradw_workspace_query(GEOM_FROM_LAYER);
+}
+
+size_t mellin_mcorrlcorr_forward_workspace_bytes_f16(MELLIN_LAYER_GEOMETRY) { return half_buffers(GEOM_FROM_LAYER, 0).total(); }
+size_t mellin_mcorrlcorr_grad_input_workspace_bytes_f16(MELLIN_LAYER_GEOMETRY) { return half_buffers(GEOM_FROM_LAYER, 1).total(); }
+size_t mellin_mcorrlcorr_grad_weight_workspace_bytes_f16(MELLIN_LAYER_GEOMETRY) { return half_buffers(GEOM_FROM_LAYER, 2).total(); }
+
+int mellin_mcorrlcorr_forward_f16(const void *x, const void *w, const void *bias, MELLIN_LAYER_GEOMETRY, void *y,
+                                  void *workspace, size_t workspace_bytes, void *stream) {
+  const Geometry2D q = GEOM_FROM_LAYER;
+  const HalfBuffers h = half_buffers(q, 0);
+  int rc = half_check("mcorrlcorr_forward_f16", q, h, workspace, workspace_bytes);
+  if (rc) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  unsigned char *base = static_cast<unsigned char *>(workspace);
+  float *x32 = reinterpret_cast<float *>(base), *w32 = reinterpret_cast<float *>(base + h.x);
+  float *b32 = reinterpret_cast<float *>(base + h.x + h.w), *y32 = reinterpret_cast<float *>(base + h.x + h.w + h.b);
+  if ((rc = convert_launch(true, x, x32, q.batch * q.c_in * q.ngx * q.ngy, st))) return rc;
+  if ((rc = convert_launch(true, w, w32, q.c_out * q.c_in * q.nfx * q.nfy, st))) return rc;
+  if ((rc = convert_launch(true, bias, b32, q.c_out, st))) return rc;
+  rc = op2d<float>("mcorrlcorr_forward_f16", Relation::Corr, w32, x32, q, 0, 0, 0, y32, bias ? b32 : nullptr, false,
+                   base + h.x + h.w + h.b + h.y, h.inner, stream, nullptr, 0, 0.0, 0, /*exact=*/1);
+  if (rc) return rc;
+  return convert_launch(false, y32, y, q.batch * q.c_out * q.nhx * q.nhy, st);
+}
+
+int mellin_mcorrlcorr_grad_input_f16(const void *w, const void *grad_y, MELLIN_LAYER_GEOMETRY, void *grad_x,
+                                     void *workspace, size_t workspace_bytes, void *stream) {
+  const Geometry2D q = GEOM_FROM_LAYER;
+  const HalfBuffers h = half_buffers(q, 1);
+  int rc = half_check("mcorrlcorr_grad_input_f16", q, h, workspace, workspace_bytes);
+  if (rc) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  unsigned char *base = static_cast<unsigned char *>(workspace);
+  float *x32 = reinterpret_cast<float *>(base), *w32 = reinterpret_cast<float *>(base + h.x);
+  float *y32 = reinterpret_cast<float *>(base + h.x + h.w + h.b);
+  if ((rc = convert_launch(true, w, w32, q.c_out * q.c_in * q.nfx * q.nfy, st))) return rc;
+  if ((rc = convert_launch(true, grad_y, y32, q.batch * q.c_out * q.nhx * q.nhy, st))) return rc;
+  rc = grad_input<float>("mcorrlcorr_grad_input_f16", w32, y32, q, x32, base + h.x + h.w + h.b + h.y, h.inner, stream,
+                         nullptr, /*exact=*/1);
+  if (rc) return rc;
+  return convert_launch(false, x32, grad_x, q.batch * q.c_in * q.ngx * q.ngy, st);
+}
+
+int mellin_mcorrlcorr_grad_weight_f16(const void *x, const void *grad_y, MELLIN_LAYER_GEOMETRY, void *grad_w,
+                                      void *grad_b, void *workspace, size_t workspace_bytes, void *stream) {
+  const Geometry2D q = GEOM_FROM_LAYER;
+  const HalfBuffers h = half_buffers(q, 2);
+  int rc = half_check("mcorrlcorr_grad_weight_f16", q, h, workspace, workspace_bytes);
+  if (rc) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  unsigned char *base = static_cast<unsigned char *>(workspace);
+  float *x32 = reinterpret_cast<float *>(base), *w32 = reinterpret_cast<float *>(base + h.x);
+  float *b32 = reinterpret_cast<float *>(base + h.x + h.w), *y32 = reinterpret_cast<float *>(base + h.x + h.w + h.b);
+  if ((rc = convert_launch(true, x, x32, q.batch * q.c_in * q.ngx * q.ngy, st))) return rc;
+  if ((rc = convert_launch(true, grad_y, y32, q.batch * q.c_out * q.nhx * q.nhy, st))) return rc;
+  rc = grad_weight<float>("mcorrlcorr_grad_weight_f16", x32, y32, q, w32, grad_b ? b32 : nullptr,
+                          base + h.x + h.w + h.b + h.y, h.inner, stream, nullptr, /*exact=*/1);
+  if (rc) return rc;
+  if ((rc = convert_launch(false, w32, grad_w, q.c_out * q.c_in * q.nfx * q.nfy, st))) return rc;
+  return grad_b ? convert_launch(false, b32, grad_b, q.c_out, st) : MELLIN_OK;
 }
 
 }  // extern "C"

@@ -66,6 +66,9 @@ struct DirectProblem {
   // drop_threshold (= p * 2^32; 0 switches dropout off) and scaled by drop_scale = 1 / (1 - p) otherwise
   unsigned drop_threshold = 0, drop_seed = 0;
   float drop_scale = 1.f;
+  // Both operands hold values that are exact in TF32 (e.g. widened float16): the tensor-core kernels then skip the
+  // two error-compensation products of their hi/lo split (the lo parts are all zero) -- one MMA per product, not three.
+  int exact_tf32 = 0;
 };
 
 // Stateless per-element random number of the fused dropout: a 32-bit avalanche hash of (seed, element offset).
@@ -97,6 +100,7 @@ struct GradWProblem {
   int N = 0, A = 0, B = 0;
   int nkx = 0, nky = 0, nix = 0, niy = 0, nox = 0, noy = 0;
   int Ay = 1, By = 1, Cy = 0, Dy = 1;
+  int exact_tf32 = 0;  // as in DirectProblem
 };
 
 // gather / scatter between a signal and its column form

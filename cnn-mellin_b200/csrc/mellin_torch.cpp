@@ -146,6 +146,26 @@ Tensor conv_like(const char *c, Op op, int64_t dim, const Tensor &input, const T
   c10::cuda::CUDAGuard guard(weight.device());
   if (weight.scalar_type() == at::kHalf && input.scalar_type() == at::kHalf &&
       (!bias || bias->scalar_type() == at::kHalf)) {
+    if (op == Op::Corr && lens == nullptr && input.is_contiguous() && weight.is_contiguous()) {
+      // the float16 entry point: widened in the library's scratch, one MMA per product on the tensor cores
+      ConvArgs a = check_conv(c, dim, input, weight, bias);
+      const int64_t nhx = mellin_mcorr_valid_size(a.nfx, a.ngx, s[0], d[0], p[0], u[0]) + r[0];
+      const int64_t nhy = dim == 4 ? mellin_lcorr_valid_size(a.nfy, a.ngy, s[1], d[1], p[1], u[1]) + r[1] : 1;
+      TORCH_CHECK(nhx >= 0 && nhy >= 0, c, ": r makes the output size negative");
+      std::vector<int64_t> size = {a.batch, a.c_out, nhx};
+      if (dim == 4) size.push_back(nhy);
+      Tensor out = at::empty(size, weight.options());
+      if (out.numel() == 0) return out;
+      LayerGeometry q{a.batch, a.c_in, a.c_out, a.nfx, a.nfy, a.ngx, a.ngy, nhx, nhy, s, d, p, u};
+      const size_t bytes = mellin_mcorrlcorr_forward_workspace_bytes_f16(LAYER_ARGS(q));
+      Tensor ws = at::empty({static_cast<int64_t>(bytes)}, weight.options().dtype(at::kByte));
+      Tensor b = bias ? bias->contiguous() : Tensor();
+      check_status(mellin_mcorrlcorr_forward_f16(input.data_ptr(), weight.data_ptr(), bias ? b.data_ptr() : nullptr,
+                                                 LAYER_ARGS(q), out.data_ptr(), ws.data_ptr(), bytes,
+                                                 current_stream(weight)),
+                   c);
+      return out;
+    }
     const OptTensor wide_bias = bias ? OptTensor(bias->to(at::kFloat)) : OptTensor();
     return conv_like(c, op, dim, input.to(at::kFloat), weight.to(at::kFloat), wide_bias, s, d, p, u, r, lens, relu,
                      dropout_p, seed)
@@ -375,6 +395,34 @@ std::vector<Tensor> layer_backward(const Tensor &grad_out_in, const Tensor &inpu
                                    bool need_bias, const Tensor *lens = nullptr) {
   const bool one_d = input_in.dim() == 3;
   c10::cuda::CUDAGuard guard(weight_in.device());
+  if (weight_in.scalar_type() == at::kHalf && lens == nullptr && grad_out_in.scalar_type() == at::kHalf &&
+      input_in.scalar_type() == at::kHalf && grad_out_in.numel() > 0 && input_in.numel() > 0 && weight_in.numel() > 0) {
+    // the float16 entry points (one MMA per product on the tensor cores)
+    Tensor go = grad_out_in.contiguous(), x = input_in.contiguous(), w = weight_in.contiguous();
+    LayerGeometry q{x.size(0), x.size(1), w.size(0), w.size(2), one_d ? 1 : w.size(3), x.size(2),
+                    one_d ? 1 : x.size(3), go.size(2), one_d ? 1 : go.size(3), s, d, p, u};
+    void *stream = current_stream(w);
+    Tensor gi, gw, gb;
+    if (need_input) {
+      gi = at::empty_like(x);
+      const size_t bytes = mellin_mcorrlcorr_grad_input_workspace_bytes_f16(LAYER_ARGS(q));
+      Tensor ws = at::empty({static_cast<int64_t>(bytes)}, w.options().dtype(at::kByte));
+      check_status(mellin_mcorrlcorr_grad_input_f16(w.data_ptr(), go.data_ptr(), LAYER_ARGS(q), gi.data_ptr(), ws.data_ptr(),
+                                                    bytes, stream),
+                   "mcorrlcorr_grad_input");
+    }
+    if (need_weight || (need_bias && has_bias)) {
+      gw = at::empty_like(w);
+      if (need_bias && has_bias) gb = at::empty({w.size(0)}, w.options());
+      const size_t bytes = mellin_mcorrlcorr_grad_weight_workspace_bytes_f16(LAYER_ARGS(q));
+      Tensor ws = at::empty({static_cast<int64_t>(bytes)}, w.options().dtype(at::kByte));
+      check_status(mellin_mcorrlcorr_grad_weight_f16(x.data_ptr(), go.data_ptr(), LAYER_ARGS(q), gw.data_ptr(),
+                                                     gb.defined() ? gb.data_ptr() : nullptr, ws.data_ptr(), bytes, stream),
+                   "mcorrlcorr_grad_weight");
+      if (!need_weight) gw = Tensor();
+    }
+    return {gi, gw, gb};
+  }
   if (weight_in.scalar_type() == at::kHalf) {
     std::vector<Tensor> wide = layer_backward(grad_out_in.to(at::kFloat), input_in.to(at::kFloat),
                                               weight_in.to(at::kFloat), has_bias, s, d, p, u, need_input, need_weight,

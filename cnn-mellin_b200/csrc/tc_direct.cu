@@ -116,6 +116,7 @@ struct TcParams {
   uint32_t w_res_bytes;  // > 0: the whole packed weight set (hi, then lo) stays in shared memory for the
                          // life of the block and stages hold activations only
   int profile;
+  int exact;  // operands are exact in TF32: no compensation MMAs
 };
 
 __device__ __forceinline__ float tf32_hi(float x) { return __uint_as_float(__float_as_uint(x) & 0xffffe000u); }
@@ -685,9 +686,12 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map,
               const uint64_t db_lo = db_hi + (p.w_res_bytes >> 4);
               uint32_t a_off = (uint32_t)(2 * j * p.RW), b_off = 0;
               for (int t = 0; t < p.nky; ++t) {
-                tc::mma_tf32(d_addr, da_lo0 + a_off, db_hi + b_off, idesc, accumulate);
-                tc::mma_tf32(d_addr, da_hi0 + a_off, db_lo + b_off, idesc, 1u);
-                tc::mma_tf32(d_addr, da_hi0 + a_off, db_hi + b_off, idesc, 1u);
+                if (!p.exact) {
+                  tc::mma_tf32(d_addr, da_lo0 + a_off, db_hi + b_off, idesc, accumulate);
+                  tc::mma_tf32(d_addr, da_hi0 + a_off, db_lo + b_off, idesc, 1u);
+                  accumulate = 1u;
+                }
+                tc::mma_tf32(d_addr, da_hi0 + a_off, db_hi + b_off, idesc, accumulate);
                 accumulate = 1u;
                 a_off += (uint32_t)p.absBy;
                 b_off += tap_stride;
@@ -699,9 +703,12 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map,
             uint32_t a_off = (uint32_t)(2 * j * p.RW + TAP_GROUP * p.TG * p.absBy);  // 16-byte units
             uint32_t b_off = (uint32_t)(j * 2 * p.NP);
             for (int t = 0; t < taps_here; ++t) {
-              tc::mma_tf32(d_addr, da_lo0 + a_off, db_hi0 + b_off, idesc, accumulate);
-              tc::mma_tf32(d_addr, da_hi0 + a_off, db_lo0 + b_off, idesc, 1u);
-              tc::mma_tf32(d_addr, da_hi0 + a_off, db_hi0 + b_off, idesc, 1u);
+              if (!p.exact) {
+                tc::mma_tf32(d_addr, da_lo0 + a_off, db_hi0 + b_off, idesc, accumulate);
+                tc::mma_tf32(d_addr, da_hi0 + a_off, db_lo0 + b_off, idesc, 1u);
+                accumulate = 1u;
+              }
+              tc::mma_tf32(d_addr, da_hi0 + a_off, db_hi0 + b_off, idesc, accumulate);
               accumulate = 1u;
               a_off += (uint32_t)p.absBy;
               b_off += (uint32_t)(JB * 2 * p.NP);
@@ -757,6 +764,7 @@ bool plan_tc_direct(const DirectProblem<float> &p, TcPlan &plan) {
   q.drop_threshold = p.drop_threshold, q.drop_seed = p.drop_seed, q.drop_scale = p.drop_threshold ? p.drop_scale : 1.f;
 #endif
   q.bias = p.accumulate ? nullptr : p.bias, q.out = p.out;
+  q.exact = p.exact_tf32;
   q.table_in_smem = (p.nox <= kMaxTableRows && p.table.num_entries <= kMaxTableEntries) ? 1 : 0;
   q.row_ptr = p.table.row_ptr, q.entries = p.table.entries, q.order = p.table.order, q.num_entries = (int)p.table.num_entries;
   q.N = p.N, q.A = p.A, q.B = p.B, q.Bp = (p.B + 3) / 4 * 4, q.nkx = p.nkx, q.nky = p.nky, q.nox = p.nox, q.noy = p.noy;

@@ -80,6 +80,7 @@ struct GwParams {
   int target_slices;       // sum of Z[kx] aimed at
   int stages_per_row;      // ceil(noy / 16)
   int profile;
+  int exact;               // operands are exact in TF32: no compensation MMAs
   int raw_stages;          // 3 .. kRawStages, as shared memory allows
   int chunks, chunk_stages;  // a row of positions is cut into `chunks` runs of at most `chunk_stages` stages
   uint32_t go_raw_bytes, x_raw_bytes, go_op_bytes, x_op_bytes;  // per stage; operand sizes per hi or lo part (x: per tap)
@@ -432,9 +433,12 @@ tc_gradw_kernel(const GwParams p, const __grid_constant__ CUtensorMap go_map, co
             for (int ks = 0; ks < kKB / 8; ++ks) {
               // the three products of the hi/lo split
               const uint32_t ka = soff + (uint32_t)(ks * 2 * (kGoSlab / 16)), kb = soff + (uint32_t)(ks * 2 * (kXSlab / 16));
-              tc::mma_tf32(tmem_base, dgo_lo + ka, dx_hi + kb, idesc, fresh);
-              tc::mma_tf32(tmem_base, dgo_hi + ka, dx_lo + kb, idesc, 1u);
-              tc::mma_tf32(tmem_base, dgo_hi + ka, dx_hi + kb, idesc, 1u);
+              if (!p.exact) {
+                tc::mma_tf32(tmem_base, dgo_lo + ka, dx_hi + kb, idesc, fresh);
+                tc::mma_tf32(tmem_base, dgo_hi + ka, dx_lo + kb, idesc, 1u);
+                fresh = 1u;
+              }
+              tc::mma_tf32(tmem_base, dgo_hi + ka, dx_hi + kb, idesc, fresh);
               fresh = 1u;
             }
             ++ms;
@@ -532,6 +536,7 @@ bool plan_tc_gradw(const GradWProblem<float> &p, int g0, int nky, GwPlan &plan) 
   q.N = p.N, q.A = p.A, q.B = p.B, q.nkx = p.nkx, q.nky = nky, q.noy = p.noy;
   q.g0 = g0, q.nky_total = p.nky;
   q.absBy = absBy, q.By = p.By;
+  q.exact = p.exact_tf32;
   q.xs0 = p.Cy + std::min(0, p.By * (p.nky - 1)) + g0 * absBy;
   q.RXW = (kKB + halo + 3 + 3) / 4 * 4;
   q.a_tiles = (p.A + kTM - 1) / kTM;

@@ -243,6 +243,24 @@ int mellin_mcorrlcorr_grad_weight_f64(const double *x, const double *grad_y,
 int mellin_mcorrlcorr_grad_weight_noalloc_f32(const float *x, const float *grad_y, MELLIN_LAYER_GEOMETRY,
                                               float *grad_w, float *grad_b, void *stream);
 
+/* ---- float16 ------------------------------------------------------------------ */
+
+/* Layer-level entry points on float16 tensors (`const void *` = device pointers to IEEE half values), as the
+ * reference's CUDA binding dispatches Half into its kernels (ext/torch_cuda.cu:62) with a float32 accumulator
+ * (mconv_cuda.cuh:135-139): operands are widened into the workspace, the float32 kernels run on them, results are
+ * rounded to float16 once.  Because every float16 value is exact in TF32, the tensor-core kernels issue one MMA per
+ * product here instead of the three of their float32 hi/lo split.  The workspace (256-byte aligned) must hold
+ * mellin_mcorrlcorr_*_workspace_bytes_f16(...) bytes: float32 copies of the tensors plus the operator's scratch. */
+size_t mellin_mcorrlcorr_forward_workspace_bytes_f16(MELLIN_LAYER_GEOMETRY);
+size_t mellin_mcorrlcorr_grad_input_workspace_bytes_f16(MELLIN_LAYER_GEOMETRY);
+size_t mellin_mcorrlcorr_grad_weight_workspace_bytes_f16(MELLIN_LAYER_GEOMETRY);
+int mellin_mcorrlcorr_forward_f16(const void *x, const void *w, const void *bias, MELLIN_LAYER_GEOMETRY, void *y,
+                                  void *workspace, size_t workspace_bytes, void *stream);
+int mellin_mcorrlcorr_grad_input_f16(const void *w, const void *grad_y, MELLIN_LAYER_GEOMETRY, void *grad_x,
+                                     void *workspace, size_t workspace_bytes, void *stream);
+int mellin_mcorrlcorr_grad_weight_f16(const void *x, const void *grad_y, MELLIN_LAYER_GEOMETRY, void *grad_w,
+                                      void *grad_b, void *workspace, size_t workspace_bytes, void *stream);
+
 /* ---- diagnostics ------------------------------------------------------------ */
 
 /* Number of kernels this library has launched from the calling process since
