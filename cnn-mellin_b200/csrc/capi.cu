@@ -129,8 +129,12 @@ int dispatch_direct(const DirectProblem<float> &p, void *workspace, size_t works
     return rc ? rc : launch_mask_relu(p, stream);
   }
   if (p.A <= 4) {
-    // a handful of output channels: the row-streaming CUDA-core kernel
-    const int rc = launch_direct_rows(p, workspace, workspace_bytes, stream);
+    // a handful of output channels: by source row on the tensor cores (each row of the reduced tensor
+    // fetched once, partial planes in the workspace) when covered, else the row-streaming CUDA-core kernel
+    int rc = (p.accumulate || !tensor_cores_enabled()) ? MELLIN_ERR_UNSUPPORTED
+                                                       : launch_tc_scatter(p, workspace, workspace_bytes, stream);
+    if (rc != MELLIN_ERR_UNSUPPORTED) return rc;
+    rc = launch_direct_rows(p, workspace, workspace_bytes, stream);
     if (rc != MELLIN_ERR_UNSUPPORTED) return rc;
   }
   if (!p.accumulate && tensor_cores_enabled() && workspace != nullptr) {
@@ -407,6 +411,12 @@ int op2d(const char *who, Relation rel, const T *f, const T *g, const Geometry2D
     p.drop_seed = dropout_seed;
     p.drop_scale = (float)(1.0 / (1.0 - dropout_p));
   }
+  if constexpr (std::is_same<T, float>::value) {
+    if (has_terms && p.A <= 4 && !accumulate && workspace != nullptr) {
+      rc = get_device_table(IndexMapKey{rel, SortBy::G, q.nfx, q.ngx, q.nhx, q.sx, q.dx, q.px, q.ux}, &p.table_by_in);
+      if (rc) return rc;
+    }
+  }
   if (accumulate && workspace == nullptr) {
     rc = dispatch_accumulating(p, static_cast<cudaStream_t>(stream));
     if (rc != MELLIN_ERR_UNSUPPORTED) return rc;
@@ -470,6 +480,13 @@ int grad_input(const char *who, const T *w, const T *go, const Geometry2D &q, T 
   p.Ay = (int)q.uy, p.By = -(int)q.dy, p.Cy = (int)q.py, p.Dy = (int)q.sy;
   p.accumulate = false;
   p.exact_tf32 = exact;
+  if constexpr (std::is_same<T, float>::value) {
+    if (has_terms && p.A <= 4 && workspace != nullptr) {
+      rc = get_device_table(IndexMapKey{Relation::Corr, SortBy::H, q.nfx, q.ngx, q.nhx, q.sx, q.dx, q.px, q.ux},
+                            &p.table_by_in);
+      if (rc) return rc;
+    }
+  }
   if (lens != nullptr && q.uy == 1 && p.A > 4) {
     // grad_y is zero from position lens[n] on, so grad_x is zero from this position on: the last
     // input position any output below lens[n] reads is s (len - 1) - p + d (nfy - 1)
@@ -761,6 +778,9 @@ int mellin_device_status(int *code) {
   rows_code = 0;
   rc = direct_rows_take_error(&rows_code);
   if (rc == MELLIN_OK && *code == 0 && rows_code != 0) *code = 300 + rows_code;
+  if (rc) return rc;
+  rc = tc_scatter_take_error(&rows_code);
+  if (rc == MELLIN_OK && *code == 0 && rows_code != 0) *code = 400 + rows_code;
   return rc;
 }
 int mellin_selftest_unarmed_wait(void *stream) { return launch_unarmed_wait(static_cast<cudaStream_t>(stream)); }
@@ -787,7 +807,14 @@ size_t direct_workspace_query(const Geometry2D &q, bool input_gradient) {
   p.Cy = input_gradient ? (int)q.py : -(int)q.py;
   p.Dy = input_gradient ? (int)q.sy : (int)q.uy;
   p.table.max_row = (int)q.nfx;  // upper bound: one entry per kernel tap
-  const size_t rows = p.A <= 4 ? direct_rows_workspace_bytes(p) : 0;
+  size_t rows = p.A <= 4 ? direct_rows_workspace_bytes(p) : 0;
+  if (p.A <= 4 && q.nfx <= 16 && q.nfx > 0) {
+    // the by-source-row kernel keeps one partial plane per table entry: count them
+    p.table_by_in.num_entries =
+        (int64_t)enumerate_triples(Relation::Corr, q.nfx, q.ngx, q.nhx, q.sx, q.dx, q.px, q.ux).size();
+    p.table_by_in.max_row = (int)q.nfx;
+    rows = std::max(rows, tc_scatter_workspace_bytes(p));
+  }
   // the query describes dense tensors
   p.in_sb = (long long)p.nix * p.niy, p.in_sn = (long long)p.B * p.nix * p.niy;
   return std::max(std::max(rows, direct_tc_workspace_bytes(p)),

@@ -51,6 +51,9 @@ struct DirectProblem {
   const T *bias = nullptr;  // used when !accumulate; may be null
   T *out = nullptr;
   DeviceTable table;  // rows = ox, entries (kx, ix)
+  // The same triples by SOURCE row (rows = ix, entries (kx, ox)); optional: filled in for problems
+  // with a handful of output channels, which tc_scatter.cu walks by source row.
+  DeviceTable table_by_in;
   int N = 0, A = 0, B = 0;
   int nkx = 0, nky = 0, nix = 0, niy = 0, nox = 0, noy = 0;
   long long in_sn = 0, in_sb = 0;    // element strides of in[n], in[.., b]
@@ -128,6 +131,10 @@ size_t direct_tc_workspace_bytes(const DirectProblem<float> &p);
 int launch_direct_tc(const DirectProblem<float> &p, void *workspace, size_t workspace_bytes, cudaStream_t stream);
 int tc_take_error(int *code);
 int direct_rows_take_error(int *code);
+// few-output-channel operator walked by source row on tensor cores (tc_scatter.cu); needs p.table_by_in
+size_t tc_scatter_workspace_bytes(const DirectProblem<float> &p);
+int launch_tc_scatter(const DirectProblem<float> &p, void *workspace, size_t workspace_bytes, cudaStream_t stream);
+int tc_scatter_take_error(int *code);
 int gradw_rows_take_error(int *code);
 int launch_unarmed_wait(cudaStream_t stream);  // self-test of the bounded waits (gradw_rows.cu)
 // tensor-core forward with the fused length mask / ReLU epilogue (tc_direct_masked.cu)

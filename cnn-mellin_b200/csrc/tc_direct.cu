@@ -629,7 +629,12 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map,
     PROF_END(3);
   } else if (warp == kMmaWarp) {
     // =========================== MMA issuer ===========================
-    if (lane == 0) {
+    // The whole warp walks the tiles and one elected lane issues: addresses and descriptors computed by all
+    // lanes from warp-uniform values (what is read from shared or global memory is broadcast from lane 0 to
+    // say so) can live in the uniform registers the MMA reads them from.  Issued from inside an
+    // `if (lane == 0)` region the same MMAs cost the issuing thread about twice as long.
+    {
+      const uint32_t tmem0 = tc::uniform(tmem_base);
       const uint32_t idesc = tc::idesc_tf32(kTileM, p.NP);
       const uint32_t a_lbo = (uint32_t)p.RW * 16u;
       const uint32_t b_lbo = (uint32_t)p.NP * 16u;
@@ -639,8 +644,8 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map,
       bool failed = false;
       PROF_BEGIN();
       TileWalker tc_;
-      for (tc_.init(p, order); tc_.tile < p.tiles && !*abort_flag && !failed; tc_.next(p)) {
-        const int Kr = TILE_ROWS((rowptr[tc_.ox + 1] - rowptr[tc_.ox]) * p.Bp);
+      for (tc_.init(p, order); tc_.tile < p.tiles && !tc::uniform((uint32_t)*abort_flag) && !failed; tc_.next(p)) {
+        const int Kr = (int)tc::uniform((uint32_t)TILE_ROWS((rowptr[tc_.ox + 1] - rowptr[tc_.ox]) * p.Bp));
         uint32_t accumulate = 0;
         int left = 0;  // K-blocks left in the open accumulation interval
         int kb = 0;
@@ -658,13 +663,13 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map,
                            (!opens || tc::mbar_wait(&ctl->dempty[acc], (uint32_t)(((g >> 1) & 1) ^ 1), kSpinLimit));
           PROF_WAIT_END();
           if (opens) accumulate = 0;
-          if (!okf) {
-            raise_timeout(ctl, 4);
+          if (!__all_sync(0xffffffffu, okf)) {
+            if (lane == 0) raise_timeout(ctl, 4);
             failed = true;
             break;
           }
           tc::tc_fence_after_sync();
-          const uint32_t d_addr = tmem_base + (uint32_t)(acc * p.NP);
+          const uint32_t d_addr = tmem0 + (uint32_t)(acc * p.NP);
           const uint32_t st = tc::smem_u32(stage_base + (size_t)s * stage_bytes);
           // descriptors of (k-step 0, tap 0); the others differ only in the start-address field
           const uint64_t da_hi0 = tc::smem_desc(st, a_lbo, 128u);
@@ -673,50 +678,64 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map,
           const uint64_t db_lo0 = tc::smem_desc(st + 2 * p.a_stage_bytes + p.w_stage_bytes, b_lbo, 128u);
           const int rows_here = min(p.KB, Kr - k0);
           const int jb_here = (rows_here + 7) >> 3;
+          const bool commit_tile = left == 0 || LAST_STAGE_OF_TILE;
           if (p.w_res_bytes) {
             // resident weights: the two 16-byte K-chunks of a k-step are the chunks
             // of two consecutive (entry, channel group) rows; their distance goes
             // into the descriptor
-            const uint32_t wr = tc::smem_u32(w_res) + (uint32_t)(tc_.at * tile_chunks) * 16u;
+            const uint32_t wr = tc::smem_u32(w_res) + tc::uniform((uint32_t)(tc_.at * tile_chunks)) * 16u;
             const uint32_t tap_stride = (uint32_t)(B4 * p.NP);  // 16-byte units between taps
             const uint2 *ks = kstep_s + kofs_s[tc_.ox] + (k0 >> 3);
             for (int j = 0; j < jb_here; ++j) {
               const uint2 k = ks[j];
-              const uint64_t db_hi = tc::smem_desc(wr + k.x * 16u, k.y * 16u, 128u);
+              const uint64_t db_hi = tc::smem_desc(wr + tc::uniform(k.x) * 16u, tc::uniform(k.y) * 16u, 128u);
               const uint64_t db_lo = db_hi + (p.w_res_bytes >> 4);
-              uint32_t a_off = (uint32_t)(2 * j * p.RW), b_off = 0;
-              for (int t = 0; t < p.nky; ++t) {
-                if (!p.exact) {
-                  tc::mma_tf32(d_addr, da_lo0 + a_off, db_hi + b_off, idesc, accumulate);
-                  tc::mma_tf32(d_addr, da_hi0 + a_off, db_lo + b_off, idesc, 1u);
-                  accumulate = 1u;
+              if (tc::elect_one()) {
+                uint32_t a_off = (uint32_t)(2 * j * p.RW), b_off = 0;
+                uint32_t accum = accumulate;
+                for (int t = 0; t < p.nky; ++t) {
+                  if (!p.exact) {
+                    tc::mma_tf32(d_addr, da_lo0 + a_off, db_hi + b_off, idesc, accum);
+                    tc::mma_tf32(d_addr, da_hi0 + a_off, db_lo + b_off, idesc, 1u);
+                    accum = 1u;
+                  }
+                  tc::mma_tf32(d_addr, da_hi0 + a_off, db_hi + b_off, idesc, accum);
+                  accum = 1u;
+                  a_off += (uint32_t)p.absBy;
+                  b_off += tap_stride;
                 }
-                tc::mma_tf32(d_addr, da_hi0 + a_off, db_hi + b_off, idesc, accumulate);
-                accumulate = 1u;
-                a_off += (uint32_t)p.absBy;
-                b_off += tap_stride;
               }
+              accumulate = 1u;
+            }
+            if (tc::elect_one()) {
+              tc::tc_commit(&ctl->empty[s]);
+              if (commit_tile) tc::tc_commit(&ctl->dfull[acc]);
             }
           } else {
-          const int taps_here = TAPS_HERE;
-          for (int j = 0; j < jb_here; ++j) {
-            uint32_t a_off = (uint32_t)(2 * j * p.RW + TAP_GROUP * p.TG * p.absBy);  // 16-byte units
-            uint32_t b_off = (uint32_t)(j * 2 * p.NP);
-            for (int t = 0; t < taps_here; ++t) {
-              if (!p.exact) {
-                tc::mma_tf32(d_addr, da_lo0 + a_off, db_hi0 + b_off, idesc, accumulate);
-                tc::mma_tf32(d_addr, da_hi0 + a_off, db_lo0 + b_off, idesc, 1u);
-                accumulate = 1u;
+            const int taps_here = TAPS_HERE;
+            if (tc::elect_one()) {
+              uint32_t accum = accumulate;
+              for (int j = 0; j < jb_here; ++j) {
+                uint32_t a_off = (uint32_t)(2 * j * p.RW + TAP_GROUP * p.TG * p.absBy);  // 16-byte units
+                uint32_t b_off = (uint32_t)(j * 2 * p.NP);
+                for (int t = 0; t < taps_here; ++t) {
+                  if (!p.exact) {
+                    tc::mma_tf32(d_addr, da_lo0 + a_off, db_hi0 + b_off, idesc, accum);
+                    tc::mma_tf32(d_addr, da_hi0 + a_off, db_lo0 + b_off, idesc, 1u);
+                    accum = 1u;
+                  }
+                  tc::mma_tf32(d_addr, da_hi0 + a_off, db_hi0 + b_off, idesc, accum);
+                  accum = 1u;
+                  a_off += (uint32_t)p.absBy;
+                  b_off += (uint32_t)(JB * 2 * p.NP);
+                }
               }
-              tc::mma_tf32(d_addr, da_hi0 + a_off, db_hi0 + b_off, idesc, accumulate);
-              accumulate = 1u;
-              a_off += (uint32_t)p.absBy;
-              b_off += (uint32_t)(JB * 2 * p.NP);
+              tc::tc_commit(&ctl->empty[s]);
+              if (commit_tile) tc::tc_commit(&ctl->dfull[acc]);
             }
+            accumulate = 1u;
           }
-          }
-          tc::tc_commit(&ctl->empty[s]);
-          if (left == 0 || LAST_STAGE_OF_TILE) tc::tc_commit(&ctl->dfull[acc]);
+          __syncwarp();
         }
         if (Kr > 0) ++g;
       }

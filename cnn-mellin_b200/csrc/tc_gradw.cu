@@ -387,7 +387,13 @@ tc_gradw_kernel(const GwParams p, const __grid_constant__ CUtensorMap go_map, co
     __syncwarp();
   } else if (warp == kMmaWarp) {
     // ===================== MMA issuer =====================
-    if (lane == 0) {
+    // The whole warp walks the items and one elected lane issues: addresses and descriptors computed by all
+    // lanes from warp-uniform values (what is read from shared or global memory is broadcast from lane 0 to
+    // say so) can live in the uniform registers the MMA reads them from.
+    {
+      const uint32_t tmem0 = tc::uniform(tmem_base);
+      const int zu = (int)tc::uniform((uint32_t)z), Zu = (int)tc::uniform((uint32_t)Z);
+      const int items_u = (int)tc::uniform((uint32_t)items), mma_stages_u = (int)tc::uniform((uint32_t)mma_stages);
       const uint32_t idesc = tc::idesc_tf32(kTM, NKY * kNB);  // the taps side by side in the columns
       // descriptors of stage 0; a stage's are these plus its offset
       const uint32_t ops0 = tc::smem_u32(op_base);
@@ -400,16 +406,17 @@ tc_gradw_kernel(const GwParams p, const __grid_constant__ CUtensorMap go_map, co
       bool failed = false;
       long long prof_l1 = 0;
       PROF_BEGIN();
-      for (int i = z; i < items && !failed; i += Z) {
-        const bool bias_only = (p.entries[ITEM_ENTRY(i)].x & kFlagBiasOnly) != 0;
-        const int s_end = ITEM_END_STAGE(i);
-        for (int sidx = ITEM_FIRST_STAGE(i); sidx < s_end; ++sidx, ++it) {
+      for (int i = zu; i < items_u && !failed; i += Zu) {
+        const bool bias_only = tc::uniform((uint32_t)(p.entries[ITEM_ENTRY(i)].x & kFlagBiasOnly)) != 0;
+        const int s_first = (int)tc::uniform((uint32_t)ITEM_FIRST_STAGE(i));
+        const int s_end = (int)tc::uniform((uint32_t)ITEM_END_STAGE(i));
+        for (int sidx = s_first; sidx < s_end; ++sidx, ++it) {
           const int s = it % kOpStages;
           PROF_WAIT_START();
           const bool full_ok = tc::mbar_wait(&ctl->full[s], (uint32_t)((it / kOpStages) & 1), kSpinLimit);
           PROF_WAIT_END();
-          if (!full_ok) {
-            raise_timeout(ctl, 4);
+          if (!__all_sync(0xffffffffu, full_ok)) {
+            if (lane == 0) raise_timeout(ctl, 4);
             failed = true;
             break;
           }
@@ -420,8 +427,8 @@ tc_gradw_kernel(const GwParams p, const __grid_constant__ CUtensorMap go_map, co
               const long long l1_t0 = p.profile ? clock64() : 0;
               const bool l1_ok = tc::mbar_wait(&ctl->l1_empty, (uint32_t)((iv & 1) ^ 1), kSpinLimit);
               if (p.profile) prof_l1 += clock64() - l1_t0;
-              if (!l1_ok) {
-                raise_timeout(ctl, 2);
+              if (!__all_sync(0xffffffffu, l1_ok)) {
+                if (lane == 0) raise_timeout(ctl, 2);
                 failed = true;
                 break;
               }
@@ -429,28 +436,34 @@ tc_gradw_kernel(const GwParams p, const __grid_constant__ CUtensorMap go_map, co
             }
             tc::tc_fence_after_sync();
             const uint32_t soff = (uint32_t)s * (op_bytes >> 4);  // descriptor addresses count 16-byte units
+            if (tc::elect_one()) {
+              uint32_t fr = fresh;
 #pragma unroll
-            for (int ks = 0; ks < kKB / 8; ++ks) {
-              // the three products of the hi/lo split
-              const uint32_t ka = soff + (uint32_t)(ks * 2 * (kGoSlab / 16)), kb = soff + (uint32_t)(ks * 2 * (kXSlab / 16));
-              if (!p.exact) {
-                tc::mma_tf32(tmem_base, dgo_lo + ka, dx_hi + kb, idesc, fresh);
-                tc::mma_tf32(tmem_base, dgo_hi + ka, dx_lo + kb, idesc, 1u);
-                fresh = 1u;
+              for (int ks = 0; ks < kKB / 8; ++ks) {
+                // the three products of the hi/lo split
+                const uint32_t ka = soff + (uint32_t)(ks * 2 * (kGoSlab / 16)), kb = soff + (uint32_t)(ks * 2 * (kXSlab / 16));
+                if (!p.exact) {
+                  tc::mma_tf32(tmem0, dgo_lo + ka, dx_hi + kb, idesc, fr);
+                  tc::mma_tf32(tmem0, dgo_hi + ka, dx_lo + kb, idesc, 1u);
+                  fr = 1u;
+                }
+                tc::mma_tf32(tmem0, dgo_hi + ka, dx_hi + kb, idesc, fr);
+                fr = 1u;
               }
-              tc::mma_tf32(tmem_base, dgo_hi + ka, dx_hi + kb, idesc, fresh);
-              fresh = 1u;
             }
+            fresh = 1u;
             ++ms;
           }
-          tc::tc_commit(&ctl->empty[s]);
-          if (!bias_only && (ms % kPromote == 0 || ms == mma_stages)) tc::tc_commit(&ctl->l1_full);
+          if (tc::elect_one()) {
+            tc::tc_commit(&ctl->empty[s]);
+            if (!bias_only && (ms % kPromote == 0 || ms == mma_stages_u)) tc::tc_commit(&ctl->l1_full);
+          }
+          __syncwarp();
         }
       }
       PROF_END(2);
-      if (blockIdx.x == 0 && p.profile) g_gw_prof[12] = prof_l1, g_gw_prof[13] = it;
+      if (blockIdx.x == 0 && lane == 0 && p.profile) g_gw_prof[12] = prof_l1, g_gw_prof[13] = it;
     }
-    __syncwarp();
   }
 
   tc::tc_fence_before_sync();

@@ -11,6 +11,21 @@ __device__ __forceinline__ uint32_t smem_u32(const void *p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// One lane of a converged warp (the same one every time).  Code that issues tcgen05.mma / commit keeps
+// the whole warp in the loop and predicates the instruction with this: descriptors and addresses computed
+// by all lanes from warp-uniform values can live in uniform registers, which is where the instruction
+// reads them from; computed inside an `if (lane == 0)` region they are moved there one by one.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+__device__ __forceinline__ uint32_t uniform(uint32_t v) { return __shfl_sync(0xffffffffu, v, 0); }
+
 // ---- mbarrier ------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
@@ -114,6 +129,19 @@ __device__ __forceinline__ void mma_tf32(uint32_t taddr_d, uint64_t desc_a, uint
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
       :
       : "r"(taddr_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// the same with operand A in tensor memory: row m of A in lane m, its K elements in consecutive
+// 32-bit columns starting at `taddr_a`
+__device__ __forceinline__ void mma_tf32_a_tmem(uint32_t taddr_d, uint32_t taddr_a, uint64_t desc_b, uint32_t idesc,
+                                                uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
+      :
+      : "r"(taddr_d), "r"(taddr_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 

@@ -277,8 +277,8 @@ int mellin_set_tensor_cores(int enable);
  * that launch are incomplete.  This call synchronises the current device,
  * stores the first code recorded since the last query in *code (0 = healthy;
  * 1..99 tensor-core forward / grad-input, 100.. tensor-core weight gradient,
- * 200.. row-streaming weight gradient, 300.. row-streaming grad-input) and
- * clears it. */
+ * 200.. row-streaming weight gradient, 300.. row-streaming grad-input by
+ * output row, 400.. tensor-core grad-input by source row) and clears it. */
 int mellin_device_status(int *code);
 
 /* Self-test of the bounded waits: launches one thread that waits, with a limit
