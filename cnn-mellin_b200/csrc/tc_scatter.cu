@@ -110,6 +110,7 @@ struct TsParams {
   float *out;
   float *b_pack;               // [ix][k-block][hi | lo][4-channel chunk][column][4]
   float *planes;               // [n][entry][a][plane]
+  int *plane_of;               // for every entry of the by-output-row table: the entry of the by-source-row table (= plane)
   long long w_sa, w_sb, out_sn, out_sa;
   long long entries;           // table entries = planes per (n, a)
   int N, A, B, nkx, nky, nix, nox, noy, By;
@@ -156,29 +157,40 @@ __device__ __forceinline__ int pad16(int v) { return (v + 15) & ~15; }
 
 // The B operand of every source row: column (entry, a, tap) of row ix holds W[a, b, kx(entry), ky(tap)]
 // (taps in increasing input offset), split into TF32 hi / lo parts, in the K-major operand layout of a
-// GEMM with pad16(columns) columns; unused columns and channels past the last are zero.
-__global__ void pack_scatter_b_kernel(const TsParams p) {
-  const int ix = blockIdx.x / p.kblocks, kb = blockIdx.x % p.kblocks;
+// GEMM with pad16(columns) columns; unused columns and channels past the last are zero.  Grid: (chunks of
+// 256 elements, source row x k-block); one more row of blocks (blockIdx.y = nix * kblocks) finds, for every
+// entry of the by-output-row table, the partial plane that holds its sums.
+__global__ void __launch_bounds__(256) pack_scatter_b_kernel(const TsParams p) {
+  if ((int)blockIdx.y == p.nix * p.kblocks) {
+    const int total = p.row_ptr_out[p.nox];
+    for (int e = blockIdx.x * 256 + threadIdx.x; e < total; e += gridDim.x * 256) {
+      const int2 t = p.entries_out[e];  // (kx, ix)
+      int found = 0;
+      for (int j = p.row_ptr_in[t.y]; j < p.row_ptr_in[t.y + 1]; ++j)
+        if (p.entries_in[j].x == t.x) found = j;
+      p.plane_of[e] = found;
+    }
+    return;
+  }
+  const int ix = blockIdx.y / p.kblocks, kb = blockIdx.y % p.kblocks;
   const int e0 = p.row_ptr_in[ix];
   const int cols = (p.row_ptr_in[ix + 1] - e0) * p.AN;
-  if (cols == 0) return;
   const int n_pad = pad16(cols);
-  float *dst = p.b_pack + (size_t)blockIdx.x * 64 * p.n_max_pad;
-  for (int j = threadIdx.x; j < 64 * n_pad; j += blockDim.x) {
-    const int part = j / (32 * n_pad), r1 = j % (32 * n_pad);
-    const int c = r1 / (4 * n_pad), r2 = r1 % (4 * n_pad);
-    const int col = r2 >> 2, b = kb * kKB + 4 * c + (r2 & 3);
-    float v = 0.f;
-    if (col < cols && b < p.B) {
-      const int e = col / p.AN, a = (col % p.AN) / p.nky, k = col % p.nky;
-      const int ky = p.By < 0 ? p.nky - 1 - k : k;
-      const int kx = p.entries_in[e0 + e].x;
-      const float w = p.w[a * p.w_sa + b * p.w_sb + (long long)kx * p.nky + ky];
-      const float hi = tf32_hi(w);
-      v = part ? w - hi : hi;
-    }
-    dst[j] = v;
+  const int j = blockIdx.x * 256 + threadIdx.x;
+  if (j >= 64 * n_pad) return;  // also rows without entries
+  const int part = j / (32 * n_pad), r1 = j % (32 * n_pad);
+  const int c = r1 / (4 * n_pad), r2 = r1 % (4 * n_pad);
+  const int col = r2 >> 2, b = kb * kKB + 4 * c + (r2 & 3);
+  float v = 0.f;
+  if (col < cols && b < p.B) {
+    const int e = col / p.AN, a = (col % p.AN) / p.nky, k = col % p.nky;
+    const int ky = p.By < 0 ? p.nky - 1 - k : k;
+    const int kx = p.entries_in[e0 + e].x;
+    const float w = p.w[a * p.w_sa + b * p.w_sb + (long long)kx * p.nky + ky];
+    const float hi = tf32_hi(w);
+    v = part ? w - hi : hi;
   }
+  p.b_pack[(size_t)blockIdx.y * 64 * p.n_max_pad + j] = v;
 }
 
 template <int NKY>
@@ -272,16 +284,21 @@ tc_scatter_kernel(const TsParams p, const __grid_constant__ CUtensorMap in_map) 
         }
         // all the shuffles first, in converged code; the stores (lane-dependent) after them
         float sums[16];
+        const int left = nea - c0;  // warp-uniform
 #pragma unroll
-        for (int jj = 0; jj < 16; ++jj) {
-          sums[jj] = __uint_as_float(v[(jj * NKY) / 16][(jj * NKY) % 16]);
+        for (int half = 0; half < 2; ++half) {
+          if (8 * half < left) {  // the second eight pairs only where the row has them
 #pragma unroll
-          for (int k = 1; k < NKY; ++k)
-            sums[jj] += __shfl_down_sync(0xffffffffu, __uint_as_float(v[(jj * NKY + k) / 16][(jj * NKY + k) % 16]), k);
+            for (int jj = 8 * half; jj < 8 * half + 8; ++jj) {
+              sums[jj] = __uint_as_float(v[(jj * NKY) / 16][(jj * NKY) % 16]);
+#pragma unroll
+              for (int k = 1; k < NKY; ++k)
+                sums[jj] += __shfl_down_sync(0xffffffffu, __uint_as_float(v[(jj * NKY + k) / 16][(jj * NKY + k) % 16]), k);
+            }
+          }
         }
         if (store) {
           float *d = dst + (size_t)c0 * p.plane;
-          const int left = nea - c0;
 #pragma unroll
           for (int jj = 0; jj < 16; ++jj)
             if (jj < left) d[(size_t)jj * p.plane] = sums[jj];
@@ -478,29 +495,26 @@ tc_scatter_kernel(const TsParams p, const __grid_constant__ CUtensorMap in_map) 
 }
 
 // out[n, a, ox, oy] = init + sum of the planes of row ox's entries, in table order.
-// A block owns (n, ox); a thread takes groups of 4 consecutive positions, so that up to
+// A block owns (n, ox, a); a thread takes groups of 4 consecutive positions, so that up to
 // 4 x entries independent loads are in flight per thread (the planes were written a moment
 // ago: most of them are still in L2).
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(128)
 gather_planes_kernel(const TsParams p, int vec_store) {
   __shared__ int pid[kMaxEntries];
-  const int ox = blockIdx.x % p.nox, n = blockIdx.x / p.nox;
+  int bid = blockIdx.x;
+  const int a = bid % p.A;
+  bid /= p.A;
+  const int ox = bid % p.nox, n = bid / p.nox;
   const int e0 = p.row_ptr_out[ox];
   const int np = min(p.row_ptr_out[ox + 1] - e0, kMaxEntries);
-  if ((int)threadIdx.x < np) {
-    const int2 e = p.entries_out[e0 + threadIdx.x];  // (kx, ix)
-    int found = 0;
-    for (int j = p.row_ptr_in[e.y]; j < p.row_ptr_in[e.y + 1]; ++j)
-      if (p.entries_in[j].x == e.x) found = j;
-    pid[threadIdx.x] = found;
-  }
+  if ((int)threadIdx.x < np) pid[threadIdx.x] = p.plane_of[e0 + threadIdx.x];
   __syncthreads();
-  const float *__restrict__ base = p.planes + (size_t)n * p.entries * p.A * p.plane + p.shift;
-  const int groups = (p.noy + 3) / 4;
-  for (int i = threadIdx.x; i < p.A * groups; i += 256) {
-    const int a = i / groups, oy = 4 * (i - a * groups);
-    float *out = p.out + n * p.out_sn + a * p.out_sa + (long long)ox * p.noy + oy;
-    const float bias = (!p.accumulate && p.bias != nullptr) ? __ldg(p.bias + a) : 0.f;
+  const float *__restrict__ base = p.planes + ((size_t)n * p.entries * p.A + a) * p.plane + p.shift;
+  const size_t entry_pitch = (size_t)p.A * p.plane;
+  float *out_row = p.out + n * p.out_sn + a * p.out_sa + (long long)ox * p.noy;
+  const float bias = (!p.accumulate && p.bias != nullptr) ? __ldg(p.bias + a) : 0.f;
+  for (int oy = 4 * threadIdx.x; oy < p.noy; oy += 4 * 128) {
+    float *out = out_row + oy;
     float v[4] = {bias, bias, bias, bias};
     if (vec_store && oy + 3 < p.noy) {
       if (p.accumulate) {
@@ -508,16 +522,16 @@ gather_planes_kernel(const TsParams p, int vec_store) {
         v[0] = old.x, v[1] = old.y, v[2] = old.z, v[3] = old.w;
       }
       for (int e = 0; e < np; ++e) {
-        const float *src = base + ((size_t)pid[e] * p.A + a) * p.plane + oy;
+        const float *src = base + (size_t)pid[e] * entry_pitch + oy;
 #pragma unroll
         for (int j = 0; j < 4; ++j) v[j] += __ldcg(src + j);
       }
       *reinterpret_cast<float4 *>(out) = make_float4(v[0], v[1], v[2], v[3]);
     } else {
       for (int j = 0; j < 4 && oy + j < p.noy; ++j) {
-        float s = p.accumulate ? out[j] : bias;
-        for (int e = 0; e < np; ++e) s += __ldcg(base + ((size_t)pid[e] * p.A + a) * p.plane + oy + j);
-        out[j] = s;
+        float sum = p.accumulate ? out[j] : bias;
+        for (int e = 0; e < np; ++e) sum += __ldcg(base + (size_t)pid[e] * entry_pitch + oy + j);
+        out[j] = sum;
       }
     }
   }
@@ -527,7 +541,8 @@ size_t round256(size_t v) { return (v + 255) / 256 * 256; }
 
 struct TsPlan {
   TsParams params;
-  size_t smem = 0, b_pack_bytes = 0, planes_bytes = 0;
+  size_t smem = 0, b_pack_bytes = 0, planes_bytes = 0, index_bytes = 0;
+  size_t total() const { return b_pack_bytes + planes_bytes + index_bytes; }
   int blocks = 0;
 };
 
@@ -570,6 +585,7 @@ bool plan_tc_scatter(const DirectProblem<float> &p, TsPlan &plan) {
   if (plan.smem > 227 * 1024) return false;
   plan.b_pack_bytes = round256((size_t)p.nix * q.kblocks * 64 * q.n_max_pad * sizeof(float));
   plan.planes_bytes = round256((size_t)p.N * q.entries * p.A * q.plane * sizeof(float));
+  plan.index_bytes = round256((size_t)q.entries * sizeof(int));
   plan.blocks = (int)std::min<long long>(sm_count(), total);
   return true;
 }
@@ -610,7 +626,7 @@ extern "C" int mellin_tc_scatter_profile(long long *out) {
 size_t tc_scatter_workspace_bytes(const DirectProblem<float> &p) {
   TsPlan plan;
   if (!plan_tc_scatter(p, plan)) return 0;
-  return plan.b_pack_bytes + plan.planes_bytes;
+  return plan.total();
 }
 
 // MELLIN_ERR_UNSUPPORTED when the problem is outside this kernel's coverage or the workspace too small.
@@ -618,7 +634,7 @@ int launch_tc_scatter(const DirectProblem<float> &p, void *workspace, size_t wor
   TsPlan plan;
   if (p.table_by_in.row_ptr == nullptr || p.table.row_ptr == nullptr || !plan_tc_scatter(p, plan))
     return MELLIN_ERR_UNSUPPORTED;
-  if (workspace == nullptr || workspace_bytes < plan.b_pack_bytes + plan.planes_bytes ||
+  if (workspace == nullptr || workspace_bytes < plan.total() ||
       reinterpret_cast<uintptr_t>(workspace) % 256 != 0)
     return MELLIN_ERR_UNSUPPORTED;
   EncodeTiledFn encode = tensor_map_encoder();
@@ -641,7 +657,8 @@ int launch_tc_scatter(const DirectProblem<float> &p, void *workspace, size_t wor
   unsigned char *base = static_cast<unsigned char *>(workspace);
   q.b_pack = reinterpret_cast<float *>(base);
   q.planes = reinterpret_cast<float *>(base + plan.b_pack_bytes);
-  pack_scatter_b_kernel<<<(unsigned)(p.nix * q.kblocks), 256, 0, stream>>>(q);
+  q.plane_of = reinterpret_cast<int *>(base + plan.b_pack_bytes + plan.planes_bytes);
+  pack_scatter_b_kernel<<<dim3((unsigned)((64 * q.n_max_pad + 255) / 256), (unsigned)(p.nix * q.kblocks + 1)), 256, 0, stream>>>(q);
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return fail(MELLIN_ERR_LAUNCH, std::string("pack_scatter_b_kernel: ") + cudaGetErrorString(err));
   count_launch();
@@ -654,7 +671,7 @@ int launch_tc_scatter(const DirectProblem<float> &p, void *workspace, size_t wor
   count_launch();
   const int vec_store =
       (reinterpret_cast<uintptr_t>(p.out) % 16 == 0 && p.noy % 4 == 0 && p.out_sn % 4 == 0 && p.out_sa % 4 == 0) ? 1 : 0;
-  gather_planes_kernel<<<(unsigned)(p.N * p.nox), 256, 0, stream>>>(q, vec_store);
+  gather_planes_kernel<<<(unsigned)(p.N * p.nox * p.A), 128, 0, stream>>>(q, vec_store);
   err = cudaGetLastError();
   if (err != cudaSuccess) return fail(MELLIN_ERR_LAUNCH, std::string("gather_planes_kernel: ") + cudaGetErrorString(err));
   count_launch();
