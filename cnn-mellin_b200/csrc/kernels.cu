@@ -601,6 +601,39 @@ __global__ void reduce_partials_kernel(const T *__restrict__ part, T *__restrict
   }
 }
 
+// The same for the weight sums and the bias sums of one launch together: blocks [0, w_blocks) own weights,
+// the rest own bias entries.  Four running sums per thread keep the loads independent.
+template <typename T>
+__global__ void reduce_partials_pair_kernel(const T *__restrict__ part_w, T *__restrict__ out_w, long long count_w,
+                                            const T *__restrict__ part_b, T *__restrict__ out_b, long long count_b,
+                                            int slices, long long w_blocks) {
+  __shared__ T red[8][33];
+  const int lane = threadIdx.x & 31, zs = threadIdx.x >> 5;
+  const bool weights = (long long)blockIdx.x < w_blocks;
+  const T *__restrict__ part = weights ? part_w : part_b;
+  const long long count = weights ? count_w : count_b;
+  const long long i = (weights ? blockIdx.x : blockIdx.x - w_blocks) * 32LL + lane;
+  T s0 = 0, s1 = 0, s2 = 0, s3 = 0;
+  if (i < count) {
+    int z = zs;
+    for (; z + 24 < slices; z += 32) {
+      s0 += part[z * count + i];
+      s1 += part[(z + 8) * count + i];
+      s2 += part[(z + 16) * count + i];
+      s3 += part[(z + 24) * count + i];
+    }
+    for (; z < slices; z += 8) s0 += part[z * count + i];
+  }
+  red[zs][lane] = (s0 + s1) + (s2 + s3);
+  __syncthreads();
+  if (zs == 0 && i < count) {
+    T t = 0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += red[k][lane];
+    (weights ? out_w : out_b)[i] = t;
+  }
+}
+
 bool plan_gradw(const GradWProblem<float> &p, GradWTiling &t, int &RM, int &RN) {
   if (p.Dy != 1 || p.Ay != 1 || p.noy < 16) return false;
   if (!(p.nky >= 1 && p.nky <= 5)) return false;
@@ -812,15 +845,10 @@ int launch_gradw<float>(const GradWProblem<float> &p, void *workspace, size_t wo
       int rc = launch_gradw_rows(p, pw, pb, &slices, stream);
       if (rc != MELLIN_ERR_UNSUPPORTED) {
         if (rc) return rc;
-        reduce_partials_kernel<float><<<(unsigned)((gw_count + 31) / 32), 256, 0, stream>>>(pw, p.gw, gw_count, slices,
-                                                                                           gw_count);
-        rc = check_launch("reduce_partials_kernel");
-        if (rc) return rc;
-        if (p.gb != nullptr) {
-          reduce_partials_kernel<float><<<(unsigned)ceil_div(p.A, 32), 256, 0, stream>>>(pb, p.gb, p.A, slices, p.A);
-          rc = check_launch("reduce_partials_kernel(bias)");
-        }
-        return rc;
+        const long long w_blocks = (gw_count + 31) / 32, b_blocks = p.gb != nullptr ? ceil_div(p.A, 32) : 0;
+        reduce_partials_pair_kernel<float><<<(unsigned)(w_blocks + b_blocks), 256, 0, stream>>>(
+            pw, p.gw, gw_count, pb, p.gb, p.A, slices, w_blocks);
+        return check_launch("reduce_partials_pair_kernel");
       }
     }
   }
