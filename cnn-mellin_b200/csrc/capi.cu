@@ -128,6 +128,12 @@ int dispatch_direct(const DirectProblem<float> &p, void *workspace, size_t works
     const int rc = dispatch_direct(plain, workspace, workspace_bytes, stream);
     return rc ? rc : launch_mask_relu(p, stream);
   }
+  if (p.B <= 4 && p.A >= 16 && !p.accumulate && tensor_cores_enabled() && workspace != nullptr) {
+    // a handful of input channels (a first layer): taps folded into the reduction, operand A in tensor memory,
+    // output tiles written by TMA stores
+    const int rc = launch_tc_few_in(p, workspace, workspace_bytes, stream);
+    if (rc != MELLIN_ERR_UNSUPPORTED) return rc;
+  }
   if (p.A <= 4) {
     // a handful of output channels: by source row on the tensor cores (each row of the reduced tensor
     // fetched once, partial planes in the workspace) when covered, else the row-streaming CUDA-core kernel
@@ -781,6 +787,9 @@ int mellin_device_status(int *code) {
   if (rc) return rc;
   rc = tc_scatter_take_error(&rows_code);
   if (rc == MELLIN_OK && *code == 0 && rows_code != 0) *code = 400 + rows_code;
+  if (rc) return rc;
+  rc = tc_few_in_take_error(&rows_code);
+  if (rc == MELLIN_OK && *code == 0 && rows_code != 0) *code = 500 + rows_code;
   return rc;
 }
 int mellin_selftest_unarmed_wait(void *stream) { return launch_unarmed_wait(static_cast<cudaStream_t>(stream)); }
@@ -808,12 +817,21 @@ size_t direct_workspace_query(const Geometry2D &q, bool input_gradient) {
   p.Dy = input_gradient ? (int)q.sy : (int)q.uy;
   p.table.max_row = (int)q.nfx;  // upper bound: one entry per kernel tap
   size_t rows = p.A <= 4 ? direct_rows_workspace_bytes(p) : 0;
-  if (p.A <= 4 && q.nfx <= 16 && q.nfx > 0) {
-    // the by-source-row kernel keeps one partial plane per table entry: count them
-    p.table_by_in.num_entries =
-        (int64_t)enumerate_triples(Relation::Corr, q.nfx, q.ngx, q.nhx, q.sx, q.dx, q.px, q.ux).size();
-    p.table_by_in.max_row = (int)q.nfx;
-    rows = std::max(rows, tc_scatter_workspace_bytes(p));
+  if ((p.A <= 4 || p.B <= 4) && q.nfx <= 16 && q.nfx > 0) {
+    // the first-layer tensor-core kernels size their scratch by the number of table entries: count them
+    const int64_t triples = (int64_t)enumerate_triples(Relation::Corr, q.nfx, q.ngx, q.nhx, q.sx, q.dx, q.px, q.ux).size();
+    if (p.A <= 4) {
+      p.table_by_in.num_entries = triples;
+      p.table_by_in.max_row = (int)q.nfx;
+      rows = std::max(rows, tc_scatter_workspace_bytes(p));
+    }
+    if (p.B <= 4) {
+      p.table.num_entries = triples;
+      DirectProblem<float> dense = p;  // the query describes dense, aligned tensors
+      dense.in_sb = (long long)p.nix * p.niy, dense.in_sn = (long long)p.B * p.nix * p.niy;
+      dense.out_sa = (long long)p.nox * p.noy, dense.out_sn = (long long)p.A * p.nox * p.noy;
+      rows = std::max(rows, tc_few_in_workspace_bytes(dense));
+    }
   }
   // the query describes dense tensors
   p.in_sb = (long long)p.nix * p.niy, p.in_sn = (long long)p.B * p.nix * p.niy;

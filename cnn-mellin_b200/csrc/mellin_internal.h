@@ -131,6 +131,10 @@ size_t direct_tc_workspace_bytes(const DirectProblem<float> &p);
 int launch_direct_tc(const DirectProblem<float> &p, void *workspace, size_t workspace_bytes, cudaStream_t stream);
 int tc_take_error(int *code);
 int direct_rows_take_error(int *code);
+// few-input-channel forward on tensor cores (tc_few_in.cu)
+size_t tc_few_in_workspace_bytes(const DirectProblem<float> &p);
+int launch_tc_few_in(const DirectProblem<float> &p, void *workspace, size_t workspace_bytes, cudaStream_t stream);
+int tc_few_in_take_error(int *code);
 // few-output-channel operator walked by source row on tensor cores (tc_scatter.cu); needs p.table_by_in
 size_t tc_scatter_workspace_bytes(const DirectProblem<float> &p);
 int launch_tc_scatter(const DirectProblem<float> &p, void *workspace, size_t workspace_bytes, cudaStream_t stream);
