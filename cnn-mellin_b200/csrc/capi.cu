@@ -790,6 +790,9 @@ int mellin_device_status(int *code) {
   if (rc) return rc;
   rc = tc_few_in_take_error(&rows_code);
   if (rc == MELLIN_OK && *code == 0 && rows_code != 0) *code = 500 + rows_code;
+  if (rc) return rc;
+  rc = tc_gradw_few_in_take_error(&rows_code);
+  if (rc == MELLIN_OK && *code == 0 && rows_code != 0) *code = 600 + rows_code;
   return rc;
 }
 int mellin_selftest_unarmed_wait(void *stream) { return launch_unarmed_wait(static_cast<cudaStream_t>(stream)); }

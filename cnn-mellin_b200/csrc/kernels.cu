@@ -814,7 +814,8 @@ int launch_direct<double>(const DirectProblem<double> &p, cudaStream_t stream) {
 
 template <>
 size_t gradw_workspace_bytes<float>(const GradWProblem<float> &p) {
-  const size_t rows = std::max(std::max(gradw_rows_workspace_floats(p, nullptr), gradw_tc_workspace_floats(p, nullptr)) * sizeof(float),
+  const size_t rows = std::max(std::max(std::max(gradw_rows_workspace_floats(p, nullptr), tc_gradw_few_in_workspace_floats(p)),
+                                        gradw_tc_workspace_floats(p, nullptr)) * sizeof(float),
                                std::max(gradw_batch_inner_workspace_bytes(p), gradw_repitch_workspace_bytes(p)));
   GradWTiling t;
   int RM = 0, RN = 0;
@@ -831,6 +832,11 @@ template <>
 int launch_gradw<float>(const GradWProblem<float> &p, void *workspace, size_t workspace_bytes,
                         cudaStream_t stream) {
   const long long gw_count = (long long)p.A * p.B * p.nkx * p.nky;
+  if (tensor_cores_enabled() && p.B <= 4) {
+    // layers with few input channels, on the tensor cores: grad_y read once, operand A in tensor memory
+    const int rc = launch_tc_gradw_few_in(p, workspace, workspace_bytes, stream);
+    if (rc != MELLIN_ERR_UNSUPPORTED) return rc;
+  }
   {
     // layers with few input channels: the kernel that reads grad_y once
     size_t rows_bias_off = 0;

@@ -169,6 +169,11 @@ int set_tensor_cores(int enable);
 template <typename T> size_t gradw_workspace_bytes(const GradWProblem<T> &p);
 template <typename T>
 int launch_gradw(const GradWProblem<T> &p, void *workspace, size_t workspace_bytes, cudaStream_t stream);
+// few-input-channel weight gradient on tensor cores (tc_gradw_few_in.cu): scratch in floats (0 = not covered),
+// partial sums and their reduction
+size_t tc_gradw_few_in_workspace_floats(const GradWProblem<float> &p);
+int launch_tc_gradw_few_in(const GradWProblem<float> &p, void *workspace, size_t workspace_bytes, cudaStream_t stream);
+int tc_gradw_few_in_take_error(int *code);
 // few-input-channel weight gradient (gradw_rows.cu): partial-sum scratch in floats
 // (0 = not covered) and the launch that fills it
 size_t gradw_rows_workspace_floats(const GradWProblem<float> &p, size_t *bias_offset);

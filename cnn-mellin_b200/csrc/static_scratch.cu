@@ -141,7 +141,10 @@ extern "C" int mellin_mcorrlcorr_grad_weight_noalloc_f32(const float *x, const f
   p.nkx = (int)nfx, p.nky = (int)nfy, p.nix = (int)ngx, p.niy = (int)ngy, p.nox = (int)nhx, p.noy = (int)nhy;
   p.Ay = (int)sy, p.By = (int)dy, p.Cy = -(int)py, p.Dy = (int)uy;
   // size check first: nothing is touched when the geometry does not fit
-  const size_t need = gradw_workspace_bytes<float>(p);
+  // (the row-streaming kernel's need where it covers the problem: a faster kernel that wants more than the built-in
+  // scratch holds simply declines, and the launch below falls through to this one)
+  const size_t rows_need = gradw_rows_workspace_floats(p, nullptr) * sizeof(float);
+  const size_t need = rows_need > 0 ? rows_need : gradw_workspace_bytes<float>(p);
   if (need > kScratchBytes)
     return fail(MELLIN_ERR_WORKSPACE, std::string(who) + ": the partial sums of this geometry need " + std::to_string(need) +
                                           " bytes, above the " + std::to_string(kScratchBytes) +
