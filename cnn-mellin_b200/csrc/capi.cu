@@ -111,6 +111,10 @@ int launch_mask_relu(const DirectProblem<T> &p, cudaStream_t stream) {
 int dispatch_direct(const DirectProblem<float> &p, void *workspace, size_t workspace_bytes, cudaStream_t stream) {
   if (p.lens != nullptr || p.relu || p.drop_threshold) {
     // fused length mask / ReLU / dropout: the tensor-core kernel that carries it, else the plain operator and one more pass
+    if (p.B <= 4 && p.A >= 16 && !p.accumulate && tensor_cores_enabled() && workspace != nullptr) {
+      const int rc = launch_tc_few_in(p, workspace, workspace_bytes, stream);
+      if (rc != MELLIN_ERR_UNSUPPORTED) return rc;
+    }
     if (p.lens != nullptr && !p.accumulate && tensor_cores_enabled() && workspace != nullptr && p.A > 4) {
       const size_t need = direct_tc_workspace_bytes_masked(p);
       if (need > 0 && workspace_bytes >= need) {

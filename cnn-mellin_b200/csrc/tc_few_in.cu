@@ -18,6 +18,8 @@
 //           by a small kernel, fetched per item with one bulk copy
 //   MMAs  : 3 (lo*hi, hi*lo, hi*hi) per 8 terms of K, issued by one elected lane of a converged warp
 //   bias  : one more term of K -- A holds the constant 1 there, B the bias -- so the epilogue adds nothing
+//   fused : the models' length mask, ReLU and dropout (a hash of the element's offset) are applied on the way out;
+//           tiles that start past their utterance's length are not computed at all (zeros are stored)
 //   out   : the epilogue warps move the accumulator tile from TMEM to shared memory as
 //           [channel][position] and ONE TMA store writes the 64 x 128 box (clipped at the tensor's
 //           edges); two staging tiles, so a store runs under the next item's work
@@ -109,6 +111,13 @@ struct FiParams {
   int lead, ws0;           // box start = tile start + ws0 - lead (a multiple of 4); tap k of position m reads staged m + k + lead
   int k8_max, k16_max;     // longest reduction of the launch, rounded to 8 / 16
   int raw_stages;
+  // fused epilogue: out = (oy < lens[n] * len_scale + len_offset) ? dropout(act(value)) : 0; tiles wholly past the
+  // bound are not computed at all
+  const int *lens;
+  int len_scale, len_offset, relu;
+  unsigned drop_threshold, drop_seed;
+  float drop_scale;
+  long long out_sn, out_sa;  // element strides of out (the dropout mask is a hash of the element's offset)
   int total;               // items
   int num_entries;
   uint32_t b_stage_bytes;  // 512 * k8_max
@@ -118,6 +127,11 @@ __device__ __forceinline__ float tf32_hi(float x) { return __uint_as_float(__flo
 __device__ __forceinline__ void raise_timeout(Control *ctl, int code) {
   atomicCAS(&g_tc_few_in_error, 0, code);
   ctl->abort = 1;
+}
+// first position of utterance n that the length mask zeroes (no mask: past every tile)
+template <bool FUSED>
+__device__ __forceinline__ int mask_bound(const FiParams &p, int n) {
+  return (FUSED && p.lens != nullptr) ? p.lens[n] * p.len_scale + p.len_offset : 0x7fffffff;
 }
 
 // Items (n, y tile, channel tile, ox) in round-robin order over the blocks, rows varying fastest; advanced
@@ -206,7 +220,7 @@ __device__ __forceinline__ void convert_chunks(const float *raw, int ne, uint32_
   }
 }
 
-template <int NB, int NKY>
+template <int NB, int NKY, bool FUSED>
 __global__ void __launch_bounds__(kThreads, 1)
 tc_few_in_kernel(const FiParams p, const __grid_constant__ CUtensorMap in_map, const __grid_constant__ CUtensorMap out_map) {
   constexpr int BK = NB * NKY;
@@ -256,35 +270,61 @@ tc_few_in_kernel(const FiParams p, const __grid_constant__ CUtensorMap in_map, c
     // ===================== epilogue: TMEM -> [channel][position] staging tile -> one TMA store =====================
     const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
     const int m = warp * 32 + lane;
-    int j = 0;
+    const float floor_ = p.relu ? 0.f : -3.0e38f;
+    int j = 0, jt = 0;  // items; items that were computed (the others lie past their utterance's length: zeros)
     PROF_BEGIN();
     for (ItemIter it(p); it.id < p.total; it.next(p)) {
-      const int buf = j & 1;
+      const int buf = j & 1, acc = jt & 1;
       const uint32_t par = (uint32_t)((j >> 1) & 1);
+      const int bound = mask_bound<FUSED>(p, it.n);
+      const bool dead = it.yt * kTM >= bound;
       if (tid == 0) {
         tc::bulk_wait_group_read<1>();  // the store that read this staging tile two items ago has finished reading
         tc::mbar_arrive(&ctl->out_free[buf]);
       }
       PROF_WAIT_START();
-      const bool ok = tc::mbar_wait(&ctl->out_free[buf], par, kSpinLimit) && tc::mbar_wait(&ctl->acc_full[buf], par, kSpinLimit);
+      bool ok = tc::mbar_wait(&ctl->out_free[buf], par, kSpinLimit);
+      if (!dead) ok = ok && tc::mbar_wait(&ctl->acc_full[acc], (uint32_t)((jt >> 1) & 1), kSpinLimit);
       PROF_WAIT_END();
       if (!__all_sync(0xffffffffu, ok)) {
         raise_timeout(ctl, 4);
         break;
       }
-      tc::tc_fence_after_sync();
       float *stage = reinterpret_cast<float *>(out_base + (size_t)buf * kOutBytes) + m;
-      uint32_t v[kNP / 16][16];
+      if (dead) {
 #pragma unroll
-      for (int g = 0; g < kNP / 16; ++g) tc::tmem_ld16(tmem_base + lane_base + (uint32_t)(buf * kNP + 16 * g), v[g]);
-      tc::tmem_ld_wait();
-      // the tile is in registers: the MMAs of the item after next may overwrite it
-      tc::tc_fence_before_sync();
-      tc::mbar_arrive(&ctl->acc_empty[buf]);
+        for (int c = 0; c < kNP; ++c) stage[c * kTM] = 0.f;
+      } else {
+        tc::tc_fence_after_sync();
+        uint32_t v[kNP / 16][16];
 #pragma unroll
-      for (int g = 0; g < kNP / 16; ++g)
+        for (int g = 0; g < kNP / 16; ++g) tc::tmem_ld16(tmem_base + lane_base + (uint32_t)(acc * kNP + 16 * g), v[g]);
+        tc::tmem_ld_wait();
+        // the tile is in registers: the MMAs of the item after next may overwrite it
+        tc::tc_fence_before_sync();
+        tc::mbar_arrive(&ctl->acc_empty[acc]);
+        if (!FUSED) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) stage[(16 * g + i) * kTM] = __uint_as_float(v[g][i]);
+          for (int g = 0; g < kNP / 16; ++g)
+#pragma unroll
+            for (int i = 0; i < 16; ++i) stage[(16 * g + i) * kTM] = __uint_as_float(v[g][i]);
+        } else {
+          const int oy = it.yt * kTM + m;
+          const float keep = oy < bound ? 1.f : 0.f;
+          const unsigned long long off0 = (unsigned long long)(it.n * p.out_sn + (long long)(it.at * kNP) * p.out_sa +
+                                                               (long long)it.ox * p.noy + oy);
+#pragma unroll
+          for (int g = 0; g < kNP / 16; ++g)
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float scale = (p.drop_threshold != 0u &&
+                                   dropout_hash(p.drop_seed, off0 + (unsigned long long)((16 * g + i) * p.out_sa)) < p.drop_threshold)
+                                      ? 0.f
+                                      : p.drop_scale;
+              stage[(16 * g + i) * kTM] = fmaxf(__uint_as_float(v[g][i]), floor_) * keep * scale;
+            }
+        }
+      }
       tc::fence_proxy_async();  // the staging tile was written through the generic proxy; the store reads it through the async one
       tc::mbar_arrive(&ctl->out_full[buf]);
       if (tid == 0) {
@@ -297,6 +337,7 @@ tc_few_in_kernel(const FiParams p, const __grid_constant__ CUtensorMap in_map, c
       }
       __syncwarp();
       ++j;
+      jt += dead ? 0 : 1;
     }
     if (warp == 1) { PROF_END(0); }
     if (tid == 0) tc::bulk_wait_group_all();
@@ -310,6 +351,7 @@ tc_few_in_kernel(const FiParams p, const __grid_constant__ CUtensorMap in_map, c
     bool failed = false;
     PROF_BEGIN();
     for (ItemIter it(p); it.id < p.total && !failed; it.next(p)) {
+      if (it.yt * kTM >= mask_bound<FUSED>(p, it.n)) continue;  // past the utterance's length: the epilogue writes zeros
       const int ne = rp[it.ox + 1] - rp[it.ox];
       const int r = st % p.raw_stages, s = st % kOpStages;
       PROF_WAIT_START();
@@ -344,6 +386,7 @@ tc_few_in_kernel(const FiParams p, const __grid_constant__ CUtensorMap in_map, c
       bool failed = false;
       PROF_BEGIN();
       for (ItemIter it(p); it.id < p.total && !failed; it.next(p)) {
+        if (it.yt * kTM >= mask_bound<FUSED>(p, it.n)) continue;
         const int e0 = rp[it.ox], ne = rp[it.ox + 1] - e0;
         const int r = st % p.raw_stages;
         PROF_WAIT_START();
@@ -370,6 +413,7 @@ tc_few_in_kernel(const FiParams p, const __grid_constant__ CUtensorMap in_map, c
       int st = 0;
       bool failed = false;
       for (ItemIter it(p); it.id < p.total && !failed; it.next(p)) {
+        if (it.yt * kTM >= mask_bound<FUSED>(p, it.n)) continue;
         const int K = (rp[it.ox + 1] - rp[it.ox]) * BK + 1;  // + the bias term
         const int s = st % kBStages;
         if (!tc::mbar_wait(&ctl->b_empty[s], (uint32_t)(((st / kBStages) & 1) ^ 1), kSpinLimit)) {
@@ -398,6 +442,7 @@ tc_few_in_kernel(const FiParams p, const __grid_constant__ CUtensorMap in_map, c
     bool failed = false;
     PROF_BEGIN();
     for (ItemIter it(p); it.id < p.total && !failed; it.next(p)) {
+      if ((int)tc::uniform((uint32_t)(it.yt * kTM >= mask_bound<FUSED>(p, it.n)))) continue;
       const int K = (int)tc::uniform((uint32_t)(rp[it.ox + 1] - rp[it.ox])) * BK + 1;  // + the bias term
       const int ksteps = (K + 7) >> 3;
       const int buf = st & 1, s = st % kOpStages, sb = st % kBStages;
@@ -456,7 +501,6 @@ struct FiPlan {
 // Needs p.table.num_entries and .max_row (upper bounds will do for a workspace query).
 bool plan_tc_few_in(const DirectProblem<float> &p, FiPlan &plan) {
   if (p.Dy != 1 || p.Ay != 1 || p.accumulate) return false;
-  if (p.lens != nullptr || p.relu || p.drop_threshold) return false;
   if (p.B < 1 || p.B > kBoxChannels || p.A < 16 || p.A > kMaxA || p.nky < 1 || p.nky > 3) return false;
   if (p.nky > 1 && p.By != 1 && p.By != -1) return false;
   if (p.nkx < 1 || p.noy < 64 || p.nox < 1 || p.nox > kMaxRows || p.N < 1 || p.nix < 1) return false;
@@ -483,6 +527,9 @@ bool plan_tc_few_in(const DirectProblem<float> &p, FiPlan &plan) {
   if (total >= (1LL << 30)) return false;
   q.total = (int)total;
   q.num_entries = (int)p.table.num_entries;
+  q.lens = p.lens, q.len_scale = p.len_scale, q.len_offset = p.len_offset, q.relu = p.relu;
+  q.drop_threshold = p.drop_threshold, q.drop_seed = p.drop_seed, q.drop_scale = p.drop_scale;
+  q.out_sn = p.out_sn, q.out_sa = p.out_sa;
   q.b_stage_bytes = 512u * (uint32_t)q.k8_max;
   for (q.raw_stages = kMaxRawStages; q.raw_stages >= 2; --q.raw_stages) {
     plan.smem = kHeaderBytes + (size_t)q.raw_stages * kRawBytes + (size_t)kBStages * q.b_stage_bytes + 2 * kOutBytes;
@@ -528,7 +575,13 @@ bool make_map(CUtensorMap *map, const float *base, int inner, int rows, int batc
 template <int NB>
 int launch_for_b(const FiPlan &plan, const CUtensorMap &in_map, const CUtensorMap &out_map, cudaStream_t stream) {
   const FiParams &q = plan.params;
-  auto kernel = q.nky == 1 ? tc_few_in_kernel<NB, 1> : q.nky == 2 ? tc_few_in_kernel<NB, 2> : tc_few_in_kernel<NB, 3>;
+  const bool fused = q.lens != nullptr || q.relu || q.drop_threshold != 0u;
+  auto kernel = fused ? (q.nky == 1   ? tc_few_in_kernel<NB, 1, true>
+                         : q.nky == 2 ? tc_few_in_kernel<NB, 2, true>
+                                      : tc_few_in_kernel<NB, 3, true>)
+                      : (q.nky == 1   ? tc_few_in_kernel<NB, 1, false>
+                         : q.nky == 2 ? tc_few_in_kernel<NB, 2, false>
+                                      : tc_few_in_kernel<NB, 3, false>);
   cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem);
   if (err != cudaSuccess) return fail(MELLIN_ERR_LAUNCH, std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(err));
   kernel<<<plan.blocks, kThreads, plan.smem, stream>>>(q, in_map, out_map);
