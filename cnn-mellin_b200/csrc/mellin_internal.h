@@ -14,6 +14,21 @@ void set_error(const std::string &msg);
 int fail(int code, const std::string &msg);  // records msg, returns code
 void count_launch(int n = 1);
 
+// Launches `kernel` so that it may begin while the kernel before it in the stream still runs (programmatic
+// dependent launch): its blocks are scheduled as that kernel's blocks make room, run their prologue, and wait
+// in tc::grid_dependency_wait() for that kernel to complete.  Only for kernels that make that call.
+template <typename... KernelArgs, typename... Args>
+cudaError_t launch_after_predecessor(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem,
+                                     cudaStream_t stream, Args &&...args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr, cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, KernelArgs(args)...);
+}
+
 // ---- device-resident index maps ------------------------------------------------
 struct DeviceTable {
   const int32_t *row_ptr = nullptr;

@@ -163,6 +163,7 @@ struct ItemIter {
 // W[a, b, kx(entry), ky(tap)] (taps in increasing input offset), split into TF32 hi / lo parts, in the
 // K-major operand layout (4-term chunks of 64 rows x 16 bytes); unused terms and channels are zero.
 __global__ void __launch_bounds__(256) pack_few_in_b_kernel(const FiParams p) {
+  tc::launch_dependents();  // the main kernel may set itself up meanwhile; it waits for this grid before reading
   const int ox = blockIdx.y / p.a_tiles, at = blockIdx.y % p.a_tiles;
   const int e0 = p.row_ptr[ox];
   const int K = (p.row_ptr[ox + 1] - e0) * p.BK;  // then one more term: the bias (A holds a 1 there)
@@ -259,6 +260,7 @@ tc_few_in_kernel(const FiParams p, const __grid_constant__ CUtensorMap in_map, c
     tc::tmem_alloc(&ctl->tmem_base, kTmemCols);
     tc::tmem_relinquish();
   }
+  tc::grid_dependency_wait();  // the weight operands come from the kernel before
   tc::tc_fence_before_sync();
   __syncthreads();
   tc::tc_fence_after_sync();
@@ -584,8 +586,8 @@ int launch_for_b(const FiPlan &plan, const CUtensorMap &in_map, const CUtensorMa
                                       : tc_few_in_kernel<NB, 3, false>);
   cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem);
   if (err != cudaSuccess) return fail(MELLIN_ERR_LAUNCH, std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(err));
-  kernel<<<plan.blocks, kThreads, plan.smem, stream>>>(q, in_map, out_map);
-  err = cudaGetLastError();
+  err = launch_after_predecessor(kernel, dim3(plan.blocks), dim3(kThreads), plan.smem, stream, q, in_map, out_map);
+  if (err == cudaSuccess) err = cudaGetLastError();
   if (err != cudaSuccess) return fail(MELLIN_ERR_LAUNCH, std::string("tc_few_in_kernel: ") + cudaGetErrorString(err));
   count_launch();
   return MELLIN_OK;

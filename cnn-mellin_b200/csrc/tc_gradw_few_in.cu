@@ -216,6 +216,7 @@ tc_gradw_few_in_kernel(const GfParams p, const __grid_constant__ CUtensorMap go_
     tc::tmem_alloc(&ctl->tmem_base, kTmemCols);
     tc::tmem_relinquish();
   }
+  tc::launch_dependents();  // the reduction may be scheduled; it waits for this grid before reading the partial sums
   tc::fence_proxy_async();  // the zero fill above, before the tensor core reads those rows
   tc::tc_fence_before_sync();
   __syncthreads();
@@ -572,6 +573,7 @@ __global__ void __launch_bounds__(kReduceGroups * kCo) tc_gradw_few_in_reduce_ke
   for (int i = threadIdx.x; i < p.num_entries; i += blockDim.x) kx_s[i] = p.entries[i].x;
   __syncthreads();
   for (int b = threadIdx.x; b <= nblocks; b += blockDim.x) first_s[b] = first_item(p, rp_s, b, nblocks);
+  tc::grid_dependency_wait();  // the partial sums come from the kernel before
   __syncthreads();
   const int al = threadIdx.x & (kCo - 1), grp = threadIdx.x >> 6;
   const int weight_blocks = p.B * p.nkx * p.nky * p.a_tiles;
@@ -786,8 +788,9 @@ int launch_tc_gradw_few_in(const GradWProblem<float> &p, void *workspace, size_t
   }
   if (rc) return rc;
   const int reduce_blocks = p.B * p.nkx * p.nky * q.a_tiles + (p.gb != nullptr ? q.a_tiles : 0);
-  tc_gradw_few_in_reduce_kernel<<<(unsigned)reduce_blocks, kReduceGroups * kCo, 0, stream>>>(q, plan.blocks);
-  const cudaError_t err = cudaGetLastError();
+  cudaError_t err = launch_after_predecessor(tc_gradw_few_in_reduce_kernel, dim3((unsigned)reduce_blocks),
+                                             dim3(kReduceGroups * kCo), 0, stream, q, plan.blocks);
+  if (err == cudaSuccess) err = cudaGetLastError();
   if (err != cudaSuccess)
     return fail(MELLIN_ERR_LAUNCH, std::string("tc_gradw_few_in_reduce_kernel: ") + cudaGetErrorString(err));
   count_launch();

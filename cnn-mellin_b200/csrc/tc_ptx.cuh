@@ -26,6 +26,15 @@ __device__ __forceinline__ bool elect_one() {
 }
 __device__ __forceinline__ uint32_t uniform(uint32_t v) { return __shfl_sync(0xffffffffu, v, 0); }
 
+// ---- programmatic dependent launch ------------------------------------------------
+// A kernel launched with the programmatic-stream-serialization attribute may start while the kernel before
+// it in the stream still runs; it must call grid_dependency_wait() before it touches anything that kernel
+// writes (the call returns once that grid has completed and its writes are visible).  The earlier kernel
+// lets its successor start early with launch_dependents(); without the call the successor starts as the
+// earlier grid's blocks exit.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- mbarrier ------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");

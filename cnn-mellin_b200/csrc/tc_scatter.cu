@@ -161,6 +161,7 @@ __device__ __forceinline__ int pad16(int v) { return (v + 15) & ~15; }
 // 256 elements, source row x k-block); one more row of blocks (blockIdx.y = nix * kblocks) finds, for every
 // entry of the by-output-row table, the partial plane that holds its sums.
 __global__ void __launch_bounds__(256) pack_scatter_b_kernel(const TsParams p) {
+  tc::launch_dependents();  // the main kernel may set itself up meanwhile; it waits for this grid before reading
   if ((int)blockIdx.y == p.nix * p.kblocks) {
     const int total = p.row_ptr_out[p.nox];
     for (int e = blockIdx.x * 256 + threadIdx.x; e < total; e += gridDim.x * 256) {
@@ -232,6 +233,8 @@ tc_scatter_kernel(const TsParams p, const __grid_constant__ CUtensorMap in_map) 
     tc::tmem_alloc(&ctl->tmem_base, kTmemCols);  // two accumulator tiles, then the operand A ring
     tc::tmem_relinquish();
   }
+  tc::launch_dependents();      // the plane sum may be scheduled; it waits for this grid before reading
+  tc::grid_dependency_wait();   // the weight operands and the plane index come from the kernel before
   tc::tc_fence_before_sync();
   __syncthreads();
   tc::tc_fence_after_sync();
@@ -507,6 +510,7 @@ gather_planes_kernel(const TsParams p, int vec_store) {
   const int ox = bid % p.nox, n = bid / p.nox;
   const int e0 = p.row_ptr_out[ox];
   const int np = min(p.row_ptr_out[ox + 1] - e0, kMaxEntries);
+  tc::grid_dependency_wait();  // the planes (and, before them, the plane index) come from the kernels before
   if ((int)threadIdx.x < np) pid[threadIdx.x] = p.plane_of[e0 + threadIdx.x];
   __syncthreads();
   const float *__restrict__ base = p.planes + ((size_t)n * p.entries * p.A + a) * p.plane + p.shift;
@@ -665,14 +669,14 @@ int launch_tc_scatter(const DirectProblem<float> &p, void *workspace, size_t wor
   auto kernel = p.nky == 1 ? tc_scatter_kernel<1> : p.nky == 2 ? tc_scatter_kernel<2> : tc_scatter_kernel<3>;
   err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem);
   if (err != cudaSuccess) return fail(MELLIN_ERR_LAUNCH, std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(err));
-  kernel<<<plan.blocks, kThreads, plan.smem, stream>>>(q, in_map);
-  err = cudaGetLastError();
+  err = launch_after_predecessor(kernel, dim3(plan.blocks), dim3(kThreads), plan.smem, stream, q, in_map);
+  if (err == cudaSuccess) err = cudaGetLastError();
   if (err != cudaSuccess) return fail(MELLIN_ERR_LAUNCH, std::string("tc_scatter_kernel: ") + cudaGetErrorString(err));
   count_launch();
   const int vec_store =
       (reinterpret_cast<uintptr_t>(p.out) % 16 == 0 && p.noy % 4 == 0 && p.out_sn % 4 == 0 && p.out_sa % 4 == 0) ? 1 : 0;
-  gather_planes_kernel<<<(unsigned)(p.N * p.nox * p.A), 128, 0, stream>>>(q, vec_store);
-  err = cudaGetLastError();
+  err = launch_after_predecessor(gather_planes_kernel, dim3((unsigned)(p.N * p.nox * p.A)), dim3(128), 0, stream, q, vec_store);
+  if (err == cudaSuccess) err = cudaGetLastError();
   if (err != cudaSuccess) return fail(MELLIN_ERR_LAUNCH, std::string("gather_planes_kernel: ") + cudaGetErrorString(err));
   count_launch();
   return MELLIN_OK;
