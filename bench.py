@@ -456,9 +456,12 @@ def bench_headline(ctx, sampler):
             total += evs[0].elapsed_time(evs[4])
         if n_blocks == 0:
             launches = capi.launch_count() - launches0
-        vals = ctx.max_over_ranks([total / args.steps] + [v / args.steps for v in per])
+        # the block's wall time rides in the same reduction: every rank must take the SAME number of blocks (each
+        # block ends in collectives), so the decision to go on is made on a value all ranks share
+        vals = ctx.max_over_ranks([total / args.steps] + [v / args.steps for v in per] + [(t1 - t0) * 1e3])
+        block_ms = vals.pop()
         blocks.append((t0, t1, vals))
-        device_ms += (t1 - t0) * 1e3
+        device_ms += block_ms
         n_blocks += 1
     order = sorted(range(len(blocks)), key=lambda i: blocks[i][2][0])
     med = blocks[order[len(order) // 2]][2]
@@ -568,8 +571,10 @@ def bench_headline(ctx, sampler):
         download((counter["next_step"] - 1) % 2)  # the last step's gradients
         read_back((counter["next_step"] - 1) % 2)
         ctx.barrier()
-        e2e_device_ms += (time.perf_counter() - t0) * 1e3
-        e2e_blocks.append(ctx.max_over_ranks([e_start.elapsed_time(e_end) / args.steps])[0])
+        # (as above: the wall time that decides whether to go on is the maximum over the ranks)
+        step_ms, wall_ms = ctx.max_over_ranks([e_start.elapsed_time(e_end) / args.steps, (time.perf_counter() - t0) * 1e3])
+        e2e_device_ms += wall_ms
+        e2e_blocks.append(step_ms)
     ms_e2e = statistics.median(e2e_blocks)
     h2d_ms = ctx.max_over_ranks([statistics.median([a.elapsed_time(b_) for a, b_ in h2d_events])])[0]
 
@@ -870,13 +875,23 @@ def bench_incumbent():
 
 
 def run_ours(args):
+    t_start = time.time()
+
+    def note(msg):
+        # progress on stderr (the JSON line is the only thing on stdout): tells where a multi-rank run stands
+        sys.stderr.write("[bench rank %s +%.1fs] %s\n" % (os.environ.get("RANK", "0"), time.time() - t_start, msg))
+        sys.stderr.flush()
+
+    note("starting")
     ctx = Ctx(args)
     rank, world = ctx.rank, ctx.world
     skip = set(args.skip.split(",")) if args.skip else set()
     sampler = ClockSampler(ctx.local_rank)
     if rank == 0:
         sampler.start()
+    note("process group up, headline")
     line = bench_headline(ctx, sampler)
+    note("headline done")
     if args.kernels_only:
         if rank == 0:
             sampler.stop()
@@ -893,10 +908,13 @@ def run_ours(args):
         line["latency_us"] = bench_latency(ctx)
     if "layers" not in skip:
         line["layers"] = bench_layers(ctx)
+    note("latency and layers done, sweep")
     if "sweep" not in skip:
         line["sweep"] = bench_sweep(ctx)
+    note("sweep done, train step")
     if "train" not in skip:
         line["train_step"] = bench_train_step(ctx)
+    note("train step done, peaks")
     ctx.torch.cuda.synchronize()
     time.sleep(2.0)  # let the clocks recover from the blocks above before the burst figures are taken
     peaks = measure_peaks(ctx)
@@ -916,6 +934,7 @@ def run_ours(args):
                 line["gpu_incumbent"] = bench_incumbent()
             line["cpu_baseline"] = cpu_baseline_leg()  # timed on rank 0 of the single-GPU run only
         print(json.dumps(line), flush=True)
+    note("line printed" if rank == 0 else "done")
     if world > 1:
         ctx.dist.barrier()
         ctx.dist.destroy_process_group()

@@ -29,7 +29,7 @@ LAYER = ["mellin_mcorrlcorr_forward", "mellin_mcorrlcorr_forward_masked", "melli
          "mellin_mcorrlcorr_grad_input_masked",
          "mellin_mcorrlcorr_grad_weight", "mellin_mcorrlcorr_grad_weight_masked"]
 MISC = ["mellin_abi_version", "mellin_last_error", "mellin_launch_count", "mellin_clear_tables",
-        "mellin_set_tensor_cores", "mellin_device_status", "mellin_mcorrlcorr_forward_workspace_bytes",
+        "mellin_set_tensor_cores", "mellin_set_dependent_launch", "mellin_device_status", "mellin_mcorrlcorr_forward_workspace_bytes",
         "mellin_mcorrlcorr_grad_input_workspace_bytes", "mellin_mcorrlcorr_grad_weight_noalloc_f32",
         "mellin_mcorrlcorr_grad_weight_workspace_bytes", "mellin_index_map_build",
         "mellin_selftest_unarmed_wait", "mellin_selftest_fma_rate",
@@ -171,6 +171,11 @@ def _geometry(x_shape, w_shape, y_shape, s, d, p, u):
     c_out, _, nfx, nfy = w_shape
     nhx, nhy = y_shape[2:]
     return [_I64(v) for v in (batch, c_in, c_out, nfx, nfy, ngx, ngy, nhx, nhy, sx, sy, dx, dy, px, py, ux, uy)]
+
+
+def set_dependent_launch(enable):
+    """Switch the programmatic dependent launches of the first-layer operators on/off process-wide; returns the previous setting."""
+    return int(lib().mellin_set_dependent_launch(_INT(1 if enable else 0)))
 
 
 def set_tensor_cores(enable):

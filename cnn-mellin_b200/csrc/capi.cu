@@ -773,6 +773,7 @@ int mellin_tc_profile(long long *out) { return mellin::tc_read_prof(out); }
 int mellin_tc_gradw_profile(long long *out) { return mellin::tc_gradw_read_prof(out); }
 #endif
 int mellin_set_tensor_cores(int enable) { return set_tensor_cores(enable); }
+int mellin_set_dependent_launch(int enable) { return set_dependent_launch(enable); }
 int mellin_device_status(int *code) {
   if (code == nullptr) return fail(MELLIN_ERR_BAD_ARGUMENT, "device_status: null pointer");
   int rc = tc_take_error(code);

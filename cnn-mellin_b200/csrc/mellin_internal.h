@@ -14,6 +14,11 @@ void set_error(const std::string &msg);
 int fail(int code, const std::string &msg);  // records msg, returns code
 void count_launch(int n = 1);
 
+// Programmatic dependent launch can be switched off (environment variable MELLIN_DEPENDENT_LAUNCH=0, read once,
+// or mellin_set_dependent_launch): the kernels' waits then return at once and every launch is an ordinary one.
+bool dependent_launch_enabled();
+int set_dependent_launch(int enable);
+
 // Launches `kernel` so that it may begin while the kernel before it in the stream still runs (programmatic
 // dependent launch): its blocks are scheduled as that kernel's blocks make room, run their prologue, and wait
 // in tc::grid_dependency_wait() for that kernel to complete.  Only for kernels that make that call.
@@ -25,7 +30,7 @@ cudaError_t launch_after_predecessor(void (*kernel)(KernelArgs...), dim3 grid, d
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr, cfg.numAttrs = 1;
+  cfg.attrs = attr, cfg.numAttrs = dependent_launch_enabled() ? 1 : 0;  // without it: an ordinary launch
   return cudaLaunchKernelEx(&cfg, kernel, KernelArgs(args)...);
 }
 

@@ -1,4 +1,5 @@
 // Per-device cache of uploaded index maps, error bookkeeping.
+#include <cstdlib>
 #include <map>
 #include <mutex>
 #include <atomic>
@@ -64,6 +65,24 @@ int fail(int code, const std::string &msg) {
 const std::string &last_error() { return g_last_error; }
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 int64_t launch_count() { return g_launches.load(std::memory_order_relaxed); }
+
+namespace {
+std::atomic<int> g_dependent_launch{-1};  // -1: not decided yet (the environment is read on first use)
+}
+bool dependent_launch_enabled() {
+  int v = g_dependent_launch.load(std::memory_order_relaxed);
+  if (v < 0) {
+    const char *env = getenv("MELLIN_DEPENDENT_LAUNCH");
+    v = (env != nullptr && env[0] == '0') ? 0 : 1;
+    g_dependent_launch.store(v, std::memory_order_relaxed);
+  }
+  return v != 0;
+}
+int set_dependent_launch(int enable) {
+  const int before = dependent_launch_enabled() ? 1 : 0;
+  g_dependent_launch.store(enable ? 1 : 0, std::memory_order_relaxed);
+  return before;
+}
 
 bool tensor_cores_enabled() { return g_tensor_cores.load(std::memory_order_relaxed) != 0; }
 int set_tensor_cores(int enable) { return g_tensor_cores.exchange(enable ? 1 : 0); }

@@ -271,6 +271,13 @@ int64_t mellin_launch_count(void);
  * returns the previous setting.  Disabled, every operator runs on CUDA cores. */
 int mellin_set_tensor_cores(int enable);
 
+/* The first-layer operators launch their helper kernels (weight operands before, plane sum / reduction after the
+ * main kernel) programmatically dependent: a kernel's set-up runs under the kernel before it in the stream.  This
+ * switches that off (0) or on (non-zero) process-wide and returns the previous setting; off, every launch is an
+ * ordinary one.  The environment variable MELLIN_DEPENDENT_LAUNCH=0, read on first use, does the same.  No
+ * reference counterpart. */
+int mellin_set_dependent_launch(int enable);
+
 /* Every kernel that waits on a barrier (the tensor-core kernels and the
  * row-streaming first-layer kernels) bounds the wait; if one ever gives up it
  * records a non-zero code on the device instead of hanging, and the results of
