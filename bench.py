@@ -25,7 +25,9 @@ with bucketed gradient all-reduce overlapped with backward), ``layers`` (the
 wide layers of the three-layer stack against measured TF32 / FP32 peaks),
 ``sweep`` (the 1-D Mellin and linear operators at batch 64 x 256 channels x
 16384 samples, batch-sharded over the ranks), ``latency_us`` (the small 1-D
-operator against an empty launch).
+operator against an empty launch), ``prologue`` (log compression + lift in
+front of the first layer as one pass, against the HBM roofline and against the
+stock torch operators; single-GPU runs only).
 
 With ``--impl reference`` the headline step is run by the reference's own CPU
 kernels (``oracle/_ref``, OpenMP over all host cores; the C restatement when
@@ -878,6 +880,72 @@ def bench_incumbent():
     return out
 
 
+def bench_prologue(ctx):
+    """The elementwise layers in front of the first layer (log compression, then the lift along the Mellin axis) as
+    ONE pass: device time on a tensor larger than L2 (512 utterances of the headline layer's input, 201 MB) against
+    the HBM roofline (8 bytes per element forward, 12 backward), and on the headline batch itself with L2 flushed;
+    next to it the reference's formulation (layers.py:8-21,100-101: abs, add, log, arange, pow, mul as stock torch
+    kernels, autograd for the backward) on the same GPU.  No collectives: single-GPU runs only."""
+    import capi as c
+    import layers
+
+    torch, dev = ctx.torch, ctx.dev
+    out = {"what": "y = (t+1)^tau log(eps + |x|) along dim 2; fp32; ms per call, CUDA events, L2 flushed between calls"}
+
+    def ms(fn, iters=10):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        total = 0.0
+        for _ in range(iters):
+            ctx.flush()
+            a, b = ctx.ev(), ctx.ev()
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            total += a.elapsed_time(b)
+        return total / iters
+
+    for name, batch in (("headline_batch", WORKLOAD["batch"]), ("larger_than_l2", 512)):
+        shape = (batch, WORKLOAD["c_in"]) + tuple(WORKLOAD["ng"])
+        x = torch.randn(shape, device=dev)
+        gy = torch.randn(shape, device=dev)
+        pair = layers.LogCompressionLift(dim=2).to(dev)
+        log_tau, log_eps = pair.lift.log_tau.detach(), pair.log_compression.log_eps.detach()
+        y, gx = torch.empty_like(x), torch.empty_like(x)
+        g_tau, g_eps = torch.empty_like(log_tau), torch.empty_like(log_eps)
+        ws = torch.empty(c.lift_compress_workspace_bytes(), dtype=torch.uint8, device=dev)
+        outer, length, inner = batch * shape[1], shape[2], shape[3]
+        fwd = ms(lambda: c.lift_compress(x, log_tau, log_eps, True, outer, length, inner, y))
+        bwd = ms(lambda: c.lift_compress_backward(x, gy, log_tau, log_eps, True, outer, length, inner, gx, g_tau,
+                                                  g_eps, workspace=ws))
+        steps = torch.arange(1, length + 1, device=dev, dtype=torch.float32).view(1, 1, length, 1)
+
+        def stock(xin):
+            return (xin.abs() + log_eps.exp()).log() * steps ** log_tau.exp()
+
+        xr = x.clone().requires_grad_(True)
+        lt, le = log_tau.clone().requires_grad_(True), log_eps.clone().requires_grad_(True)
+
+        def stock_fwd_bwd():
+            yy = (xr.abs() + le.exp()).log() * steps ** lt.exp()
+            yy.backward(gy)
+            xr.grad = None
+
+        stock_f = ms(lambda: stock(x))
+        stock_fb = ms(stock_fwd_bwd)
+        n = x.numel()
+        out[name] = {
+            "shape": list(shape), "forward_ms": fwd, "backward_ms": bwd,
+            "forward_gbs": 8.0 * n / fwd / 1e6, "backward_gbs": 12.0 * n / bwd / 1e6,
+            "stock_torch_forward_ms": stock_f, "stock_torch_forward_backward_ms": stock_fb,
+            "launches": {"forward": 1, "backward": 2},
+        }
+        del x, gy, y, gx, xr
+    return out
+
+
 def run_ours(args):
     t_start = time.time()
 
@@ -918,6 +986,11 @@ def run_ours(args):
     note("sweep done, train step")
     if "train" not in skip:
         line["train_step"] = bench_train_step(ctx)
+    if "prologue" not in skip and world == 1:
+        try:
+            line["prologue"] = bench_prologue(ctx)
+        except Exception as e:  # an optional block: the line is printed without it
+            line["prologue"] = {"error": "%s: %s" % (type(e).__name__, e)}
     note("train step done, peaks")
     ctx.torch.cuda.synchronize()
     time.sleep(2.0)  # let the clocks recover from the blocks above before the burst figures are taken
@@ -955,7 +1028,7 @@ def main():
                          "not for bench lines")
     ap.add_argument("--kernels-only", action="store_true",
                     help="one timed block of the headline kernels only (profiler captures)")
-    ap.add_argument("--skip", default="", help="comma-separated blocks to leave out: train, layers, sweep, latency, incumbent")
+    ap.add_argument("--skip", default="", help="comma-separated blocks to leave out: train, layers, sweep, latency, prologue, incumbent")
     ap.add_argument("--engine", default="tensor_cores", choices=["tensor_cores", "cuda_cores"],
                     help="with --kernels-only: cuda_cores switches the tcgen05 kernels off (profiler captures of the "
                          "CUDA-core kernels); bench lines always run the default engine")

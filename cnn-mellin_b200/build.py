@@ -21,7 +21,7 @@ INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 CAPI_SO = os.path.join(LIBDIR, "libmellin_b200.so")
 TORCH_SO = os.path.join(LIBDIR, "mellin_torch.so")
 
-CAPI_SOURCES = ["capi.cu", "kernels.cu", "tc_direct.cu", "tc_direct_taps.cu", "tc_direct_masked.cu", "tc_gradw.cu", "batch_inner.cu", "gradw_rows.cu", "direct_rows.cu", "tc_scatter.cu", "tc_few_in.cu", "tc_gradw_few_in.cu", "few_in_rows.cu", "static_scratch.cu", "table_cache.cu", "peaks.cu", "index_map.cpp"]
+CAPI_SOURCES = ["capi.cu", "kernels.cu", "tc_direct.cu", "tc_direct_taps.cu", "tc_direct_masked.cu", "tc_gradw.cu", "batch_inner.cu", "gradw_rows.cu", "direct_rows.cu", "tc_scatter.cu", "tc_few_in.cu", "tc_gradw_few_in.cu", "few_in_rows.cu", "prologue.cu", "static_scratch.cu", "table_cache.cu", "peaks.cu", "index_map.cpp"]
 CAPI_HEADERS = ["mellin_internal.h", "index_map.h", "tc_ptx.cuh", "tuning_hooks.h"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -35,13 +35,14 @@ MISC = ["mellin_abi_version", "mellin_last_error", "mellin_launch_count", "melli
         "mellin_selftest_unarmed_wait", "mellin_selftest_fma_rate",
         "mellin_mcorrlcorr_forward_f16", "mellin_mcorrlcorr_grad_input_f16", "mellin_mcorrlcorr_grad_weight_f16",
         "mellin_mcorrlcorr_forward_workspace_bytes_f16", "mellin_mcorrlcorr_grad_input_workspace_bytes_f16",
-        "mellin_mcorrlcorr_grad_weight_workspace_bytes_f16"]
+        "mellin_mcorrlcorr_grad_weight_workspace_bytes_f16", "mellin_lift_compress_workspace_bytes"]
+PROLOGUE = ["mellin_lift_compress", "mellin_lift_compress_backward"]
 
 
 def exported_symbols():
     """Every symbol the header declares."""
     names = list(SIZE_FUNCTIONS) + MISC
-    for base in OP1D + OP2D + COL1D + COL2D + LAYER:
+    for base in OP1D + OP2D + COL1D + COL2D + LAYER + PROLOGUE:
         names += [base + "_f32", base + "_f64"]
     return names
 
@@ -72,6 +73,7 @@ def lib():
             for sfx in ("", "_f16"):
                 fn = getattr(_lib, "mellin_mcorrlcorr_%s_workspace_bytes%s" % (name, sfx))
                 fn.restype, fn.argtypes = ctypes.c_size_t, [_I64] * 17
+        _lib.mellin_lift_compress_workspace_bytes.restype = ctypes.c_size_t
     return _lib
 
 
@@ -265,6 +267,31 @@ def relu_dropout_backward(grad_y, y, scale, grad_pre):
     fn = getattr(lib(), "mellin_relu_dropout_backward" + _sfx(y))
     _check(fn(_p(grad_y), _p(y), ctypes.c_double(scale), _p(grad_pre), _I64(y.numel()), _stream()))
     return grad_pre
+
+
+def lift_compress_workspace_bytes():
+    return int(lib().mellin_lift_compress_workspace_bytes())
+
+
+def lift_compress(x, tau, eps, log_domain, outer, length, inner, y):
+    """y = (t + 1)^tau * log(eps + |x|) on x viewed as [outer][length][inner]; tau / eps: device scalars or None."""
+    fn = getattr(lib(), "mellin_lift_compress" + _sfx(x))
+    _check(fn(_p(x), _p(tau), _p(eps), _INT(1 if log_domain else 0), _I64(outer), _I64(length), _I64(inner), _p(y),
+              _stream()))
+    return y
+
+
+def lift_compress_backward(x, grad_y, tau, eps, log_domain, outer, length, inner, grad_x, grad_tau, grad_eps,
+                           workspace=None):
+    import torch
+
+    need = lift_compress_workspace_bytes()
+    if workspace is None:
+        workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
+    fn = getattr(lib(), "mellin_lift_compress_backward" + _sfx(x))
+    _check(fn(_p(x), _p(grad_y), _p(tau), _p(eps), _INT(1 if log_domain else 0), _I64(outer), _I64(length), _I64(inner),
+              _p(grad_x), _p(grad_tau), _p(grad_eps), _p(workspace), ctypes.c_size_t(workspace.numel()), _stream()))
+    return grad_x
 
 
 def grad_input(w, grad_y, grad_x, s, d, p, u, workspace=None):

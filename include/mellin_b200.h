@@ -261,6 +261,31 @@ int mellin_mcorrlcorr_grad_input_f16(const void *w, const void *grad_y, MELLIN_L
 int mellin_mcorrlcorr_grad_weight_f16(const void *x, const void *grad_y, MELLIN_LAYER_GEOMETRY, void *grad_w,
                                       void *grad_b, void *workspace, size_t workspace_bytes, void *stream);
 
+/* ---- the elementwise layers in front of the first Mellin layer ----------------
+ * Replace layers.py:8-21 (dilation_lift / DilationLift) and layers.py:100-101 (LogCompression.forward) of the
+ * reference, which models.py:413-417 applies one after the other, by ONE pass over the tensor:
+ *     y[o, t, i] = (t + 1)^tau * log(eps + |x[o, t, i]|)
+ * on a contiguous tensor viewed as [outer][len][inner] with `len` the lifted axis.  tau and eps are DEVICE scalars
+ * (the layers' parameters); either may be NULL, which leaves that step out (tau NULL: log compression alone; eps
+ * NULL: the lift alone).  With log_domain != 0 they hold log(tau) / log(eps), as the reference's modules store
+ * them (log_tau, log_eps), and the parameter gradients are those of the logarithms.
+ *
+ * Backward: grad_x as above, grad_tau / grad_eps (device scalars, either may be NULL) summed in a fixed order,
+ * so that two runs give the same bits.  workspace: mellin_lift_compress_workspace_bytes() bytes, 8-byte aligned. */
+size_t mellin_lift_compress_workspace_bytes(void);
+int mellin_lift_compress_f32(const float *x, const float *tau, const float *eps, int log_domain, int64_t outer,
+                             int64_t len, int64_t inner, float *y, void *stream);
+int mellin_lift_compress_f64(const double *x, const double *tau, const double *eps, int log_domain, int64_t outer,
+                             int64_t len, int64_t inner, double *y, void *stream);
+int mellin_lift_compress_backward_f32(const float *x, const float *grad_y, const float *tau, const float *eps,
+                                      int log_domain, int64_t outer, int64_t len, int64_t inner, float *grad_x,
+                                      float *grad_tau, float *grad_eps, void *workspace, size_t workspace_bytes,
+                                      void *stream);
+int mellin_lift_compress_backward_f64(const double *x, const double *grad_y, const double *tau, const double *eps,
+                                      int log_domain, int64_t outer, int64_t len, int64_t inner, double *grad_x,
+                                      double *grad_tau, double *grad_eps, void *workspace, size_t workspace_bytes,
+                                      void *stream);
+
 /* ---- diagnostics ------------------------------------------------------------ */
 
 /* Number of kernels this library has launched from the calling process since
@@ -285,7 +310,9 @@ int mellin_set_dependent_launch(int enable);
  * stores the first code recorded since the last query in *code (0 = healthy;
  * 1..99 tensor-core forward / grad-input, 100.. tensor-core weight gradient,
  * 200.. row-streaming weight gradient, 300.. row-streaming grad-input by
- * output row, 400.. tensor-core grad-input by source row) and clears it. */
+ * output row, 400.. tensor-core grad-input by source row, 500.. tensor-core
+ * first-layer forward, 600.. tensor-core first-layer weight gradient) and
+ * clears it. */
 int mellin_device_status(int *code);
 
 /* Self-test of the bounded waits: launches one thread that waits, with a limit

@@ -101,3 +101,24 @@ def test_pair_counts_of_the_baseline_configurations():
 def test_bad_index_map_arguments():
     with pytest.raises(capi.MellinError):
         capi.index_map("corr", "h", 3, 5, 5, 1, 1, -1, 1)
+
+
+def test_prologue_layers_keep_the_reference_names_and_refuse_the_cpu():
+    """``layers.py``: parameter names of the reference (``lift.log_tau``, ``log_compression.log_eps``), its error for a
+    bad ``dim``, and no CPU path."""
+    import pytest
+    import torch
+
+    import layers
+
+    pair = layers.LogCompressionLift()
+    assert set(pair.state_dict()) == {"log_compression.log_eps", "lift.log_tau"}
+    assert pair.lift.dim == 2 and pair.lift.log_tau.shape == () and pair.log_compression.log_eps.shape == ()
+    assert set(layers.LogCompressionLift(use_lift=False).state_dict()) == {"log_compression.log_eps"}
+    assert "dim=2" in repr(layers.DilationLift())
+    with pytest.raises(RuntimeError, match="-4 not a valid dimension for a tensor if dimension 3"):
+        layers.dilation_lift(torch.zeros(2, 3, 4), torch.tensor(1.0), -4)
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        pair(torch.zeros(2, 3, 4))
+    x = torch.zeros(2, 3)
+    assert layers.LogCompressionLift(False, False)(x) is x

@@ -131,3 +131,48 @@ def test_column_ops_against_reference_extension(oracle):
     np.testing.assert_array_equal(gg, arrays["snd2col.gg"])
     back = oracle.col2snd(arrays["snd2col.cot"], arrays["snd2col.x"].shape[2], m["s"], m["d"], m["p"], m["u"])
     assert helpers.rel_err(back, arrays["snd2col.back"]) <= 1e-6
+
+
+# ---- the elementwise layers in front of the first Mellin layer ------------------------------------------------
+
+
+def _prologue_cases():
+    import os
+
+    data = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "prologue_cases.npz"))
+    tags = sorted({k.rsplit("_", 1)[0] for k in data.files if k.endswith("_meta")})
+    return data, tags
+
+
+def test_prologue_restatement_against_the_reference_layers():
+    """``oracle/prologue_oracle.py`` against values and autograd gradients recorded from the reference's ``layers.py``."""
+    from oracle import prologue_oracle as po
+
+    data, tags = _prologue_cases()
+    assert len(tags) == 18
+    for tag in tags:
+        dim, use_lc, use_lift = (int(v) for v in data[tag + "_meta"])
+        log_tau, log_eps = (float(v) for v in data[tag + "_params"])
+        lt, le = (log_tau if use_lift else None), (log_eps if use_lc else None)
+        x, gy = data[tag + "_x"], data[tag + "_grad_y"]
+        tol = 2e-6 if x.dtype == np.float32 else 1e-13
+        y = po.lift_compress(x, lt, le, dim)
+        assert y.dtype == x.dtype
+        assert helpers.rel_err(y, data[tag + "_y"]) <= tol, tag
+        gx, g_tau, g_eps = po.lift_compress_backward(x, gy, lt, le, dim)
+        assert helpers.rel_err(gx, data[tag + "_grad_x"]) <= tol, tag
+        ref_tau, ref_eps = data[tag + "_grad_params"]
+        ptol = 2e-5 if x.dtype == np.float32 else 1e-11  # the reference sums in the tensor's own precision
+        if use_lift:
+            assert abs(g_tau - ref_tau) <= ptol * max(1.0, abs(ref_tau)), (tag, g_tau, ref_tau)
+        if use_lc:
+            assert abs(g_eps - ref_eps) <= ptol * max(1.0, abs(ref_eps)), (tag, g_eps, ref_eps)
+
+
+def test_prologue_restatement_rejects_a_bad_dim():
+    from oracle import prologue_oracle as po
+
+    with pytest.raises(RuntimeError, match="3 not a valid dimension for a tensor if dimension 3"):
+        po.dilation_lift(np.zeros((2, 3, 4), np.float32), 1.0, 3)
+    with pytest.raises(RuntimeError, match="-4 not a valid dimension"):
+        po.dilation_lift(np.zeros((2, 3, 4), np.float32), 1.0, -4)
