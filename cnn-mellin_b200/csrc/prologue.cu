@@ -97,16 +97,15 @@ lift_compress_kernel(const T *__restrict__ x, T *__restrict__ y, const T *__rest
 //   y = w c, w = (t+1)^tau, c = log(eps + |x|)
 //   d y / d tau = y log(t+1);  d y / d eps = w / (eps + |x|);  d y / d x = w sign(x) / (eps + |x|)
 template <typename T>
-__device__ __forceinline__ T backward_element(T x, T gy, T w, T log_t1, const Params<T> &q, double &sum_tau,
-                                              double &sum_eps) {
+__device__ __forceinline__ T backward_element(T x, T gy, T w, T log_t1, const Params<T> &q, T &sum_tau, T &sum_eps) {
   const T gc = gy * w;
   T gx = gc;
   if (q.compress) {
     const T inv = T(1) / (q.eps + fabs(x));
-    sum_eps += (double)(gc * inv);
+    sum_eps += gc * inv;
     gx = x > T(0) ? gc * inv : (x < T(0) ? -gc * inv : T(0));
   }
-  if (q.lift) sum_tau += (double)(gc * compressed(x, q) * log_t1);
+  if (q.lift) sum_tau += gc * compressed(x, q) * log_t1;
   return gx;
 }
 
@@ -121,7 +120,9 @@ lift_compress_backward_kernel(const T *__restrict__ x, const T *__restrict__ gra
   __shared__ double warp_sums[2][kThreads / 32];
   const Params<T> q = load_params(tau_p, eps_p, log_domain);
   build_table(table, len, table_in_smem != 0, q);
-  double sum_tau = 0.0, sum_eps = 0.0;
+  // a thread adds its own few hundred terms in T (double-precision adds per element would cost more than the
+  // rest of the element's work); across threads and blocks the sums are carried in double
+  T thread_tau = T(0), thread_eps = T(0);
   const long long groups = total / VEC, step = (long long)gridDim.x * blockDim.x;
   for (long long g = blockIdx.x * (long long)blockDim.x + threadIdx.x; g < groups; g += step) {
     const long long i = g * VEC, t = axis_index<I>(i, inner, len);
@@ -131,16 +132,17 @@ lift_compress_backward_kernel(const T *__restrict__ x, const T *__restrict__ gra
       const float4 v = *reinterpret_cast<const float4 *>(x + i);
       const float4 gy = *reinterpret_cast<const float4 *>(grad_y + i);
       float4 o;
-      o.x = backward_element((T)v.x, (T)gy.x, w, log_t1, q, sum_tau, sum_eps);
-      o.y = backward_element((T)v.y, (T)gy.y, w, log_t1, q, sum_tau, sum_eps);
-      o.z = backward_element((T)v.z, (T)gy.z, w, log_t1, q, sum_tau, sum_eps);
-      o.w = backward_element((T)v.w, (T)gy.w, w, log_t1, q, sum_tau, sum_eps);
+      o.x = backward_element((T)v.x, (T)gy.x, w, log_t1, q, thread_tau, thread_eps);
+      o.y = backward_element((T)v.y, (T)gy.y, w, log_t1, q, thread_tau, thread_eps);
+      o.z = backward_element((T)v.z, (T)gy.z, w, log_t1, q, thread_tau, thread_eps);
+      o.w = backward_element((T)v.w, (T)gy.w, w, log_t1, q, thread_tau, thread_eps);
       *reinterpret_cast<float4 *>(grad_x + i) = o;
     } else {
-      grad_x[i] = backward_element(x[i], grad_y[i], w, log_t1, q, sum_tau, sum_eps);
+      grad_x[i] = backward_element(x[i], grad_y[i], w, log_t1, q, thread_tau, thread_eps);
     }
   }
   // block sums in a fixed order: lanes by shuffle tree, warps one after the other
+  double sum_tau = (double)thread_tau, sum_eps = (double)thread_eps;
   for (int off = 16; off > 0; off >>= 1) {
     sum_tau += __shfl_down_sync(0xffffffffu, sum_tau, off);
     sum_eps += __shfl_down_sync(0xffffffffu, sum_eps, off);
@@ -173,6 +175,18 @@ __global__ void lift_compress_finish_kernel(const double *__restrict__ block_sum
   }
 }
 
+// Blocks of `kernel` that one SM holds at a time.  The kernels walk the tensor in grid-sized strides, so the grid
+// must be what the device holds at once: a grid of 8 blocks per SM under a kernel that fits 6 runs as 1.33 waves.
+template <typename K>
+int resident_blocks(K kernel, size_t smem) {
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, smem) != cudaSuccess || per_sm < 1) {
+    (void)cudaGetLastError();
+    per_sm = 1;
+  }
+  return per_sm;
+}
+
 struct Plan {
   long long total;
   int blocks, vec, table_in_smem, wide_index;
@@ -195,8 +209,7 @@ int make_plan(const char *who, int64_t outer, int64_t len, int64_t inner, const 
   plan->table_in_smem = (size_t)len * sizeof(T) <= (size_t)kTableBytes ? 1 : 0;
   plan->smem = plan->table_in_smem ? (size_t)len * sizeof(T) : 0;
   const long long groups = plan->total / plan->vec, per_block = (long long)kThreads * 4;
-  plan->blocks = (int)std::max<long long>(
-      1, std::min<long long>((groups + per_block - 1) / per_block, std::min<long long>(kMaxBlocks, (long long)sm_count() * 8)));
+  plan->blocks = (int)std::max<long long>(1, std::min<long long>((groups + per_block - 1) / per_block, kMaxBlocks));
   return MELLIN_OK;
 }
 
@@ -208,6 +221,7 @@ int launch_forward(const T *x, const T *tau, const T *eps, int log_domain, int64
   if (rc != MELLIN_OK || plan.total == 0) return rc;
   auto st = static_cast<cudaStream_t>(stream);
   auto go = [&](auto kernel) {
+    plan.blocks = std::min(plan.blocks, sm_count() * resident_blocks(kernel, plan.smem));
     kernel<<<plan.blocks, kThreads, plan.smem, st>>>(x, y, tau, eps, log_domain, plan.total, len, inner,
                                                      plan.table_in_smem);
   };
@@ -238,6 +252,7 @@ int launch_backward(const T *x, const T *grad_y, const T *tau, const T *eps, int
   double *block_sums = static_cast<double *>(workspace);
   if (plan.total > 0) {
     auto go = [&](auto kernel) {
+      plan.blocks = std::min(plan.blocks, sm_count() * resident_blocks(kernel, plan.smem));
       kernel<<<plan.blocks, kThreads, plan.smem, st>>>(x, grad_y, grad_x, tau, eps, log_domain, plan.total, len, inner,
                                                        plan.table_in_smem, block_sums);
     };

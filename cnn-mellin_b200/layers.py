@@ -11,8 +11,10 @@ single-pass backward.  The parameter gradients are summed in a fixed order:
 two runs give the same bits.
 
 There is no CPU path: the functions raise on tensors that are not on a CUDA
-device.  ``ScaledGaussianNoise`` of the reference's file is training-time noise
-made of stock torch operators and has no counterpart here.
+device.  ``ScaledGaussianNoise`` (``layers.py:104-137`` there; imported by the
+reference's ``running.py:19``) is training-time noise outside the accelerated
+path: it is kept, on stock torch operators, only so that this module can stand
+in for the reference's file.
 """
 from typing import Optional
 
@@ -20,7 +22,8 @@ import torch
 
 import capi
 
-__all__ = ["dilation_lift", "log_compression", "lift_compress", "DilationLift", "LogCompression", "LogCompressionLift"]
+__all__ = ["dilation_lift", "log_compression", "lift_compress", "DilationLift", "LogCompression", "LogCompressionLift",
+           "ScaledGaussianNoise"]
 
 
 def _scalar_for(param: Optional[torch.Tensor], like: torch.Tensor) -> Optional[torch.Tensor]:
@@ -154,3 +157,24 @@ class LogCompressionLift(torch.nn.Module):
         log_tau = None if self.lift is None else self.lift.log_tau
         log_eps = None if self.log_compression is None else self.log_compression.log_eps
         return lift_compress(input, log_tau, log_eps, self.lift.dim if self.lift is not None else 0)
+
+
+class ScaledGaussianNoise(torch.nn.Module):
+    """Training only: adds zero-mean Gaussian noise whose deviation is ``eps`` times the largest magnitude along
+    ``dim``; the identity in evaluation mode (reference ``layers.py:24-38,104-137``).  Stock torch operators."""
+
+    __constants__ = ["dim", "eps"]
+
+    def __init__(self, dim: int = 1, eps: float = 1e-3):
+        super().__init__()
+        self.dim, self.eps = dim, eps
+
+    def extra_repr(self) -> str:
+        return f"dim={self.dim}, eps={self.eps}"
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        dim = _checked_dim(x, self.dim)
+        if not self.training:
+            return x
+        peak = x.abs().amax(dim, keepdim=True)
+        return x + (peak * self.eps) * torch.randn_like(x)

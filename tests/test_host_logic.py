@@ -122,3 +122,11 @@ def test_prologue_layers_keep_the_reference_names_and_refuse_the_cpu():
         pair(torch.zeros(2, 3, 4))
     x = torch.zeros(2, 3)
     assert layers.LogCompressionLift(False, False)(x) is x
+    # the noise layer the reference's training loop imports from the same file: identity in evaluation mode,
+    # deviation eps * max|x| along dim when training
+    noise = layers.ScaledGaussianNoise(1, 0.5)
+    x = torch.ones(4, 20000)
+    assert noise.eval()(x) is x
+    torch.manual_seed(1)
+    y = noise.train()(x)
+    assert abs(float((y - x).std()) - 0.5) < 0.02 and abs(float((y - x).mean())) < 0.02
