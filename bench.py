@@ -957,6 +957,11 @@ def run_ours(args):
     note("starting")
     ctx = Ctx(args)
     rank, world = ctx.rank, ctx.world
+    if args.prologue_only:
+        if world > 1:
+            raise SystemExit("--prologue-only is a single-GPU run")
+        print(json.dumps({"prologue": bench_prologue(ctx)}), flush=True)
+        return
     skip = set(args.skip.split(",")) if args.skip else set()
     sampler = ClockSampler(ctx.local_rank)
     if rank == 0:
@@ -1028,6 +1033,8 @@ def main():
                          "not for bench lines")
     ap.add_argument("--kernels-only", action="store_true",
                     help="one timed block of the headline kernels only (profiler captures)")
+    ap.add_argument("--prologue-only", action="store_true",
+                    help="only the prologue block (log compression + lift), single GPU (profiler captures)")
     ap.add_argument("--skip", default="", help="comma-separated blocks to leave out: train, layers, sweep, latency, prologue, incumbent")
     ap.add_argument("--engine", default="tensor_cores", choices=["tensor_cores", "cuda_cores"],
                     help="with --kernels-only: cuda_cores switches the tcgen05 kernels off (profiler captures of the "
