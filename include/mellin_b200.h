@@ -5,6 +5,15 @@
  * stream (passed as void*; a cudaStream_t is a pointer).  Nothing here
  * depends on PyTorch.  All calls are asynchronous with respect to the host:
  * they enqueue work on `stream` and return.  The caller owns every buffer.
+ * One exception: the FIRST call of a geometry (kernel / signal / output extents
+ * on the Mellin axis with s, d, p, u) on a device builds its index table on the
+ * host, allocates device memory for it and uploads it with a synchronous copy,
+ * so that call blocks, allocates, and cannot be part of a stream capture.  The
+ * tables (a few KB to a few MB each) are kept per device until
+ * mellin_clear_tables(); nothing evicts them, so a caller that feeds a 1-D
+ * Mellin operator signals of ever-changing length should call it now and then.
+ * The operator-level entry points without a workspace argument also keep one
+ * scratch arena per (device, stream), grown on demand and freed by the same call.
  *
  * Return value: MELLIN_OK (0) or one of the error codes below; a
  * human-readable description of the most recent failure on the calling thread
