@@ -229,16 +229,44 @@ struct TileWalker {
   int dat, dyt, dn, drank;       // `step` as digits (at, yt, n, rank): next() adds with carries, no divisions
   int eat, eyt, en, erank;       // `step_after` as digits; the two swap every round
   const int *order_s;
+#ifdef MELLIN_MASKED
+  // With per-utterance lengths the (n, yt) digits as walked are a PLACE in a list of the row's (n, yt) pairs
+  // that holds the pairs with data first and the pairs past their utterance's end (epilogue-only tiles) last:
+  // in walk order the dead tiles fall on the blocks at random and leave them 11-14 % apart in work; with the
+  // live tiles of a row contiguous the blocks end within 3-5 % of each other.
+  int wn, wyt;
+  const unsigned short *pairs;  // (n << 6 | yt) by place; nullptr: the digits are the tile
+#define WALK_N wn
+#define WALK_YT wyt
+  __device__ __forceinline__ void resolve(const TcParams &p) {
+    if (pairs != nullptr) {
+      const unsigned v = pairs[wn * p.y_tiles + wyt];
+      n = (int)(v >> 6), yt = (int)(v & 63u);
+    } else {
+      n = wn, yt = wyt;
+    }
+  }
+#else
+#define WALK_N n
+#define WALK_YT yt
+  __device__ __forceinline__ void resolve(const TcParams &) {}
+#endif
   __device__ __forceinline__ static void digits(const TcParams &p, int t, int &a, int &y, int &nn, int &r) {
     a = t % p.a_tiles, t /= p.a_tiles;
     y = t % p.y_tiles, t /= p.y_tiles;
     nn = t % p.N;
     r = t / p.N;
   }
-  __device__ __forceinline__ void init(const TcParams &p, const int *order_smem) {
+  __device__ __forceinline__ void init(const TcParams &p, const int *order_smem, const unsigned short *pairs_smem) {
     order_s = order_smem;
+#ifdef MELLIN_MASKED
+    pairs = pairs_smem;
+#else
+    (void)pairs_smem;
+#endif
     tile = blockIdx.x;
-    digits(p, tile, at, yt, n, rank);
+    digits(p, tile, at, WALK_YT, WALK_N, rank);
+    resolve(p);
     ox = rank < p.nox ? order_s[rank] : 0;
     step = 2 * (int)gridDim.x - 1 - 2 * (int)blockIdx.x;
     step_after = 2 * (int)blockIdx.x + 1;
@@ -250,13 +278,14 @@ struct TileWalker {
     at += dat;
     int carry = at >= p.a_tiles;
     at -= carry ? p.a_tiles : 0;
-    yt += dyt + carry;
-    carry = yt >= p.y_tiles;
-    yt -= carry ? p.y_tiles : 0;
-    n += dn + carry;
-    carry = n >= p.N;
-    n -= carry ? p.N : 0;
+    WALK_YT += dyt + carry;
+    carry = WALK_YT >= p.y_tiles;
+    WALK_YT -= carry ? p.y_tiles : 0;
+    WALK_N += dn + carry;
+    carry = WALK_N >= p.N;
+    WALK_N -= carry ? p.N : 0;
     rank += drank + carry;
+    resolve(p);
     ox = rank < p.nox ? order_s[rank] : 0;
     int t;
     t = step, step = step_after, step_after = t;
@@ -266,6 +295,39 @@ struct TileWalker {
     t = drank, drank = erank, erank = t;
   }
 };
+
+#ifdef MELLIN_MASKED
+// The list TileWalker::pairs: the (n, yt) pairs of one output row, those with yt * kTileM < lens_s[n] first, both
+// groups in (n, yt) order.  Built by warp 0 behind the cached lengths (the list and the lengths share the
+// kMaxLens * 4 bytes set aside for the lengths; a batch too large for that walks the tiles as they come).
+// Every thread of the block calls this (it ends in a barrier); lens_s must be complete.
+__device__ __forceinline__ const unsigned short *live_first_pairs(const TcParams &p, int *lens_s, int warp, int lane) {
+  const int U = p.N * p.y_tiles;
+  const bool fits = p.y_tiles <= 64 && p.N * 4 + U * 2 <= kMaxLens * 4;
+  unsigned short *pairs = reinterpret_cast<unsigned short *>(lens_s + p.N);
+  if (fits && warp == 0) {
+    int live_total = 0;
+    for (int base = 0; base < U; base += 32) {
+      const int u = base + lane, n = u / p.y_tiles, yt = u - n * p.y_tiles;
+      const bool live = u < U && yt * kTileM < lens_s[n < p.N ? n : 0];
+      live_total += __popc(__ballot_sync(0xffffffffu, live));
+    }
+    int n_live = 0, n_dead = 0;
+    const unsigned below = (1u << lane) - 1u;
+    for (int base = 0; base < U; base += 32) {
+      const int u = base + lane, n = u / p.y_tiles, yt = u - n * p.y_tiles;
+      const bool in = u < U, live = in && yt * kTileM < lens_s[n < p.N ? n : 0];
+      const unsigned m_live = __ballot_sync(0xffffffffu, live), m_dead = __ballot_sync(0xffffffffu, in && !live);
+      const unsigned short v = (unsigned short)((n << 6) | yt);
+      if (live) pairs[n_live + __popc(m_live & below)] = v;
+      else if (in) pairs[live_total + n_dead + __popc(m_dead & below)] = v;
+      n_live += __popc(m_live), n_dead += __popc(m_dead);
+    }
+  }
+  __syncthreads();
+  return fits ? pairs : nullptr;
+}
+#endif
 
 // This file is compiled twice.  As itself it is the kernel for layers whose
 // linear taps all fit one stage.  Included by tc_direct_taps.cu with
@@ -409,6 +471,11 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map,
   __syncthreads();
   tc::tc_fence_after_sync();
   const uint32_t tmem_base = ctl->tmem_base;
+#ifdef MELLIN_MASKED
+  const unsigned short *tile_pairs = live_first_pairs(p, lens_s, warp, lane);
+#else
+  const unsigned short *tile_pairs = nullptr;
+#endif
   if (p.w_res_bytes) {
     // weight chunk pair of every k-step of every table row (output-channel tile 0)
     if (tid == 0) {
@@ -438,7 +505,7 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map,
     int g = 0;  // accumulation intervals consumed so far
     PROF_BEGIN();
     TileWalker tc_;
-    for (tc_.init(p, order); tc_.tile < p.tiles; tc_.next(p)) {
+    for (tc_.init(p, order, tile_pairs); tc_.tile < p.tiles; tc_.next(p)) {
       // tcgen05.ld is warp-collective: keep every exit decision warp-uniform
       if (__any_sync(0xffffffffu, *abort_flag)) break;
       const int Kr = TILE_ROWS((rowptr[tc_.ox + 1] - rowptr[tc_.ox]) * p.Bp);
@@ -508,7 +575,7 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map,
     bool failed = false;
     PROF_BEGIN();
     TileWalker tc_;
-    for (tc_.init(p, order); tc_.tile < p.tiles && !*abort_flag && !failed; tc_.next(p)) {
+    for (tc_.init(p, order, tile_pairs); tc_.tile < p.tiles && !*abort_flag && !failed; tc_.next(p)) {
       const int Kr = TILE_ROWS((rowptr[tc_.ox + 1] - rowptr[tc_.ox]) * p.Bp);
       const int lead = (tc_.yt * kTileM + p.ws0) & 3;  // the copy started at the 16-byte boundary below
       STAGE_LOOP() {
@@ -565,7 +632,7 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map,
         (uint32_t)p.RWt * 16u + (p.w_res_bytes ? 0u : 2u * (uint32_t)p.TG * w_chunk_bytes);
     PROF_BEGIN();
     TileWalker tc_;
-    for (tc_.init(p, order); tc_.tile < p.tiles && !failed; tc_.next(p)) {
+    for (tc_.init(p, order, tile_pairs); tc_.tile < p.tiles && !failed; tc_.next(p)) {
       if (__any_sync(0xffffffffu, *abort_flag)) break;
       const int e0 = rowptr[tc_.ox];
       const int Kr = TILE_ROWS((rowptr[tc_.ox + 1] - e0) * p.Bp);
@@ -644,7 +711,7 @@ tc_direct_kernel(const TcParams p, const __grid_constant__ CUtensorMap in_map,
       bool failed = false;
       PROF_BEGIN();
       TileWalker tc_;
-      for (tc_.init(p, order); tc_.tile < p.tiles && !tc::uniform((uint32_t)*abort_flag) && !failed; tc_.next(p)) {
+      for (tc_.init(p, order, tile_pairs); tc_.tile < p.tiles && !tc::uniform((uint32_t)*abort_flag) && !failed; tc_.next(p)) {
         const int Kr = (int)tc::uniform((uint32_t)TILE_ROWS((rowptr[tc_.ox + 1] - rowptr[tc_.ox]) * p.Bp));
         uint32_t accumulate = 0;
         int left = 0;  // K-blocks left in the open accumulation interval
