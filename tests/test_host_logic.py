@@ -130,3 +130,22 @@ def test_prologue_layers_keep_the_reference_names_and_refuse_the_cpu():
     torch.manual_seed(1)
     y = noise.train()(x)
     assert abs(float((y - x).std()) - 0.5) < 0.02 and abs(float((y - x).mean())) < 0.02
+
+
+def test_prologue_entry_points_validate_before_touching_the_device():
+    """Argument checks of ``mellin_lift_compress_*`` answer on a host without a GPU: nothing is launched for them."""
+    import ctypes
+
+    lib = capi.lib()
+    i64, null = ctypes.c_int64, ctypes.c_void_p(0)
+    fwd = lib.mellin_lift_compress_f32
+    assert fwd(null, null, null, 1, i64(-1), i64(4), i64(4), null, null) == 1  # negative extent
+    assert b"negative extent" in lib.mellin_last_error()
+    assert fwd(null, null, null, 1, i64(2), i64(4), i64(4), null, null) == 1   # null tensors, 32 elements
+    assert b"null pointer" in lib.mellin_last_error()
+    assert fwd(null, null, null, 1, i64(0), i64(4), i64(4), null, null) == 0   # nothing to do
+    assert fwd(null, null, null, 1, i64(2 ** 40), i64(2 ** 20), i64(2 ** 20), null, null) == 4  # beyond 2^63 elements
+    bwd = lib.mellin_lift_compress_backward_f64
+    assert bwd(null, null, null, null, 0, i64(0), i64(4), i64(4), null, null, null, null, ctypes.c_size_t(0), null) == 3
+    assert b"workspace" in lib.mellin_last_error()
+    assert capi.lift_compress_workspace_bytes() == 4096 * 2 * 8
